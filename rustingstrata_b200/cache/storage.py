@@ -1,0 +1,32 @@
+"""Device storage behind the cache manager's page numbers and state slots.
+
+One tensor per cache group, [calls in the group, pages, 2 (K, V), kv heads, page_size,
+head_dim] in the engine's element type, so a (page, K|V, kv head) tile is one
+contiguous [page_size, head_dim] block; one float32 [max_seqs, numel] array per mixer
+call that keeps per-request state.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import torch
+
+from ..parts.spec import CacheNeed, StateNeed
+
+
+def allocate_caches(groups: Sequence[CacheNeed], group_calls: Sequence[Sequence[int]], num_pages: int, page_size: int,
+                    dtype: torch.dtype, device) -> List[torch.Tensor]:
+    out = []
+    for need, calls in zip(groups, group_calls):
+        out.append(torch.zeros((len(calls), num_pages, 2, need.n_kv_heads, page_size, need.head_dim), dtype=dtype,
+                               device=device))
+    return out
+
+
+def allocate_states(needs: Dict[int, StateNeed], max_seqs: int, device) -> Dict[int, torch.Tensor]:
+    return {i: torch.zeros((max_seqs, n.numel), dtype=torch.float32, device=device) for i, n in needs.items()}
+
+
+def cache_bytes_per_token(groups: Sequence[CacheNeed], group_calls: Sequence[Sequence[int]], dtype: torch.dtype) -> int:
+    es = torch.empty((), dtype=dtype).element_size()
+    return sum(2 * n.n_kv_heads * n.head_dim * es * len(c) for n, c in zip(groups, group_calls))

@@ -1,0 +1,71 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions.
+//
+// Every exported entry point is `extern "C"`, takes raw device pointers, sizes and
+// the CUDA stream to launch on, and returns the cudaError_t of the launch (0 = ok).
+// Element types are passed as small integer codes so one symbol serves the 32-bit
+// and the bfloat16 engine.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define RS_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum RsDtype : int { RS_F32 = 0, RS_BF16 = 1 };
+
+// status bits written by kernels that detect a bad input instead of faulting
+enum RsStatus : int {
+    RS_STATUS_BAD_TOKEN = 1,      // token id outside the vocabulary
+    RS_STATUS_BAD_PAGE = 2,       // block table entry outside the pool where a live key was expected
+    RS_STATUS_WAIT_EXPIRED = 4,   // a bounded wait on a barrier gave up
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// load element i of an array whose element type is only known at run time
+__device__ __forceinline__ float load_any(const void* p, int dt, size_t i) {
+    return dt == RS_F32 ? reinterpret_cast<const float*>(p)[i]
+                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+#define RS_DISPATCH_DTYPE(dt, T, ...)                                   \
+    do {                                                                \
+        if ((dt) == RS_F32) { using T = float; __VA_ARGS__; }           \
+        else if ((dt) == RS_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else return (int)cudaErrorInvalidValue;                         \
+    } while (0)
+
+static inline int rs_launch_result() { return (int)cudaGetLastError(); }

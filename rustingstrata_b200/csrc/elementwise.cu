@@ -1,0 +1,185 @@
+// Memory-bound kernels of the step: token embedding, RMSNorm (optionally gathering
+// rows), per-head QK-norm + rotary encoding + write of K and V into cache pages,
+// SiLU(gate)*up.  Each is templated on the activation element type so the 32-bit and
+// the bfloat16 engine run the same code; reductions and the rotation are float32.
+//
+// Reference counterparts (RustingStrata, src/cuda/kernels.cu): rms_norm :1504-1552,
+// rms_norm_rope :2196-2228, swiglu :1622-1625; host formulas src/ops.rs:3-7,14,36-45.
+#include "common.cuh"
+
+// --------------------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] as float32 (the residual stream is float32 in both engines).
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                             int H, int V, int* status) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicOr(status, RS_STATUS_BAD_TOKEN);
+        id = 0;
+    }
+    const T* row = table + (size_t)id * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<T>(row[i]);
+}
+
+RS_EXPORT int rs_embed(const void* table, int table_dt, const int* ids, float* out, int T_, int H, int V,
+                       int* status, void* stream) {
+    if (T_ <= 0) return 0;
+    RS_DISPATCH_DTYPE(table_dt, T,
+        embed_kernel<T><<<T_, 256, 0, (cudaStream_t)stream>>>((const T*)table, ids, out, H, V, status));
+    return rs_launch_result();
+}
+
+// --------------------------------------------------------------------------- RMSNorm
+// out[r, i] = x[src(r), i] * rsqrt(mean(x[src(r), :]^2) + eps) * w[i], src(r) = rows ? rows[r] : r.
+// x is the float32 residual stream; w is float32 or bfloat16; out is the activation type.
+// The sum of squares is float32 with a fixed order per row (thread-strided partials,
+// then a tree), so a row's result does not depend on what else is in the batch.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, long x_stride, const int* __restrict__ rows,
+                               const void* __restrict__ w, int w_dt, float eps, TO* __restrict__ out, long out_stride,
+                               int n) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, scratch);
+    const float s = 1.0f / sqrtf(ss / (float)n + eps);
+    TO* o = out + (size_t)r * out_stride;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * s * load_any(w, w_dt, i));
+}
+
+RS_EXPORT int rs_rmsnorm(const float* x, long x_stride, const int* rows, const void* w, int w_dt, float eps,
+                         void* out, int out_dt, long out_stride, int n_rows, int n, void* stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+    RS_DISPATCH_DTYPE(out_dt, TO,
+        rmsnorm_kernel<TO><<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, x_stride, rows, w, w_dt, eps, (TO*)out,
+                                                                        out_stride, n));
+    return rs_launch_result();
+}
+
+// --------------------------------------------------------------------------- QK-norm + RoPE + KV write
+// One warp per (token, head).  The fused projection row of a token is
+// [q heads | k heads | v heads], each head `hd` wide.  q heads and k heads get an
+// RMSNorm over hd with a weight shared by all heads (optional), then the NEOX rotation
+// of pairs (i, i + n_rot/2) with cos/sin taken from a table indexed by position
+// (optional).  q is written back in place; k and v go to the token's cache page:
+//   cache[page][0 = K, 1 = V][kv head][slot in page][hd],  page = table[seq][pos / page_size].
+// With write_kv == 0 the call reads another call's cache and only q is processed.
+template <typename T>
+__global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int n_q, int n_kv, int hd,
+                                       const void* __restrict__ q_w, const void* __restrict__ k_w, int w_dt, float eps,
+                                       const float* __restrict__ cos_sin, int n_rot,
+                                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                       const int* __restrict__ block_table, int table_stride, int page_size,
+                                       T* __restrict__ cache, long page_stride, int num_pages, int write_kv,
+                                       int n_tokens, int* status) {
+    const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n_tokens * heads_per_token) return;
+    const int t = warp / heads_per_token;
+    const int h = warp % heads_per_token;
+    const int pos = positions[t];
+    T* src = qkv + (size_t)t * row_stride + (size_t)h * hd;   // q heads, then k heads, then v heads are contiguous
+
+    T* dst = src;                                              // q: in place
+    if (h >= n_q) {
+        const int kvh = (h - n_q) % n_kv;
+        const int is_v = (h - n_q) / n_kv;
+        const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicOr(status, RS_STATUS_BAD_PAGE);
+            return;
+        }
+        dst = cache + (size_t)page * page_stride + ((size_t)(is_v * n_kv + kvh) * page_size + (pos % page_size)) * hd;
+        if (is_v) {
+            for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+            return;
+        }
+    }
+    const void* w = h < n_q ? q_w : k_w;
+    float scale = 1.f;
+    if (w != nullptr) {
+        float ss = 0.f;
+        for (int i = lane; i < hd; i += 32) { float v = to_f32<T>(src[i]); ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    const int half = n_rot / 2;
+    const float* cs = cos_sin ? cos_sin + (size_t)pos * n_rot : nullptr;   // [pos][cos(half) | sin(half)]
+    for (int i = lane; i < half; i += 32) {
+        float a = to_f32<T>(src[i]) * scale, b = to_f32<T>(src[i + half]) * scale;
+        if (w != nullptr) { a *= load_any(w, w_dt, i); b *= load_any(w, w_dt, i + half); }
+        if (cs) {
+            const float c = cs[i], s = cs[half + i];
+            const float ra = a * c - b * s, rb = a * s + b * c;
+            a = ra; b = rb;
+        }
+        dst[i] = from_f32<T>(a);
+        dst[i + half] = from_f32<T>(b);
+    }
+    for (int i = n_rot + lane; i < hd; i += 32) {               // dims beyond the rotated ones
+        float a = to_f32<T>(src[i]) * scale;
+        if (w != nullptr) a *= load_any(w, w_dt, i);
+        dst[i] = from_f32<T>(a);
+    }
+}
+
+RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, int n_kv, int hd, const void* q_w,
+                                 const void* k_w, int w_dt, float eps, const float* cos_sin, int n_rot,
+                                 const int* positions, const int* seq_of_token, const int* block_table,
+                                 int table_stride, int page_size, void* cache, long page_stride, int num_pages,
+                                 int write_kv, int n_tokens, int* status, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_rot % 2 || n_rot > hd) return (int)cudaErrorInvalidValue;
+    const long warps = (long)n_tokens * (n_q + (write_kv ? 2 * n_kv : 0));
+    const int threads = 256;
+    const long blocks = (warps * 32 + threads - 1) / threads;
+    RS_DISPATCH_DTYPE(dt, T,
+        qk_norm_rope_kv_kernel<T><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
+            (T*)qkv, row_stride, n_q, n_kv, hd, q_w, k_w, w_dt, eps, cos_sin, n_rot, positions, seq_of_token,
+            block_table, table_stride, page_size, (T*)cache, page_stride, num_pages, write_kv, n_tokens, status));
+    return rs_launch_result();
+}
+
+// --------------------------------------------------------------------------- SiLU(gate) * up
+// in: [rows, 2*I] with gate in columns [0, I) and up in [I, 2I); out: [rows, I].
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ in, long in_stride, T* __restrict__ out, long out_stride,
+                                int rows, int I) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)rows * I) return;
+    const int r = (int)(idx / I), c = (int)(idx % I);
+    const float g = to_f32<T>(in[(size_t)r * in_stride + c]);
+    const float u = to_f32<T>(in[(size_t)r * in_stride + I + c]);
+    out[(size_t)r * out_stride + c] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+RS_EXPORT int rs_silu_mul(const void* in, long in_stride, void* out, long out_stride, int dt, int rows, int I,
+                          void* stream) {
+    if (rows <= 0) return 0;
+    const long n = (long)rows * I;
+    RS_DISPATCH_DTYPE(dt, T,
+        silu_mul_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const T*)in, in_stride,
+                                                                                       (T*)out, out_stride, rows, I));
+    return rs_launch_result();
+}
+
+// --------------------------------------------------------------------------- residual add of a delta
+// x[r, :] += delta[r, :] in float32 (for parts that cannot add inside their last kernel).
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ d, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += to_f32<T>(d[i]);
+}
+
+RS_EXPORT int rs_residual_add(float* x, const void* delta, int dt, long n, void* stream) {
+    if (n <= 0) return 0;
+    RS_DISPATCH_DTYPE(dt, T,
+        residual_add_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, (const T*)delta, n));
+    return rs_launch_result();
+}

@@ -1,0 +1,288 @@
+"""The model runner: owns the model, its weights, the cache and the one step function.
+
+``step`` is the engine's only way to run the model.  It takes a batch of
+(request, its next tokens, the places whose logits are wanted) - portions of prompts
+beside single decoded tokens, cut anywhere - runs exactly those tokens as one batch
+against the cache earlier steps left, and returns the logits at the wanted places.
+Generation, the scheduler, the benchmark and trace replay all go through it.
+
+Reference: ``GpuModel::batch_rows`` (src/gpu_model/prefill.rs:781-845): rows of
+(slot, token, want_logits), consecutive rows of a slot at consecutive positions, K/V of
+every row stored before attention reads it, the head run on the wanted rows only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Mapping, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, GroupNeed, OutOfPages, allocate_caches, allocate_states, cache_bytes_per_token
+from ..config import EngineConfig, load_model_config, resolve_architecture
+from ..kernels import ops
+from ..models import CausalLM
+from ..parts import HostBatch, Runtime, StepContext
+from ..weights import load_checkpoint
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class StepError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the indices among them whose logits are wanted."""
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+class ModelRunner:
+    def __init__(self, arch, config, engine: EngineConfig, tensors_loader):
+        """Use :meth:`from_dir` or :meth:`from_random`; ``tensors_loader(needs, dtype, device)`` returns
+        name → device tensor for the model's manifest."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("rustingstrata_b200 runs on a CUDA device only; no GPU is visible")
+        self.arch, self.config, self.engine = arch, config, engine
+        self.device = torch.device(engine.device)
+        torch.cuda.set_device(self.device)
+        self.dtype = _TORCH_DTYPE[engine.dtype]
+        self.spec = arch.build_spec(config)
+        self.page_size = engine.page_size
+        self.num_pages = engine.pool_pages()
+        self.runtime = Runtime(self.dtype, self.device, engine.max_batch_tokens, engine.max_seqs,
+                               engine.max_logit_rows, engine.page_size, self.spec.max_positions,
+                               self.num_pages * engine.page_size)
+        self.model = CausalLM(self.spec, self.runtime)
+        tensors = tensors_loader(self.model.tensor_needs(), self.dtype, self.device)
+        self.model.load(tensors)
+        del tensors
+        self.vocab_size = self.spec.vocab_size
+        self.max_positions = self.spec.max_positions
+        # ---- cache and state
+        m = self.model
+        self.cache = CacheManager([GroupNeed(n.window) for n in m.cache_groups], self.page_size, self.num_pages,
+                                  engine.max_seqs)
+        self.caches = allocate_caches(m.cache_groups, m.group_calls, self.num_pages, self.page_size, self.dtype,
+                                      self.device)
+        self.states = allocate_states(m.state_needs, engine.max_seqs, self.device)
+        m.bind_storage(self.caches, self.states)
+        self.kv_bytes_per_token = cache_bytes_per_token(m.cache_groups, m.group_calls, self.dtype)
+        # ---- step metadata buffers (pinned host mirror + device), grown on demand
+        self._meta_host = None
+        self._meta_dev = None
+        self._meta_event = None
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_dir(cls, model_dir: str, engine: EngineConfig) -> "ModelRunner":
+        arch, config = load_model_config(model_dir)
+
+        def loader(needs, dtype, device):
+            cpu = load_checkpoint(model_dir, needs, dtype)
+            out = {}
+            for k in list(cpu):
+                out[k] = cpu.pop(k).to(device, non_blocking=False)
+            return out
+        return cls(arch, config, engine, loader)
+
+    @classmethod
+    def from_random(cls, config_dict: Mapping, engine: EngineConfig, seed: int = 0, std: float = 0.02,
+                    norm_std: float = 0.0) -> "ModelRunner":
+        """Weights drawn on the device (no file): projections and tables N(0, std) rounded to bfloat16,
+        norm scales 1 (+ N(0, norm_std)).  For benchmarks of sizes too large to write to disk first."""
+        arch = resolve_architecture(config_dict)
+        config = arch.config_class.from_dict(config_dict)
+
+        def loader(needs, dtype, device):
+            g = torch.Generator(device=device)
+            out = {}
+            for i, (name, need) in enumerate(needs.items()):
+                g.manual_seed((seed * 1000003 + i) & 0x7FFFFFFF)
+                if need.role == "norm":
+                    t = torch.ones(need.shape, dtype=torch.float32, device=device)
+                    if norm_std > 0:
+                        t += torch.randn(need.shape, generator=g, dtype=torch.float32, device=device) * norm_std
+                elif need.role == "int_table":
+                    t = torch.zeros(need.shape, dtype=torch.int32, device=device)
+                else:
+                    t = torch.empty(need.shape, dtype=torch.bfloat16, device=device)
+                    flat = t.view(-1)
+                    chunk = 1 << 26
+                    for s in range(0, flat.numel(), chunk):
+                        n = min(chunk, flat.numel() - s)
+                        flat[s:s + n] = (torch.randn(n, generator=g, dtype=torch.float32, device=device) * std
+                                         ).to(torch.bfloat16)
+                if dtype == torch.float32 and t.dtype == torch.bfloat16:
+                    t = t.to(torch.float32)
+                elif dtype == torch.bfloat16 and need.role == "norm":
+                    t = t.to(torch.bfloat16)
+                out[name] = t
+            return out
+        return cls(arch, config, engine, loader)
+
+    # ------------------------------------------------------------------ requests
+    def admit(self, rid: Hashable) -> int:
+        slot = self.cache.admit(rid)
+        for st in self.states.values():
+            st[slot].zero_()
+        return slot
+
+    def release(self, rid: Hashable) -> None:
+        self.cache.release(rid)
+
+    def length(self, rid: Hashable) -> int:
+        return self.cache.length(rid)
+
+    # ------------------------------------------------------------------ the step function
+    def _meta_buffers(self, n_ints: int):
+        if self._meta_host is None or self._meta_host.numel() < n_ints:
+            cap = max(n_ints, 1 << 14)
+            cap = 1 << (cap - 1).bit_length()
+            self._meta_host = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._meta_event = None
+        if self._meta_event is not None:
+            self._meta_event.synchronize()      # the previous upload has left the pinned buffer
+        return self._meta_host, self._meta_dev
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one batch.  Returns float32 logits [wanted, vocab] on the device, in the order of the
+        entries and of each entry's ``want`` (None when nothing is wanted).  Unknown requests are admitted.
+        On an error nothing advances: pages taken for the step are given back."""
+        eng = self.engine
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        ids = [e.rid for e in entries]
+        if len(set(ids)) != len(ids):
+            raise StepError("a request may appear once in a step")
+        if len(entries) > eng.max_seqs:
+            raise StepError(f"{len(entries)} requests in one step, the engine is built for {eng.max_seqs}")
+        q_lens = np.array([len(e.tokens) for e in entries], dtype=np.int32)
+        if (q_lens <= 0).any():
+            raise StepError("every entry needs at least one token")
+        T = int(q_lens.sum())
+        if T > eng.max_batch_tokens:
+            raise StepError(f"{T} tokens in one step, the engine is built for {eng.max_batch_tokens}")
+        R = sum(len(e.want) for e in entries)
+        if R > eng.max_logit_rows:
+            raise StepError(f"{R} logit rows wanted in one step, the engine is built for {eng.max_logit_rows}")
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if (tokens < 0).any() or (tokens >= self.vocab_size).any():
+            bad = int(tokens[(tokens < 0) | (tokens >= self.vocab_size)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+        for e, n in zip(entries, q_lens):
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.rid!r}: wanted place {w} is not among its {n} tokens")
+
+        admitted, reserved = [], []
+        try:
+            for e in entries:
+                if not self.cache.is_live(e.rid):
+                    self.admit(e.rid)
+                    admitted.append(e.rid)
+            old = np.array([self.cache.length(e.rid) for e in entries], dtype=np.int32)
+            kv_lens = old + q_lens
+            if (kv_lens > self.max_positions).any():
+                i = int(np.argmax(kv_lens > self.max_positions))
+                raise StepError(f"request {entries[i].rid!r} would reach {int(kv_lens[i])} positions, the model "
+                                f"has {self.max_positions}")
+            for e, n in zip(entries, q_lens):
+                self.cache.reserve(e.rid, int(n))
+                reserved.append(e.rid)
+        except Exception:
+            for rid in reserved:
+                self.cache.rollback(rid)
+            for rid in admitted:
+                self.cache.release(rid)
+            raise
+
+        ctx = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R)
+        try:
+            logits = self.model.forward(ctx)
+        except Exception:
+            for rid in reserved:
+                self.cache.rollback(rid)
+            for rid in admitted:
+                self.cache.release(rid)
+            raise
+        for e, n in zip(entries, q_lens):
+            self.cache.commit(e.rid, int(n))
+        self.steps_run += 1
+        return logits
+
+    def _build_context(self, entries, tokens, q_lens, old, kv_lens, T, R) -> StepContext:
+        S = len(entries)
+        q_start = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        seq_of_token = np.repeat(np.arange(S, dtype=np.int32), q_lens)
+        positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start[:-1], q_lens) + np.repeat(old, q_lens)
+                     ).astype(np.int32)
+        slots = np.array([self.cache.slot(e.rid) for e in entries], dtype=np.int32)
+        logit_rows = np.array([q_start[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
+        n_groups = len(self.cache.groups)
+        tables = []
+        for g in range(n_groups):
+            rows = [self.cache.table(e.rid, g) for e in entries]
+            width = max(1, max(len(r) for r in rows))
+            tab = np.full((S, width), -1, dtype=np.int32)
+            for i, r in enumerate(rows):
+                tab[i, :len(r)] = r
+            tables.append(tab)
+        batch = HostBatch(n_tokens=T, n_seqs=S, q_lens=q_lens, kv_lens=kv_lens.astype(np.int32), q_start=q_start,
+                          state_slots=slots, first_step=(old == 0).astype(np.int32), page_size=self.page_size,
+                          max_blocks=[t.shape[1] for t in tables])
+        plans = self.model.plan(batch)
+
+        arrays = [("token_ids", tokens.astype(np.int32)), ("positions", positions), ("seq_of_token", seq_of_token),
+                  ("q_start", q_start), ("kv_len", batch.kv_lens), ("state_slots", slots), ("logit_rows", logit_rows)]
+        arrays += [(("table", g), t.reshape(-1)) for g, t in enumerate(tables)]
+        for key, plan in plans.items():
+            for name, val in plan.items():
+                if isinstance(val, np.ndarray):
+                    arrays.append((("plan", key, name), val.astype(np.int32, copy=False).reshape(-1)))
+        offsets, total = [], 0
+        for _, a in arrays:
+            offsets.append(total)
+            total += _align(max(1, a.size))
+        host, dev = self._meta_buffers(total)
+        hv = host.numpy()
+        for (_, a), off in zip(arrays, offsets):
+            hv[off:off + a.size] = a
+        dev[:total].copy_(host[:total], non_blocking=True)
+        self._meta_event = torch.cuda.Event()
+        self._meta_event.record()
+        view = {name: dev[off:off + max(1, a.size)] for (name, a), off in zip(arrays, offsets)}
+        dev_plans: Dict = {}
+        for key, plan in plans.items():
+            dev_plans[key] = {name: (view[("plan", key, name)] if isinstance(val, np.ndarray) else val)
+                              for name, val in plan.items()}
+        block_tables = [view[("table", g)][: S * tables[g].shape[1]].view(S, tables[g].shape[1])
+                        for g in range(n_groups)]
+        return StepContext(n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=view["token_ids"],
+                           positions=view["positions"], seq_of_token=view["seq_of_token"], q_start=view["q_start"],
+                           kv_len=view["kv_len"], state_slots=view["state_slots"], logit_rows=view["logit_rows"],
+                           block_tables=block_tables, status=self.status, host=batch, plans=dev_plans)
+
+    def check_status(self) -> None:
+        """Waits for the device and raises if a kernel of an earlier step flagged a bad input."""
+        self._status_host.copy_(self.status, non_blocking=False)
+        code = int(self._status_host[0])
+        if code:
+            self.status.zero_()
+            what = [n for b, n in ((ops.STATUS_BAD_TOKEN, "token id outside the vocabulary"),
+                                   (ops.STATUS_BAD_PAGE, "block table entry outside the page pool"),
+                                   (ops.STATUS_WAIT_EXPIRED, "a bounded wait inside a kernel gave up"),
+                                   (ops.STATUS_NON_FINITE, "logits are not finite")) if code & b]
+            raise StepError("device status: " + "; ".join(what))

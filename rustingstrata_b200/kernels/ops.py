@@ -1,0 +1,263 @@
+"""Python launchers of the CUDA kernels: torch tensors in, raw pointers out.
+
+Every function launches on torch's current CUDA stream, checks what it can on the
+host (devices, element types, shapes, contiguity, alignment) and raises on a bad
+launch.  There is no CPU path and no library fallback: if the extension cannot be
+built or loaded the first call raises :class:`~.build.KernelBuildError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_long, c_float, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_BAD_TOKEN = 1
+STATUS_BAD_PAGE = 2
+STATUS_WAIT_EXPIRED = 4
+STATUS_NON_FINITE = 8
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported element type {t.dtype} (float32 and bfloat16 only)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel launchers take CUDA tensors only; there is no CPU path")
+
+
+def _rows_contiguous(t: torch.Tensor, name: str):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be 2-D with unit stride along its last axis, got shape {tuple(t.shape)} "
+                          f"strides {t.stride()}")
+
+
+_core = None
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = load_library("core")
+        lib.rs_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_rmsnorm.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_long,
+                                   c_int, c_int, c_void_p]
+        lib.rs_qk_norm_rope_kv.argtypes = [c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                           c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                           c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_silu_mul.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p]
+        lib.rs_residual_add.argtypes = [c_void_p, c_void_p, c_int, c_long, c_void_p]
+        lib.rs_linear_simt.argtypes = [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
+                                       c_int, c_int, c_int, c_int, c_void_p]
+        lib.rs_attention_simt.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int,
+                                          c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_void_p]
+        lib.rs_attention_simt_q_per_cta.argtypes = [c_int, c_int]
+        lib.rs_attention_simt_partial_floats.argtypes = [c_int, c_int, c_int]
+        lib.rs_attention_simt_partial_floats.restype = c_long
+        lib.rs_sample.argtypes = [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+        _core = lib
+    return _core
+
+
+# ----------------------------------------------------------------------------- elementwise
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] as float32.  ids int32 [T]; out float32 [T, H]."""
+    _cuda(table, ids, out, status)
+    T, H = out.shape
+    if ids.dtype != torch.int32 or out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embed: ids must be int32, out contiguous float32, table contiguous")
+    if table.shape[1] != H or ids.numel() < T:
+        raise KernelError(f"embed: table {tuple(table.shape)} / ids {ids.numel()} do not fit out {tuple(out.shape)}")
+    _check(core().rs_embed(_ptr(table), dtype_code(table), _ptr(ids), _ptr(out), T, H, table.shape[0], _ptr(status),
+                           _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight.  x float32 [*, n]."""
+    _cuda(x, weight, out, rows)
+    _rows_contiguous(x, "rmsnorm x")
+    _rows_contiguous(out, "rmsnorm out")
+    n = x.shape[1]
+    if x.dtype != torch.float32:
+        raise KernelError("rmsnorm reads the float32 residual stream")
+    if weight.numel() != n or out.shape[1] != n or not weight.is_contiguous():
+        raise KernelError(f"rmsnorm: weight {tuple(weight.shape)} / out {tuple(out.shape)} do not fit width {n}")
+    if n_rows is None:
+        n_rows = out.shape[0] if rows is not None else x.shape[0]
+    if n_rows > out.shape[0] or (rows is None and n_rows > x.shape[0]):
+        raise KernelError("rmsnorm: more rows than the buffers hold")
+    if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n_rows):
+        raise KernelError("rmsnorm: rows must be int32 with n_rows entries")
+    _check(core().rs_rmsnorm(_ptr(x), x.stride(0), _ptr(rows), _ptr(weight), dtype_code(weight), float(eps),
+                             _ptr(out), dtype_code(out), out.stride(0), n_rows, n, _stream()), "rmsnorm")
+
+
+def qk_norm_rope_kv(qkv: torch.Tensor, n_tokens: int, n_q: int, n_kv: int, head_dim: int,
+                    q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                    cos_sin: Optional[torch.Tensor], n_rot: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                    block_table: torch.Tensor, page_size: int, cache: torch.Tensor, write_kv: bool,
+                    status: torch.Tensor) -> None:
+    """Per-head norm and rotation of q (in place) and k, and the write of k and v into their pages.
+
+    qkv: [T, (n_q + 2 n_kv) * head_dim] (only the q part when ``write_kv`` is false);
+    cache: [pages, 2, n_kv, page_size, head_dim] of the same element type.
+    """
+    _cuda(qkv, q_weight, k_weight, cos_sin, positions, seq_of_token, block_table, cache, status)
+    _rows_contiguous(qkv, "qkv")
+    need = (n_q + (2 * n_kv if write_kv else 0)) * head_dim
+    if qkv.shape[1] < need or qkv.shape[0] < n_tokens:
+        raise KernelError(f"qk_norm_rope_kv: qkv {tuple(qkv.shape)} is smaller than {n_tokens} x {need}")
+    if cache.dtype != qkv.dtype or not cache.is_contiguous():
+        raise KernelError("qk_norm_rope_kv: cache must be contiguous and of the activations' element type")
+    if tuple(cache.shape[1:]) != (2, n_kv, page_size, head_dim):
+        raise KernelError(f"qk_norm_rope_kv: cache shape {tuple(cache.shape)} is not [pages, 2, {n_kv}, {page_size}, "
+                          f"{head_dim}]")
+    w_dt = F32
+    for w in (q_weight, k_weight):
+        if w is not None:
+            if w.numel() != head_dim or not w.is_contiguous():
+                raise KernelError("qk_norm_rope_kv: norm weights must hold head_dim values")
+            w_dt = dtype_code(w)
+    if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+        raise KernelError("qk_norm_rope_kv: q and k norm weights must share an element type")
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.shape[1] != n_rot or
+                                not cos_sin.is_contiguous()):
+        raise KernelError("qk_norm_rope_kv: cos_sin must be contiguous float32 [positions, n_rot]")
+    for name, t in (("positions", positions), ("seq_of_token", seq_of_token), ("block_table", block_table)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"qk_norm_rope_kv: {name} must be int32")
+    _check(core().rs_qk_norm_rope_kv(
+        _ptr(qkv), dtype_code(qkv), qkv.stride(0), n_q, n_kv, head_dim, _ptr(q_weight), _ptr(k_weight), w_dt,
+        float(eps), _ptr(cos_sin), n_rot, _ptr(positions), _ptr(seq_of_token), _ptr(block_table),
+        block_table.stride(0), page_size, _ptr(cache), cache.stride(0), cache.shape[0], 1 if write_kv else 0,
+        n_tokens, _ptr(status), _stream()), "qk_norm_rope_kv")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, I + c], I = out.shape[1]."""
+    _cuda(gate_up, out)
+    _rows_contiguous(gate_up, "gate_up")
+    _rows_contiguous(out, "out")
+    I = out.shape[1]
+    if gate_up.shape[1] != 2 * I or gate_up.dtype != out.dtype or n_rows > min(gate_up.shape[0], out.shape[0]):
+        raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} does not fit out {tuple(out.shape)}")
+    _check(core().rs_silu_mul(_ptr(gate_up), gate_up.stride(0), _ptr(out), out.stride(0), dtype_code(out), n_rows, I,
+                              _stream()), "silu_mul")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor, n_rows: int) -> None:
+    """x[:n_rows] += delta[:n_rows] in float32 (both contiguous, same width)."""
+    _cuda(x, delta)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not delta.is_contiguous() or x.shape[1] != delta.shape[1]:
+        raise KernelError("residual_add: x must be contiguous float32 and delta contiguous of the same width")
+    _check(core().rs_residual_add(_ptr(x), _ptr(delta), dtype_code(delta), n_rows * x.shape[1], _stream()),
+           "residual_add")
+
+
+# ----------------------------------------------------------------------------- matrix products
+def linear_simt(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False) -> None:
+    """out[:n_rows] (=|+=) a[:n_rows] @ weight.T on CUDA cores, float32 accumulation."""
+    _cuda(a, weight, out)
+    _rows_contiguous(a, "a")
+    _rows_contiguous(weight, "weight")
+    _rows_contiguous(out, "out")
+    N, K = weight.shape
+    if a.shape[1] != K or out.shape[1] != N or n_rows > min(a.shape[0], out.shape[0]):
+        raise KernelError(f"linear: a {tuple(a.shape)} x weight {tuple(weight.shape)} -> out {tuple(out.shape)} "
+                          f"for {n_rows} rows does not fit")
+    _check(core().rs_linear_simt(_ptr(a), dtype_code(a), a.stride(0), _ptr(weight), dtype_code(weight),
+                                 weight.stride(0), _ptr(out), dtype_code(out), out.stride(0), n_rows, N, K,
+                                 1 if accumulate else 0, _stream()), "linear_simt")
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False) -> None:
+    """The engine's matrix product: picks the kernel for the element types and the shape."""
+    linear_simt(a, weight, out, n_rows, accumulate)
+
+
+# ----------------------------------------------------------------------------- attention
+def attention_q_per_cta(n_q: int, n_kv: int) -> int:
+    return int(core().rs_attention_simt_q_per_cta(n_q, n_kv))
+
+
+def attention_partial_floats(total_splits: int, n_q: int, head_dim: int) -> int:
+    return int(core().rs_attention_simt_partial_floats(total_splits, n_q, head_dim))
+
+
+def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                   q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
+                   head_dim: int, page_size: int, window: int, scale: float, decode: bool, status: torch.Tensor,
+                   split_keys: int = 128, max_splits: int = 1, split_start: Optional[torch.Tensor] = None,
+                   total_splits: int = 0, partial: Optional[torch.Tensor] = None) -> None:
+    """Paged causal attention (see csrc/attention_simt.cu).  q/out: [T, >= n_q*head_dim] views."""
+    _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if q.dtype != cache.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, out and cache must share an element type")
+    if tuple(cache.shape[1:]) != (2, n_kv, page_size, head_dim) or not cache.is_contiguous():
+        raise KernelError(f"attention: cache shape {tuple(cache.shape)} is not [pages, 2, {n_kv}, {page_size}, {head_dim}]")
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"attention: head size {head_dim} is not a multiple of 16 up to 256")
+    if n_q % n_kv:
+        raise KernelError(f"attention: {n_q} query heads are not a multiple of {n_kv} key/value heads")
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"attention: {name} must be int32")
+    if decode:
+        need = attention_partial_floats(total_splits, n_q, head_dim)
+        if split_start is None or split_start.dtype != torch.int32:
+            raise KernelError("attention: the decode form needs int32 split_start")
+        if partial is None or partial.dtype != torch.float32 or partial.numel() < need:
+            raise KernelError(f"attention: the decode form needs {need} float32 values of partial workspace")
+    _check(core().rs_attention_simt(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q), _ptr(cache), cache.stride(0), cache.shape[0],
+        page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q,
+        n_kv, head_dim, int(window), float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start),
+        _ptr(partial),
+        _ptr(status), _stream()), "attention_simt")
+
+
+# ----------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, n_rows: int, out: torch.Tensor, status: torch.Tensor,
+           temps: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None) -> None:
+    """out[r] = argmax of row r when temps is None or temps[r] <= 0, else a draw at temperature temps[r]."""
+    _cuda(logits, out, status, temps, uniforms)
+    _rows_contiguous(logits, "logits")
+    if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < n_rows:
+        raise KernelError("sample: logits float32, out int32 with n_rows entries")
+    if temps is not None and (uniforms is None or temps.dtype != torch.float32 or uniforms.dtype != torch.float32):
+        raise KernelError("sample: temps and uniforms must both be float32")
+    _check(core().rs_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(temps), _ptr(uniforms),
+                            _ptr(out), _ptr(status), _stream()), "sample")

@@ -1,0 +1,156 @@
+"""Attention mixer over a paged key/value cache.
+
+Reference (src/model.rs:747-801; device decode path src/gpu_model.rs:3181-3277, batch
+path src/gpu_model/prefill.rs:811-828): q/k/v projections without biases, optional
+per-head RMSNorm on q and k with one weight shared by all heads, rotation, the new k
+and v stored at the token's position before any query of the step reads the cache,
+query head i reading kv head i // (n_heads / n_kv_heads), score scale 1/sqrt(head_dim),
+causal over all keys or over the most recent ``window`` keys, output projection added
+to the residual stream.
+
+Everything that distinguishes one architecture's attention from another's is a
+parameter: head counts, head size, whether q/k are normed and with which eps, the
+window, the score scale, which position encoding is applied, and whether this call
+projects keys and values at all (a call that reads another call's cache does not).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .base import CallInfo, HostBatch, Mixer, StepContext
+from .registry import register_part
+from .spec import CacheNeed, TensorNeed
+
+SPLIT_KEYS = 128     # keys per split of the decode form; fixed so a position's reduction order never changes
+
+
+def decode_splits(kv_len: np.ndarray, window: int) -> np.ndarray:
+    """How many SPLIT_KEYS-aligned splits hold the visible keys of a single query at position kv_len-1."""
+    lo = np.maximum(0, kv_len - window) if window > 0 else np.zeros_like(kv_len)
+    return (kv_len + SPLIT_KEYS - 1) // SPLIT_KEYS - lo // SPLIT_KEYS
+
+
+@register_part("mixer", "paged_attention")
+class PagedAttention(Mixer):
+    """params: hidden, n_heads, n_kv_heads, head_dim, qk_norm (bool), eps, window (int or None),
+    scale (float or None = 1/sqrt(head_dim)), kv_projection (bool, default True).
+    tensors: q_proj, k_proj, v_proj, o_proj, and q_norm, k_norm when qk_norm."""
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden"])
+        self.n_heads = int(p["n_heads"])
+        self.n_kv = int(p["n_kv_heads"])
+        self.hd = int(p["head_dim"])
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("eps", 0.0))
+        self.window = int(p["window"]) if p.get("window") else 0
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
+        self.kv_projection = bool(p.get("kv_projection", True))
+        self.position = position
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"paged_attention: {self.n_heads} heads are not a multiple of {self.n_kv} kv heads")
+        if self.hd % 16 or not 16 <= self.hd <= 256:
+            raise ValueError(f"paged_attention: head size {self.hd} is not supported by the attention kernels "
+                             f"(multiples of 16 from 16 to 256)")
+        self.q_width = self.n_heads * self.hd
+        self.kv_width = self.n_kv * self.hd
+        self.qkv_width = self.q_width + (2 * self.kv_width if self.kv_projection else 0)
+        self.q_per_cta = None
+        rt = runtime
+        rt.scratch("qkv", rt.max_batch_tokens, self.q_width + 2 * self.kv_width)
+        rt.scratch("attn_out", rt.max_batch_tokens, self.q_width)
+        max_total_splits = rt.pool_tokens // SPLIT_KEYS + rt.max_seqs + 1
+        rt.scratch("attn_partial", 1, max_total_splits * self.n_heads * (self.hd + 2), torch.float32)
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    # ---------------------------------------------------------------- weights
+    def tensor_needs(self):
+        t = self.spec.tensors
+        needs = {t["q_proj"]: TensorNeed((self.q_width, self.hidden)),
+                 t["o_proj"]: TensorNeed((self.hidden, self.q_width))}
+        if self.kv_projection:
+            needs[t["k_proj"]] = TensorNeed((self.kv_width, self.hidden))
+            needs[t["v_proj"]] = TensorNeed((self.kv_width, self.hidden))
+        if self.qk_norm:
+            needs[t["q_norm"]] = TensorNeed((self.hd,), "norm")
+            if self.kv_projection:
+                needs[t["k_norm"]] = TensorNeed((self.hd,), "norm")
+        return needs
+
+    def load(self, tensors):
+        t = self.spec.tensors
+        mats = [tensors[t["q_proj"]]]
+        if self.kv_projection:
+            mats += [tensors[t["k_proj"]], tensors[t["v_proj"]]]
+        if len({m.dtype for m in mats}) != 1:
+            raise ValueError("paged_attention: q, k and v projections must share an element type")
+        # one [q | k | v] matrix so the three projections are one product (the reference runs
+        # q+k as one launch and v beside it, src/gpu_model.rs:3190)
+        self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0].contiguous()
+        self.w_o = tensors[t["o_proj"]].contiguous()
+        if self.qk_norm:
+            self.q_norm_w = tensors[t["q_norm"]].contiguous()
+            self.k_norm_w = tensors[t["k_norm"]].contiguous() if self.kv_projection else None
+
+    # ---------------------------------------------------------------- state
+    def cache_need(self):
+        return CacheNeed(self.n_kv, self.hd, self.window or None)
+
+    # ---------------------------------------------------------------- planning
+    def plan_key(self):
+        if self.q_per_cta is None:
+            self.q_per_cta = ops.attention_q_per_cta(self.n_heads, self.n_kv)
+        return ("paged_attention", self.q_per_cta, self.window)
+
+    def build_plan(self, batch: HostBatch):
+        """Work lists: sequences with one query take the split (decode) form, the rest are cut into query tiles."""
+        qpc = self.q_per_cta
+        single = batch.q_lens == 1
+        dec = np.nonzero(single)[0].astype(np.int32)
+        splits = decode_splits(batch.kv_lens[dec], self.window).astype(np.int32) if len(dec) else np.zeros(0, np.int32)
+        split_start = np.zeros(len(dec) + 1, np.int32)
+        np.cumsum(splits, out=split_start[1:])
+        tiles = []
+        for s in np.nonzero(~single)[0]:
+            offs = np.arange(0, batch.q_lens[s], qpc, dtype=np.int32)
+            tiles.append(np.stack([np.full_like(offs, s), offs], axis=1))
+        pre = np.concatenate(tiles, axis=0).astype(np.int32) if tiles else np.zeros((0, 2), np.int32)
+        return {"decode_work": dec, "split_start": split_start, "prefill_work": pre.reshape(-1),
+                "n_decode": int(len(dec)), "n_prefill": int(pre.shape[0]),
+                "max_splits": int(splits.max()) if len(dec) else 0, "total_splits": int(split_start[-1])}
+
+    # ---------------------------------------------------------------- the step
+    def forward(self, h, residual, ctx: StepContext, call: CallInfo):
+        rt = self.runtime
+        T = ctx.n_tokens
+        write_kv = call.writes_cache
+        if write_kv and not self.kv_projection:
+            raise RuntimeError("paged_attention: a call without key/value projections must read another call's cache")
+        width = self.qkv_width if write_kv else self.q_width
+        qkv = rt.get_scratch("qkv")[:, :width]
+        w = self.w_qkv if write_kv else self.w_qkv[: self.q_width]
+        ops.linear(h, w, qkv, T)
+        table = ctx.block_tables[call.cache_group]
+        pos = self.position
+        ops.qk_norm_rope_kv(qkv, T, self.n_heads, self.n_kv, self.hd, self.q_norm_w, self.k_norm_w, self.eps,
+                            pos.cos_sin if pos is not None else None, pos.n_rot if pos is not None else 0,
+                            ctx.positions, ctx.seq_of_token, table, rt.page_size, call.cache, write_kv, ctx.status)
+        out = rt.get_scratch("attn_out")[:, : self.q_width]
+        plan = ctx.plans[self.plan_key()]
+        common = dict(q=qkv, out=out, cache=call.cache, block_table=table, q_start=ctx.q_start, kv_len=ctx.kv_len,
+                      n_q=self.n_heads, n_kv=self.n_kv, head_dim=self.hd, page_size=rt.page_size, window=self.window,
+                      scale=self.scale, status=ctx.status)
+        if plan["n_prefill"]:
+            ops.attention_simt(work=plan["prefill_work"], n_work=plan["n_prefill"], decode=False, **common)
+        if plan["n_decode"]:
+            ops.attention_simt(work=plan["decode_work"], n_work=plan["n_decode"], decode=True, split_keys=SPLIT_KEYS,
+                               max_splits=plan["max_splits"], split_start=plan["split_start"],
+                               total_splits=plan["total_splits"],
+                               partial=rt.get_scratch("attn_partial", torch.float32), **common)
+        ops.linear(out, self.w_o, residual, T, accumulate=True)

@@ -1,0 +1,187 @@
+"""Interfaces that every part implements, and the objects parts are handed.
+
+The reference passes raw device addresses through a ~70-method backend trait
+(src/backend.rs:98-443) and hard-codes the layer loop per architecture
+(src/gpu_model.rs:3072-3423).  Here a part is a small object with three duties:
+
+* say which checkpoint tensors it wants (:meth:`Part.tensor_needs`) and take them
+  (:meth:`Part.load`);
+* say what it keeps between steps (:meth:`Mixer.cache_need`, :meth:`Mixer.state_need`);
+* run on the tokens of one step (:meth:`forward`), reading the step's metadata from a
+  :class:`StepContext`.
+
+A part never looks at the model it is in.  Sizes and constants come from
+``PartSpec.params``; buffers come from the :class:`Runtime`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .spec import CacheNeed, PartSpec, StateNeed, TensorNeed
+
+
+class Runtime:
+    """What a part may use at build time: element type, device, limits, shared scratch buffers."""
+
+    def __init__(self, dtype: torch.dtype, device: torch.device, max_batch_tokens: int, max_seqs: int,
+                 max_logit_rows: int, page_size: int, max_positions: int, pool_tokens: int):
+        self.dtype = dtype
+        self.device = device
+        self.max_batch_tokens = max_batch_tokens
+        self.max_seqs = max_seqs
+        self.max_logit_rows = max_logit_rows
+        self.page_size = page_size
+        self.max_positions = max_positions
+        self.pool_tokens = pool_tokens          # tokens one cache group's page pool holds
+        self._buffers: Dict[str, torch.Tensor] = {}
+        self._wanted: Dict[str, tuple] = {}
+        self._shared: Dict[Any, Any] = {}
+
+    @property
+    def precise(self) -> bool:
+        return self.dtype == torch.float32
+
+    def scratch(self, name: str, rows: int, width: int, dtype: Optional[torch.dtype] = None) -> None:
+        """Declares a [rows, width] buffer shared by every part that asks for the same name and element
+        type (sized for the largest request).  It is allocated at its first use; contents do not survive
+        from one part call to the next."""
+        dtype = dtype or self.dtype
+        key = f"{name}:{dtype}"
+        r, w = self._wanted.get(key, (0, 0, None))[:2]
+        self._wanted[key] = (max(r, rows), max(w, width), dtype)
+        cur = self._buffers.get(key)
+        if cur is not None and (cur.shape[0] < rows or cur.shape[1] < width):
+            del self._buffers[key]
+
+    def get_scratch(self, name: str, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        key = f"{name}:{dtype or self.dtype}"
+        cur = self._buffers.get(key)
+        if cur is None:
+            rows, width, dt = self._wanted[key]
+            cur = torch.empty((rows, width), dtype=dt, device=self.device)
+            self._buffers[key] = cur
+        return cur
+
+    def shared(self, key, make):
+        """One object per key for the whole model (e.g. a rotation table shared by all layers)."""
+        if key not in self._shared:
+            self._shared[key] = make()
+        return self._shared[key]
+
+
+@dataclass
+class HostBatch:
+    """The step's batch as the host knows it (numpy int32 arrays of length n_seqs unless noted)."""
+    n_tokens: int
+    n_seqs: int
+    q_lens: np.ndarray            # tokens of each sequence in this step
+    kv_lens: np.ndarray           # keys of each sequence after this step
+    q_start: np.ndarray           # [n_seqs + 1] first token row of each sequence
+    state_slots: np.ndarray       # state slot of each sequence
+    first_step: np.ndarray        # 1 where the sequence has no earlier tokens
+    page_size: int
+    max_blocks: List[int]         # per cache group: width of the block tables of this step
+
+
+@dataclass
+class CallInfo:
+    """Where one entry of the run order keeps its things."""
+    index: int                            # position in the run order
+    layer: int
+    cache_group: Optional[int] = None     # page pool ("cache group") of the cache this call uses
+    cache: Optional[torch.Tensor] = None  # [pages, 2, n_kv, page_size, head_dim] view of that cache
+    writes_cache: bool = True             # False when the call reads another call's cache
+    state: Optional[torch.Tensor] = None  # [max_seqs, numel] float32 per-request state of this call
+
+
+@dataclass
+class StepContext:
+    """Device-side metadata of one step; all index tensors are int32."""
+    n_tokens: int
+    n_seqs: int
+    n_logit_rows: int
+    token_ids: torch.Tensor        # [T]
+    positions: torch.Tensor        # [T] position of each token in its sequence
+    seq_of_token: torch.Tensor     # [T] index of the token's sequence within this step
+    q_start: torch.Tensor          # [S + 1]
+    kv_len: torch.Tensor           # [S]
+    state_slots: torch.Tensor      # [S]
+    logit_rows: torch.Tensor       # [R] token rows whose logits are wanted
+    block_tables: List[torch.Tensor]   # per cache group [S, max_blocks]
+    status: torch.Tensor           # [1] error bits set by kernels
+    host: HostBatch
+    plans: Dict[Any, Dict[str, Any]] = field(default_factory=dict)   # per plan key: device arrays + host scalars
+
+
+class Part:
+    """Base of all parts."""
+    category = ""
+    kind = ""
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        self.spec = spec
+        self.runtime = runtime
+
+    # -- weights
+    def tensor_needs(self) -> Dict[str, TensorNeed]:
+        """Checkpoint tensor name → shape and role, for every tensor this part reads."""
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Takes its tensors (already on the device, in the element types the loader kept)."""
+
+    # -- per-step planning (host side, before any kernel of the step)
+    def plan_key(self):
+        """A hashable key if the part needs per-step index arrays; parts with equal keys share one plan."""
+        return None
+
+    def build_plan(self, batch: HostBatch) -> Dict[str, Any]:
+        """int32 numpy arrays (uploaded with the step's metadata) and host scalars for this step."""
+        return {}
+
+
+class Mixer(Part):
+    """Token mixer: reads the normed activations ``h`` [T, hidden] of the step and adds its output
+    into the float32 residual stream ``residual`` [T, hidden] in place."""
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext, call: CallInfo) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """Per-token feed-forward: reads ``h`` [T, hidden], adds its output into ``residual`` in place."""
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    """Normalisation of the float32 residual stream into the activation type."""
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """What a mixer needs to encode positions; the mixer's kernels consume it."""
+
+
+class Block(Part):
+    """Arrangement of norms, mixer and feed-forward around the residual stream."""
+
+    def __init__(self, spec, runtime, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm, feed_forward: FeedForward):
+        super().__init__(spec, runtime)
+        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
+
+    def forward(self, residual: torch.Tensor, ctx: StepContext, call: CallInfo) -> None:
+        raise NotImplementedError

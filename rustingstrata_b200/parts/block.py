@@ -1,0 +1,26 @@
+"""Arrangement of a layer's parts around the residual stream.
+
+Reference ``block`` (src/model.rs:587-599): x += mixer(norm(x)); x += ffn(norm(x)).
+The residual stream is float32 in both engines; the norm writes the activation type.
+"""
+from __future__ import annotations
+
+from .base import Block
+from .registry import register_part
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Block):
+    """params: hidden."""
+
+    def __init__(self, spec, runtime, mixer_norm, mixer, ff_norm, feed_forward):
+        super().__init__(spec, runtime, mixer_norm, mixer, ff_norm, feed_forward)
+        self.hidden = int(spec.params["hidden"])
+        runtime.scratch("normed", runtime.max_batch_tokens, self.hidden)
+
+    def forward(self, residual, ctx, call):
+        h = self.runtime.get_scratch("normed")[:, : self.hidden]
+        self.mixer_norm.forward(residual, h, ctx.n_tokens)
+        self.mixer.forward(h, residual, ctx, call)
+        self.ff_norm.forward(residual, h, ctx.n_tokens)
+        self.feed_forward.forward(h, residual, ctx)
