@@ -11,3 +11,14 @@ from .config import EngineConfig, ConfigError, Qwen3Config  # noqa: F401
 from . import models  # noqa: F401  (registers the architecture)
 
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # the engine classes import torch and the kernel launchers; load them on first use
+    if name in ("Engine", "ModelRunner", "StepEntry", "Scheduler", "Request"):
+        from . import engine as _e
+        return getattr(_e, name)
+    if name in ("SamplingParams", "Sampler"):
+        from . import sampling as _s
+        return getattr(_s, name)
+    raise AttributeError(name)

@@ -146,7 +146,7 @@ class CacheManager:
     def pages_to_reserve(self, rid: Hashable, n_new: int) -> List[int]:
         """Per group, the pages :meth:`reserve` would take for ``n_new`` more tokens."""
         r = self._requests[rid]
-        end = r.length + n_new
+        end = max(r.reserved, r.length + n_new)
         need = []
         for g, table in enumerate(r.tables):
             last = (end - 1) // self.page_size if end > 0 else -1

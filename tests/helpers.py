@@ -1,0 +1,84 @@
+"""Shared helpers of the test suite: the tiny configurations, model folders, trace replay, error measure."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Two tiny configurations of the architecture that differ in every size and option, and a third with
+# sizes that are no power of two anywhere (head size 48, 5 query heads on 1 kv head, odd widths).
+TINY = {
+    "A": dict(
+        config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 256, "hidden_size": 64,
+                "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+                "intermediate_size": 160, "rms_norm_eps": 1e-6, "rope_theta": 10000.0,
+                "max_position_embeddings": 384, "tie_word_embeddings": True, "use_sliding_window": False,
+                "torch_dtype": "bfloat16"},
+        seed=0, std=0.08, norm_std=0.0, page_size=4),
+    "B": dict(
+        config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 515, "hidden_size": 96,
+                "num_hidden_layers": 3, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32,
+                "intermediate_size": 250, "rms_norm_eps": 1e-5, "rope_theta": 1000000.0,
+                "max_position_embeddings": 512, "tie_word_embeddings": False, "use_sliding_window": True,
+                "sliding_window": 24, "layer_types": ["full_attention", "sliding_attention", "full_attention"],
+                "torch_dtype": "bfloat16"},
+        seed=1, std=0.08, norm_std=0.1, page_size=16),
+    "C": dict(
+        config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 301, "hidden_size": 80,
+                "num_hidden_layers": 2, "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 48,
+                "intermediate_size": 136, "rms_norm_eps": 3e-6, "rope_theta": 50000.0,
+                "max_position_embeddings": 320, "tie_word_embeddings": False, "use_sliding_window": True,
+                "sliding_window": 40, "max_window_layers": 1, "torch_dtype": "bfloat16"},
+        seed=2, std=0.1, norm_std=0.05, page_size=8),
+}
+
+# Tolerances, as max |difference| / max |reference logit| over the compared rows.  The 32-bit engine
+# differs from the float64 plain implementation by float32 rounding only; the bfloat16 engine rounds
+# activations, cache and projections to 8 bits of mantissa (2^-8 = 3.9e-3 per rounding).
+TOL = {"float32": 1e-5, "bfloat16": 3e-2}
+
+
+def make_model_dir(path: str, name: str) -> str:
+    from rustingstrata_b200.models import manifest_for
+    from rustingstrata_b200.weights import write_random_model
+    t = TINY[name]
+    write_random_model(path, t["config"], manifest_for(t["config"]), t["seed"], std=t["std"], norm_std=t["norm_std"])
+    return path
+
+
+def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
+    return float(np.max(np.abs(np.asarray(got, dtype=np.float64) - ref)) / np.max(np.abs(ref)))
+
+
+def random_tokens(vocab: int, n: int, seed: int):
+    return np.random.default_rng(seed).integers(0, vocab, size=n).tolist()
+
+
+def run_trace(model_dir: str, dtype: str, steps, max_tokens: int, page_size: int = 16, timeout: int = 600):
+    """Runs bin/trace_run on ``steps`` (list of dicts) and returns {step: float32 array [wanted, vocab]}."""
+    out = tempfile.mkdtemp(prefix="trace_out_")
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype, "--out", out,
+           "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+    r = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
+    if r.returncode != 0:
+        raise RuntimeError(f"trace_run failed ({r.returncode}):\n{r.stderr[-4000:]}")
+    done = [ln for ln in r.stdout.splitlines() if ln.startswith("done ")]
+    assert [ln.split()[1] for ln in done] == [str(s["step"]) for s in steps], "trace_run did not acknowledge every step"
+    with open(os.path.join(model_dir, "config.json")) as f:
+        vocab = json.load(f)["vocab_size"]
+    res = {}
+    for s in steps:
+        p = os.path.join(out, f"{s['step']}.f32")
+        wanted = sum(len(e.get("want", [])) for e in s["entries"])
+        if wanted:
+            res[s["step"]] = np.fromfile(p, dtype="<f4").reshape(wanted, vocab)
+        else:
+            assert not os.path.exists(p), f"step {s['step']} wanted nothing but wrote a file"
+    return res

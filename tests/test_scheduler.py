@@ -1,0 +1,171 @@
+"""The scheduler's decisions, driven without a model: the 'model' here picks token ids by a rule (no GPU)."""
+import pytest
+
+from rustingstrata_b200.cache import CacheManager, GroupNeed
+from rustingstrata_b200.engine.scheduler import Request, RequestRejected, Scheduler
+
+
+def make(num_pages=16, page_size=4, budget=16, max_seqs=4, chunk=None, windows=(None,), max_positions=1000):
+    cache = CacheManager([GroupNeed(w) for w in windows], page_size, num_pages, max_seqs)
+    return cache, Scheduler(cache, budget, max_seqs, max_positions, chunk)
+
+
+def run_step(cache, sched, pick=lambda req: 1000 + len(req.generated)):
+    """What the engine does around a step, with the model replaced by ``pick``."""
+    batch = sched.schedule()
+    for s in batch:
+        cache.reserve(s.request.rid, len(s.tokens))
+    for s in batch:
+        cache.commit(s.request.rid, len(s.tokens))
+    cache.check()
+    done = sched.advance(batch, {s.request.rid: pick(s.request) for s in batch if s.samples})
+    cache.check()
+    return batch, done
+
+
+def test_prompt_is_cut_into_portions_under_the_token_budget():
+    cache, sched = make(num_pages=32, budget=8)
+    sched.add(Request("a", list(range(19)), 3))
+    sizes, samples = [], []
+    for _ in range(3):
+        batch, _ = run_step(cache, sched)
+        sizes.append([len(s.tokens) for s in batch])
+        samples.append([s.samples for s in batch])
+    assert sizes == [[8], [8], [3]] and samples == [[False], [False], [True]]
+    batch, _ = run_step(cache, sched)
+    assert [(s.tokens, s.samples) for s in batch] == [([1000], True)]      # decoding the first generated token
+
+
+def test_decodes_go_first_and_portions_fill_the_rest():
+    cache, sched = make(num_pages=64, budget=8)
+    sched.add(Request("a", [1, 2, 3], 10))
+    run_step(cache, sched)                                   # a: whole prompt, first token chosen
+    sched.add(Request("b", list(range(20)), 2))
+    batch, _ = run_step(cache, sched)
+    assert [(s.request.rid, len(s.tokens)) for s in batch] == [("a", 1), ("b", 7)]
+    batch, _ = run_step(cache, sched)
+    assert [(s.request.rid, len(s.tokens)) for s in batch] == [("a", 1), ("b", 7)]
+    batch, _ = run_step(cache, sched)
+    assert [(s.request.rid, len(s.tokens), s.samples) for s in batch] == [("a", 1, True), ("b", 6, True)]
+
+
+def test_prefill_chunk_caps_a_portion():
+    cache, sched = make(num_pages=64, budget=16, chunk=5)
+    sched.add(Request("a", list(range(12)), 1))
+    assert [len(s.tokens) for s in run_step(cache, sched)[0]] == [5]
+
+
+def test_requests_are_admitted_in_arrival_order_and_by_free_slots():
+    cache, sched = make(num_pages=64, budget=64, max_seqs=2)
+    for rid in "abc":
+        sched.add(Request(rid, [1, 2, 3, 4], 2))
+    batch, _ = run_step(cache, sched)
+    assert [s.request.rid for s in batch] == ["a", "b"]       # two slots
+    _, done = run_step(cache, sched)                          # a and b reach their two tokens
+    assert sorted(r.rid for r in done) == ["a", "b"] and all(r.finish_reason == "length" for r in done)
+    batch, _ = run_step(cache, sched)
+    assert [s.request.rid for s in batch] == ["c"]
+
+
+def test_staggered_arrivals_wait_for_their_step():
+    cache, sched = make(num_pages=64, budget=64)
+    sched.add(Request("a", [1, 2], 8, arrival=0))
+    sched.add(Request("b", [3, 4], 8, arrival=2))
+    seen = []
+    for _ in range(4):
+        batch, _ = run_step(cache, sched)
+        seen.append([s.request.rid for s in batch])
+    assert seen == [["a"], ["a"], ["a", "b"], ["a", "b"]]
+
+
+def test_admission_needs_room_for_the_whole_prompt_and_a_decode_page():
+    cache, sched = make(num_pages=6, page_size=4, budget=64)
+    sched.add(Request("a", list(range(12)), 4))               # 3 pages + 1
+    sched.add(Request("b", list(range(9)), 2))                # 3 pages + 1 > what is left
+    batch, _ = run_step(cache, sched)
+    assert [s.request.rid for s in batch] == ["a"]
+    assert [r.rid for r in sched.waiting] == ["b"]
+    for _ in range(3):
+        run_step(cache, sched)
+    assert not cache.is_live("a")                             # a finished and gave its pages back
+    batch, _ = run_step(cache, sched)
+    assert [s.request.rid for s in batch] == ["b"]
+
+
+def test_eos_finishes_and_frees():
+    cache, sched = make()
+    sched.add(Request("a", [1, 2, 3], 50, eos_ids=(7,)))
+    run_step(cache, sched, pick=lambda r: 5)
+    _, done = run_step(cache, sched, pick=lambda r: 7)
+    assert done[0].finish_reason == "eos" and done[0].generated == [5] and cache.n_free(0) == 16
+
+
+def test_context_limit_finishes():
+    cache, sched = make(max_positions=6)
+    sched.add(Request("a", [1, 2, 3], 3))
+    for _ in range(3):
+        _, done = run_step(cache, sched)
+    assert done and done[0].finish_reason in ("length", "context") and len(done[0].generated) == 3
+
+
+def test_requests_that_can_never_fit_are_rejected():
+    cache, sched = make(num_pages=4, page_size=4, max_positions=100)
+    with pytest.raises(RequestRejected, match="context full"):
+        sched.add(Request("a", list(range(10)), 10))          # 20 tokens > 16 the cache holds
+    with pytest.raises(RequestRejected, match="positions"):
+        sched.add(Request("b", list(range(60)), 50))
+    with pytest.raises(RequestRejected, match="empty"):
+        sched.add(Request("c", [], 5))
+    with pytest.raises(RequestRejected, match="max_new_tokens"):
+        sched.add(Request("d", [1], 0))
+
+
+def test_when_pages_run_out_the_newest_request_is_preempted_and_recomputed():
+    cache, sched = make(num_pages=6, page_size=4, budget=64)
+    sched.add(Request("a", list(range(7)), 12))               # 2 pages + decode page = 3 to be admitted
+    sched.add(Request("b", list(range(6)), 12))               # the same
+    batch, _ = run_step(cache, sched)
+    assert [s.request.rid for s in batch] == ["a", "b"]
+    preempted_at = None
+    for step in range(40):
+        batch, done = run_step(cache, sched)
+        if sched.preemptions and preempted_at is None:
+            preempted_at = step
+            b = next(r for r in sched.waiting if r.rid == "b")
+            assert b.computed == 0 and b.preemptions == 1 and len(b.generated) > 0
+            assert not cache.is_live("b")                     # its pages went back
+        if not sched.has_work():
+            break
+    assert preempted_at is not None and not sched.has_work()
+    assert cache.n_free(0) == 6
+    cache.check()
+
+
+def test_preempted_request_resumes_with_its_generated_tokens_as_prompt():
+    cache, sched = make(num_pages=6, page_size=4, budget=64)
+    a, b = Request("a", list(range(7)), 12), Request("b", list(range(6)), 12)
+    sched.add(a)
+    sched.add(b)
+    fed = {"a": [], "b": []}
+    while sched.has_work():
+        batch = sched.schedule()
+        for s in batch:
+            cache.reserve(s.request.rid, len(s.tokens))
+            cache.commit(s.request.rid, len(s.tokens))
+            fed[s.request.rid].append(list(s.tokens))
+        sched.advance(batch, {s.request.rid: 1000 + len(s.request.generated) for s in batch if s.samples})
+    assert b.preemptions >= 1 and len(a.generated) == 12 and len(b.generated) == 12
+    # after the preemption, b was fed prompt + everything it had generated, as one recomputed prompt
+    recompute = [t for t in fed["b"] if len(t) > 1][-1]
+    assert recompute[:6] == list(range(6)) and recompute[6:] == b.generated[: len(recompute) - 6]
+
+
+def test_a_lone_request_is_never_preempted_and_never_deadlocks():
+    cache, sched = make(num_pages=4, page_size=4, budget=64)
+    sched.add(Request("a", list(range(5)), 11))               # exactly the 16 tokens the cache holds
+    steps = 0
+    while sched.has_work():
+        run_step(cache, sched)
+        steps += 1
+        assert steps < 40
+    assert sched.preemptions == 0 and cache.n_free(0) == 4
