@@ -1,0 +1,357 @@
+"""Each CUDA kernel alone against a plain reference of the same operation, at sizes other than the
+engine's tiny configurations: widths and vocabularies that are no power of two, head sizes in steps
+of 16, any number of heads and groups, several page sizes."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from rustingstrata_b200.kernels import ops as o
+    return o
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def tol(dtype, f32=2e-6, bf16=1e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def close(got, want, rel):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = (got - want).abs().max().item() / max(want.abs().max().item(), 1e-30)
+    assert err <= rel, f"relative error {err:.3e} > {rel:.1e}"
+
+
+# ------------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    V, H, T = 1003, 72, 37
+    table = torch.randn(V, H, device=DEV).to(dtype)
+    ids = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
+    ids[0], ids[1] = 0, V - 1
+    out = torch.empty(T, H, device=DEV)
+    st = status()
+    ops().embed(table, ids, out, st)
+    assert torch.equal(out, table[ids.long()].float()) and st.item() == 0
+    ids[3] = V
+    ops().embed(table, ids, out, st)
+    assert st.item() & ops().STATUS_BAD_TOKEN          # flagged, not a fault
+
+
+# ------------------------------------------------------------------------------- RMSNorm
+@pytest.mark.parametrize("n", [48, 100, 1000, 4096, 5120])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("w_dtype", DTYPES)
+def test_rmsnorm(n, out_dtype, w_dtype):
+    rows, eps = 13, 1e-5
+    x = torch.randn(rows, n, device=DEV) * 3
+    w = (1 + 0.1 * torch.randn(n, device=DEV)).to(w_dtype)
+    out = torch.empty(rows, n, device=DEV, dtype=out_dtype)
+    ops().rmsnorm(x, w, eps, out)
+    xd = x.double()
+    want = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + eps) * w.double()
+    close(out, want, tol(out_dtype, 1e-6, 5e-3))
+
+
+def test_rmsnorm_gathers_rows_and_respects_strides():
+    n = 200
+    big = torch.randn(9, 256, device=DEV)
+    x = big[:, :n]                                        # row stride 256
+    w = torch.ones(n, device=DEV)
+    rows = torch.tensor([7, 2, 2, 0], dtype=torch.int32, device=DEV)
+    out = torch.full((6, n), 7.0, device=DEV)
+    ops().rmsnorm(x, w, 1e-6, out, rows=rows, n_rows=4)
+    xd = x.double()[rows.long()]
+    close(out[:4], xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + 1e-6), 1e-6)
+    assert torch.all(out[4:] == 7.0)                      # rows beyond n_rows untouched
+
+
+# ------------------------------------------------------------------------------- matrix product
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 130, 77), (67, 250, 96), (130, 515, 200), (3, 1003, 4096)])
+@pytest.mark.parametrize("a_dt,w_dt,o_dt", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                            (torch.bfloat16, torch.bfloat16, torch.float32),
+                                            (torch.bfloat16, torch.float32, torch.bfloat16)])
+def test_linear_simt(M, N, K, a_dt, w_dt, o_dt):
+    a = torch.randn(M + 2, K, device=DEV).to(a_dt)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(w_dt)
+    out = torch.full((M + 2, N), 5.0, device=DEV, dtype=o_dt)
+    ops().linear_simt(a, w, out, M)
+    want = a[:M].double() @ w.double().T
+    # float32 running sum over K terms: rounding grows like sqrt(K) * 2^-24 of the terms' size
+    f32_tol = 4 * math.sqrt(K) * 2.0 ** -24
+    close(out[:M], want, tol(o_dt, f32_tol, 6e-3))
+    assert torch.all(out[M:] == 5.0)
+    if o_dt == torch.float32:
+        base = torch.randn(M + 2, N, device=DEV)
+        acc = base.clone()
+        ops().linear_simt(a, w, acc, M, accumulate=True)
+        close(acc[:M], base[:M].double() + want, f32_tol)
+
+
+def test_linear_row_result_does_not_depend_on_the_batch():
+    """Row 3 of a 50-row product equals the same row computed alone, bit for bit."""
+    K, N = 300, 130
+    a = torch.randn(50, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    full = torch.empty(50, N, device=DEV)
+    one = torch.empty(1, N, device=DEV)
+    ops().linear_simt(a, w, full, 50)
+    ops().linear_simt(a[3:4].contiguous(), w, one, 1)
+    assert torch.equal(full[3], one[0])
+
+
+# ------------------------------------------------------------------------------- SiLU * up
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    rows, I = 11, 250
+    gu = (torch.randn(rows, 2 * I, device=DEV) * 4).to(dtype)
+    out = torch.empty(rows, I, device=DEV, dtype=dtype)
+    ops().silu_mul(gu, out, rows)
+    g, u = gu[:, :I].double(), gu[:, I:].double()
+    close(out, g / (1 + torch.exp(-g)) * u, tol(dtype, 1e-6, 5e-3))
+
+
+# ------------------------------------------------------------------------------- QK-norm + RoPE + cache write
+def rope_table(n_pos, n_rot, base):
+    i = np.arange(n_rot // 2, dtype=np.float64)
+    th = np.arange(n_pos, dtype=np.float64)[:, None] * np.power(np.float64(np.float32(base)), -2.0 * i / n_rot)[None]
+    return torch.from_numpy(np.concatenate([np.cos(th), np.sin(th)], 1).astype(np.float32)).to(DEV)
+
+
+def ref_norm_rope(x, w, eps, pos, n_rot, base):
+    """x [T, heads, hd] float64; per-head RMSNorm then NEOX rotation (src/ops.rs:3-7,36-45)."""
+    if w is not None:
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+    half = n_rot // 2
+    tab = rope_table(int(pos.max()) + 1, n_rot, base).double().cpu()[pos.long().cpu()]
+    c, s = tab[:, None, :half], tab[:, None, half:]
+    a, b = x[..., :half], x[..., half:n_rot]
+    return torch.cat([a * c - b * s, a * s + b * c, x[..., n_rot:]], -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd,n_rot,page", [(4, 2, 16, 16, 4), (5, 1, 48, 48, 8), (6, 3, 80, 64, 5),
+                                                  (8, 8, 128, 128, 16), (2, 1, 256, 256, 16)])
+def test_qk_norm_rope_kv_write(dtype, n_q, n_kv, hd, n_rot, page):
+    o = ops()
+    eps, base = 1e-5, 12345.0
+    q_lens, starts = [5, 1, 9], [3, 40, 0]                # three sequences at different positions
+    T = sum(q_lens)
+    n_pages = 40
+    positions = torch.tensor([s + i for n, s in zip(q_lens, starts) for i in range(n)], dtype=torch.int32, device=DEV)
+    seq_of = torch.tensor([k for k, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    width = max((s + n + page - 1) // page for n, s in zip(q_lens, starts))
+    perm = torch.randperm(n_pages)[: 3 * width].reshape(3, width).to(torch.int32)
+    table = perm.to(DEV)
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV).to(dtype)
+    src = qkv.clone()
+    qw = (1 + 0.2 * torch.randn(hd, device=DEV)).to(dtype)
+    kw = (1 + 0.2 * torch.randn(hd, device=DEV)).to(dtype)
+    cache = torch.zeros(n_pages, 2, n_kv, page, hd, device=DEV, dtype=dtype)
+    st = status()
+    o.qk_norm_rope_kv(qkv, T, n_q, n_kv, hd, qw, kw, eps, rope_table(64, n_rot, base), n_rot, positions, seq_of,
+                      table, page, cache, True, st)
+    assert st.item() == 0
+    s64 = src.double().cpu()
+    q_ref = ref_norm_rope(s64[:, : n_q * hd].reshape(T, n_q, hd), qw.cpu(), eps, positions, n_rot, base)
+    k_ref = ref_norm_rope(s64[:, n_q * hd:(n_q + n_kv) * hd].reshape(T, n_kv, hd), kw.cpu(), eps, positions, n_rot, base)
+    v_ref = s64[:, (n_q + n_kv) * hd:].reshape(T, n_kv, hd)
+    close(qkv[:, : n_q * hd].reshape(T, n_q, hd), q_ref, tol(dtype, 2e-6, 8e-3))
+    written = torch.zeros(n_pages, page, dtype=torch.bool)
+    for t in range(T):
+        pos, sq = int(positions[t]), int(seq_of[t])
+        pg = int(perm[sq, pos // page])
+        written[pg, pos % page] = True
+        close(cache[pg, 0, :, pos % page], k_ref[t], tol(dtype, 2e-6, 8e-3))
+        assert torch.equal(cache[pg, 1, :, pos % page].cpu(), src[t, (n_q + n_kv) * hd:].reshape(n_kv, hd).cpu())
+    untouched = cache.cpu().permute(0, 3, 1, 2, 4)[~written]
+    assert torch.all(untouched == 0)                       # nothing outside the tokens' own slots
+
+
+def test_qk_without_norm_without_rope_and_without_kv():
+    o = ops()
+    T, n_q, n_kv, hd, page = 4, 2, 1, 32, 4
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV)
+    src = qkv.clone()
+    cache = torch.zeros(4, 2, n_kv, page, hd, device=DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[2]], dtype=torch.int32, device=DEV)
+    o.qk_norm_rope_kv(qkv, T, n_q, n_kv, hd, None, None, 0.0, None, 0, pos, seq, table, page, cache, False, status())
+    assert torch.equal(qkv, src) and torch.all(cache == 0)          # a reader of another call's cache writes nothing
+    o.qk_norm_rope_kv(qkv, T, n_q, n_kv, hd, None, None, 0.0, None, 0, pos, seq, table, page, cache, True, status())
+    assert torch.equal(cache[2, 0, 0], src[:, n_q * hd:(n_q + 1) * hd]) and torch.equal(cache[2, 1, 0], src[:, -hd:])
+    bad = torch.tensor([[9]], dtype=torch.int32, device=DEV)
+    st = status()
+    o.qk_norm_rope_kv(qkv, T, n_q, n_kv, hd, None, None, 0.0, None, 0, pos, seq, bad, page, cache, True, st)
+    assert st.item() & o.STATUS_BAD_PAGE                            # flagged, not a fault
+
+
+# ------------------------------------------------------------------------------- attention
+def ref_attention(q, keys, vals, q_pos, n_kv, window, scale):
+    """q [nq, hd] at position q_pos over keys/vals [L, nkv, hd] (float64): src/model.rs:778-791."""
+    nq = q.shape[0]
+    lo = max(0, q_pos - window + 1) if window else 0
+    out = torch.zeros_like(q)
+    for h in range(nq):
+        g = h // (nq // n_kv)
+        s = (keys[lo:q_pos + 1, g] @ q[h]) * scale
+        p = torch.softmax(s, 0)
+        out[h] = p @ vals[lo:q_pos + 1, g]
+    return out
+
+
+def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=None):
+    """seqs: list of (kv_len, q_len).  Builds a shuffled paged cache, runs the kernels the mixer would
+    run (split form for one query, tile form otherwise) and returns (got, want) [T, n_q, hd]."""
+    o = ops()
+    scale = scale or 1.0 / math.sqrt(hd)
+    S = len(seqs)
+    T = sum(q for _, q in seqs)
+    width = max((kv + page - 1) // page for kv, _ in seqs)
+    n_pages = S * width + 3
+    perm = torch.randperm(n_pages)[: S * width].reshape(S, width).to(torch.int32)
+    cache = torch.zeros(n_pages, 2, n_kv, page, hd, device=DEV, dtype=dtype)
+    keys, vals = [], []
+    for s, (kv, _) in enumerate(seqs):
+        k = torch.randn(kv, n_kv, hd).to(dtype)
+        v = torch.randn(kv, n_kv, hd).to(dtype)
+        if boost is not None:
+            boost(s, k)
+        keys.append(k.double())
+        vals.append(v.double())
+        for p in range(kv):
+            cache[perm[s, p // page], 0, :, p % page] = k[p].to(DEV)
+            cache[perm[s, p // page], 1, :, p % page] = v[p].to(DEV)
+    q = torch.randn(T, n_q * hd).to(dtype)
+    if boost is not None:
+        boost(None, q.view(T, n_q, hd))
+    qd = q.to(DEV)
+    out = torch.zeros(T, n_q * hd, device=DEV, dtype=dtype)
+    q_lens = np.array([ql for _, ql in seqs], np.int32)
+    kv_lens = np.array([kv for kv, _ in seqs], np.int32)
+    q_start = np.zeros(S + 1, np.int32)
+    q_start[1:] = np.cumsum(q_lens)
+    from rustingstrata_b200.parts.attention import SPLIT_KEYS, decode_splits
+    qpc = o.attention_q_per_cta(n_q, n_kv)
+    dec = np.nonzero(q_lens == 1)[0].astype(np.int32)
+    tiles = [(s, off) for s in np.nonzero(q_lens != 1)[0] for off in range(0, q_lens[s], qpc)]
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)  # noqa: E731
+    st = status()
+    common = dict(q=qd, out=out, cache=cache, block_table=perm.to(DEV), q_start=dev(q_start), kv_len=dev(kv_lens),
+                  n_q=n_q, n_kv=n_kv, head_dim=hd, page_size=page, window=window, scale=scale, status=st)
+    if tiles:
+        o.attention_simt(work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), decode=False, **common)
+    if len(dec):
+        splits = decode_splits(kv_lens[dec], window)
+        ss = np.zeros(len(dec) + 1, np.int32)
+        ss[1:] = np.cumsum(splits)
+        partial = torch.empty(o.attention_partial_floats(int(ss[-1]), n_q, hd), device=DEV)
+        o.attention_simt(work=dev(dec), n_work=len(dec), decode=True, split_keys=SPLIT_KEYS, max_splits=int(splits.max()),
+                         split_start=dev(ss), total_splits=int(ss[-1]), partial=partial, **common)
+    assert st.item() == 0
+    want = torch.zeros(T, n_q, hd, dtype=torch.float64)
+    for s, (kv, ql) in enumerate(seqs):
+        for i in range(ql):
+            t = q_start[s] + i
+            want[t] = ref_attention(q[t].double().view(n_q, hd), keys[s], vals[s], kv - ql + i, n_kv, window, scale)
+    return out.view(T, n_q, hd), want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd,page", [(4, 2, 16, 4), (5, 1, 48, 8), (6, 2, 80, 5), (8, 2, 128, 16),
+                                              (32, 8, 128, 16), (3, 3, 256, 16), (40, 2, 64, 16)])
+def test_attention_portions_and_single_queries(dtype, n_q, n_kv, hd, page):
+    seqs = [(37, 37), (300, 1), (65, 20), (1, 1), (129, 1), (200, 33), (128, 2)]
+    got, want = run_attention(dtype, n_q, n_kv, hd, page, seqs)
+    close(got, want, tol(dtype, 3e-6, 1.5e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 32, 100, 129])
+def test_attention_window_edge(dtype, window):
+    seqs = [(150, 150), (300, 1), (140, 31), (window, 1), (window + 1, 1), (257, 1)]
+    got, want = run_attention(dtype, 4, 2, 32, 8, seqs, window=window)
+    close(got, want, tol(dtype, 3e-6, 1.5e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 127, 128, 255, 511, 600])
+def test_attention_finds_a_far_key_among_hundreds(dtype, far):
+    """One key far back is made to dominate: the output must be (nearly) that key's value, so a kernel that
+    skips a page, a split or a tile edge is caught even though random scores would hide it."""
+    hd = 64
+
+    def boost(s, t):
+        if s is None:
+            t[:, :, 0] = 6.0                  # every query points along dim 0
+        else:
+            t[:, :, 0] = 0.0
+            t[far, :, 0] = 40.0               # only key `far` answers
+    seqs = [(700, 1), (700, 64), (far + 1, 1)]
+    got, want = run_attention(dtype, 4, 2, hd, 16, seqs, boost=boost)
+    close(got, want, tol(dtype, 3e-6, 1.5e-2))
+    assert (got[0].double().cpu() - want[0]).abs().max() < 0.05
+
+
+def test_attention_refuses_unsupported_sizes():
+    from rustingstrata_b200.kernels.ops import KernelError
+    with pytest.raises(KernelError, match="head size"):
+        run_attention(torch.float32, 2, 1, 24, 4, [(5, 5)])
+    with pytest.raises(KernelError, match="multiple"):
+        run_attention(torch.float32, 3, 2, 32, 4, [(5, 5)])
+
+
+# ------------------------------------------------------------------------------- sampling
+def test_argmax_first_index_on_ties_and_non_finite():
+    o = ops()
+    V = 151_937
+    logits = torch.randn(5, V, device=DEV)
+    logits[0, 77] = logits[0, 90_001] = 50.0
+    logits[1, V - 1] = 60.0
+    logits[2, 0] = 60.0
+    logits[3, 5] = float("nan")
+    logits[3, 1000] = 70.0
+    logits[4, :] = float("nan")
+    out = torch.zeros(5, dtype=torch.int32, device=DEV)
+    st = status()
+    o.sample(logits, 5, out, st)
+    assert out.tolist() == [77, V - 1, 0, 1000, -1]
+    assert st.item() & o.STATUS_NON_FINITE
+
+
+def test_temperature_draw_distribution_and_edges():
+    o = ops()
+    p = torch.tensor([0.5, 0.3, 0.15, 0.05])
+    V, R = 1003, 20000
+    logits = torch.full((R, V), -1e9, device=DEV)
+    ids = [3, 400, 401, 1002]
+    for i, pr in zip(ids, p):
+        logits[:, i] = math.log(pr)
+    temps = torch.ones(R, device=DEV)
+    u = torch.rand(R, device=DEV)
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    o.sample(logits, R, out, status(), temps, u)
+    counts = torch.bincount(out.long().cpu(), minlength=V)[ids].double() / R
+    assert torch.all((counts - p.double()).abs() < 0.012), counts
+    # inverse CDF in id order: u just below/above the first boundary
+    u2 = torch.tensor([0.0, 0.4999, 0.5001, 0.7999, 0.8001, 0.9499, 0.9501, 0.999999], device=DEV)
+    out2 = torch.zeros(8, dtype=torch.int32, device=DEV)
+    o.sample(logits[:8].contiguous(), 8, out2, status(), temps[:8].contiguous(), u2)
+    assert out2.tolist() == [3, 3, 400, 400, 401, 401, 1002, 1002]
+    # temperature sharpens; rows with temp 0 are greedy
+    temps3 = torch.tensor([0.0, 0.25], device=DEV)
+    u3 = torch.tensor([0.9, 0.9], device=DEV)
+    out3 = torch.zeros(2, dtype=torch.int32, device=DEV)
+    o.sample(logits[:2].contiguous(), 2, out3, status(), temps3, u3)
+    assert out3.tolist() == [3, 400]          # p^4 normalised: 0.5^4 / sum = 0.877 < 0.9 → second token
