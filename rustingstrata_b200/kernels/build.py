@@ -74,7 +74,7 @@ def _digest(paths: List[str], extra: str) -> str:
     h = hashlib.sha256(extra.encode())
     for p in paths:
         with open(p, "rb") as f:
-            h.update(p.encode())
+            h.update(os.path.basename(p).encode())     # not the folder: a built library travels with the tree
             h.update(f.read())
     return h.hexdigest()[:16]
 

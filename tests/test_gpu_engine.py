@@ -1,0 +1,147 @@
+"""Generation through the Python entry point and the scheduler, long decoding, the first tokens of a
+sequence, and what happens when pages run out - compared with the plain implementation."""
+import numpy as np
+import pytest
+
+import plain_qwen3 as P
+from helpers import TINY, TOL, random_tokens, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def engine(tiny_models, name, dtype, **kw):
+    from rustingstrata_b200 import Engine
+    kw.setdefault("page_size", TINY[name]["page_size"])
+    kw.setdefault("max_tokens", 1024)
+    kw.setdefault("max_batch_tokens", 256)
+    kw.setdefault("max_seqs", 8)
+    return Engine(tiny_models[name], dtype=dtype, **kw)
+
+
+def teacher_forced_ok(cfg, w, prompt, generated, dtype):
+    """Every generated token is the plain implementation's argmax given the tokens before it, or a
+    near-tie within the engine's tolerance (bfloat16 may flip such a tie; the 32-bit engine must not)."""
+    logits = P.forward_logits(cfg, w, list(prompt) + list(generated))
+    for i, t in enumerate(generated):
+        row = logits[len(prompt) - 1 + i]
+        best = int(np.argmax(row))
+        if t != best:
+            margin = (row[best] - row[t]) / np.max(np.abs(logits))
+            assert dtype == "bfloat16" and margin < 2 * TOL[dtype], f"token {i}: {t} vs argmax {best}, margin {margin:.2e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_entry_point(tiny_models, name, dtype):
+    cfg, w = P.read_model(tiny_models[name])
+    eng = engine(tiny_models, name, dtype)
+    prompts = [random_tokens(cfg["vocab_size"], n, 50 + n) for n in (1, 7, 16, 33)]
+    outs = eng.generate(prompts, max_new_tokens=8)
+    assert [len(o) for o in outs] == [8] * 4
+    for p, o in zip(prompts, outs):
+        if dtype == "float32":
+            assert o == P.greedy_generate(cfg, w, p, 8)
+        teacher_forced_ok(cfg, w, p, o, dtype)
+    single = eng.generate(prompts[2], max_new_tokens=8)            # one prompt in, one list out
+    assert single == outs[2]
+    eng.runner.cache.check()
+    assert all(eng.runner.cache.n_free(g) == eng.runner.num_pages for g in range(len(eng.runner.cache.groups)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tiny_models, dtype):
+    """A sequence fed one token at a time from its very first token for 300 positions."""
+    from rustingstrata_b200.engine import StepEntry
+    cfg, w = P.read_model(tiny_models["A"])
+    eng = engine(tiny_models, "A", dtype)
+    toks = random_tokens(cfg["vocab_size"], 300, 77)
+    ref = P.forward_logits(cfg, w, toks)
+    worst = 0.0
+    for i, t in enumerate(toks):
+        row = eng.step_raw([StepEntry("x", [t], [0])]).cpu().numpy()[0]
+        err = float(np.max(np.abs(row - ref[i])) / np.max(np.abs(ref)))
+        assert err <= TOL[dtype], f"position {i}: {err:.3e}"
+        worst = max(worst, err)
+    eng.runner.check_status()
+    eng.release("x")
+
+
+@pytest.mark.parametrize("dtype", ["float32"])
+def test_preemption_recomputes_and_gives_the_same_tokens(tiny_models, dtype):
+    """With too few pages for all requests, some are preempted and recomputed; greedy output is unchanged."""
+    cfg, w = P.read_model(tiny_models["A"])
+    prompts = [random_tokens(cfg["vocab_size"], n, 200 + n) for n in (30, 25, 41, 12)]
+    roomy = engine(tiny_models, "A", dtype).generate(prompts, max_new_tokens=40)
+    tight = engine(tiny_models, "A", dtype, num_pages=40, max_tokens=0)       # 160 tokens for 4 x ~70
+    outs = tight.generate(prompts, max_new_tokens=40)
+    assert tight.scheduler.preemptions > 0
+    assert outs == roomy
+    for p, o in zip(prompts, outs):
+        assert o == P.greedy_generate(cfg, w, p, 40)
+    tight.runner.cache.check()
+    assert tight.runner.cache.pools[0].reuses > 0
+
+
+def test_chunked_prefill_with_staggered_arrivals_and_temperature(tiny_models):
+    """Configuration B's workload: prompts of 3-120 tokens arriving over time, a small token budget so
+    prompts are cut into portions beside decoding requests, temperature 0.8 with a fixed sampler seed."""
+    from rustingstrata_b200.sampling import SamplingParams
+    cfg, w = P.read_model(tiny_models["B"])
+    lens = [3, 120, 47, 88, 19, 64]
+
+    def run(budget, chunk):
+        eng = engine(tiny_models, "B", "float32", max_batch_tokens=budget, prefill_chunk=chunk)
+        rids = [eng.add_request(random_tokens(cfg["vocab_size"], n, 300 + n), 12, SamplingParams(temp=0.8, seed=9 + i),
+                                arrival=2 * i) for i, n in enumerate(lens)]
+        done = {}
+        mixed_steps = 0
+        while eng.has_work():
+            batch_sizes = [len(s.tokens) for s in eng.scheduler.schedule()] if False else None
+            for r in eng.step():
+                done[r.rid] = r.generated
+        return [done[r] for r in rids], eng
+    a, eng_a = run(32, 16)
+    b, _ = run(256, None)
+    assert a == b and all(len(x) == 12 for x in a)           # the cut of the work does not change the draws
+    c, _ = run(32, 16)
+    assert c == a                                            # same seeds, same tokens
+    eng_a.runner.cache.check()
+
+
+def test_sampling_with_cuts_goes_through_the_host_sampler(tiny_models):
+    from rustingstrata_b200.sampling import Sampler, SamplingParams
+    cfg, w = P.read_model(tiny_models["A"])
+    eng = engine(tiny_models, "A", "float32")
+    p = random_tokens(cfg["vocab_size"], 10, 1)
+    out = eng.generate(p, max_new_tokens=6, temperature=0.7, top_k=5, top_p=0.9, seed=4)
+    # replay the same choice from the plain implementation's logits with the host sampler
+    smp = Sampler(SamplingParams(temp=0.7, top_k=5, top_p=0.9, seed=4))
+    toks = list(p)
+    for t in out:
+        row = P.forward_logits(cfg, w, toks)[-1].astype(np.float32)
+        ids, _ = smp.candidates(row)
+        assert t in ids.tolist() and len(ids) <= 5
+        smp.note(t)
+        toks.append(t)
+
+
+def test_step_errors_leave_the_cache_untouched(tiny_models):
+    from rustingstrata_b200.cache import OutOfPages
+    from rustingstrata_b200.engine import StepEntry, StepError
+    eng = engine(tiny_models, "A", "float32", num_pages=8, max_tokens=0)      # 32 tokens
+    r = eng.runner
+    r.step([StepEntry("a", list(range(10)), [9])])
+    free = r.cache.n_free(0)
+    with pytest.raises(OutOfPages):
+        r.step([StepEntry("a", [1], [0]), StepEntry("b", list(range(30)), [])])
+    assert r.cache.n_free(0) == free and r.length("a") == 10 and not r.cache.is_live("b")
+    with pytest.raises(StepError, match="vocabulary"):
+        r.step([StepEntry("a", [256], [0])])
+    with pytest.raises(StepError, match="wanted place"):
+        r.step([StepEntry("a", [1, 2], [2])])
+    with pytest.raises(StepError, match="once"):
+        r.step([StepEntry("a", [1], []), StepEntry("a", [2], [])])
+    assert r.length("a") == 10
+    r.cache.check()
+    out = r.step([StepEntry("a", [5], [0])])
+    assert out.shape == (1, 256)

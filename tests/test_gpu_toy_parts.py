@@ -1,0 +1,176 @@
+"""A toy mixer with state of its own, a toy feed-forward and a toy architecture, all defined here:
+they are registered, built, given random weights, stepped through the engine's step function in
+portions and mixed batches, and compared with a plain loop - without a change to the package."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import random_tokens, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def define_toy():
+    from rustingstrata_b200.config import register_architecture
+    from rustingstrata_b200.parts import (FeedForward, LayerCall, LayerSpec, Mixer, ModelSpec, PartSpec, StateNeed,
+                                          TensorNeed, register_part)
+    from rustingstrata_b200.kernels import ops
+
+    @register_part("mixer", "toy_decay_sum", replace=True)
+    class DecaySum(Mixer):
+        """out_t = W s_t with s_t = decay * s_{t-1} + h_t: a recurrent mixer whose only memory is a
+        fixed-size state per request (no cache pages)."""
+
+        def __init__(self, spec, runtime, position=None):
+            super().__init__(spec, runtime)
+            self.hidden, self.decay = int(spec.params["hidden"]), float(spec.params["decay"])
+
+        def tensor_needs(self):
+            return {self.spec.tensors["proj"]: TensorNeed((self.hidden, self.hidden))}
+
+        def load(self, tensors):
+            self.w = tensors[self.spec.tensors["proj"]]
+
+        def state_need(self):
+            return StateNeed(self.hidden)
+
+        def forward(self, h, residual, ctx, call):
+            hb = ctx.host
+            for s in range(hb.n_seqs):                       # a request's tokens in order, state carried
+                a, b = int(hb.q_start[s]), int(hb.q_start[s + 1])
+                slot = int(hb.state_slots[s])
+                st = call.state[slot]
+                outs = []
+                for t in range(a, b):
+                    st.mul_(self.decay).add_(h[t].float())
+                    outs.append(st.clone())
+                o = torch.stack(outs).to(h.dtype)
+                tmp = torch.zeros(b - a, self.hidden, device=h.device, dtype=torch.float32)
+                ops.linear(o.contiguous(), self.w, tmp, b - a)
+                residual[a:b] += tmp
+
+    @register_part("feed_forward", "toy_scale", replace=True)
+    class Scale(FeedForward):
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.factor = float(spec.params["factor"])
+
+        def forward(self, h, residual, ctx):
+            residual[: ctx.n_tokens] += self.factor * h[: ctx.n_tokens].float()
+
+    class ToyConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d, where=""):
+            return cls(dict(d))
+
+    def build(cfg):
+        d = cfg.d
+        H, V = d["hidden_size"], d["vocab_size"]
+        norm = lambda n: PartSpec("rmsnorm", {"width": H, "eps": d["eps"]}, {"weight": n})  # noqa: E731
+        layers = []
+        for i in range(d["layers"]):
+            if i % 2 == 0:
+                mixer = PartSpec("toy_decay_sum", {"hidden": H, "decay": d["decay"]}, {"proj": f"l{i}.proj"})
+                pos = None
+            else:                                            # the package's own attention beside the toy mixer
+                mixer = PartSpec("paged_attention", {"hidden": H, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16,
+                                                     "qk_norm": False, "window": None},
+                                 {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+                pos = PartSpec("rope_neox", {"n_rot": 8, "base": 100.0})       # partial rotation
+            ff = PartSpec("toy_scale", {"factor": 0.5}) if i == 0 else PartSpec(
+                "gated_mlp", {"hidden": H, "intermediate": 40}, {k: f"l{i}.{k}" for k in ("gate_proj", "up_proj", "down_proj")})
+            layers.append(LayerSpec(PartSpec("pre_norm", {"hidden": H}), mixer, norm(f"l{i}.n1"), ff, norm(f"l{i}.n2"), pos))
+        return ModelSpec("toy", V, H, d["max_positions"], PartSpec("token_table", {"vocab": V, "width": H}, {"weight": "emb"}),
+                         tuple(layers), tuple(LayerCall(i) for i in range(d["layers"])), norm("fn"),
+                         PartSpec("linear", {"vocab": V, "width": H}, {"weight": "head"}))
+
+    register_architecture("ToyDecayLM", ToyConfig, build, replace=True)
+
+
+TOY = {"architectures": ["ToyDecayLM"], "vocab_size": 50, "hidden_size": 32, "layers": 3, "decay": 0.8, "eps": 1e-5,
+       "max_positions": 128}
+
+
+def plain_toy(w, toks):
+    """The toy model as a plain loop over the whole sequence (float64)."""
+    import plain_qwen3 as P
+    d = TOY
+    x = w["emb"][np.asarray(toks)]
+    T = len(toks)
+    for i in range(d["layers"]):
+        h = P.rms_norm(x, w[f"l{i}.n1"], d["eps"])
+        if i % 2 == 0:
+            s, outs = np.zeros(d["hidden_size"]), []
+            for t in range(T):
+                s = d["decay"] * s + h[t]
+                outs.append(s.copy())
+            x = x + np.stack(outs) @ w[f"l{i}.proj"].T
+        else:
+            q = (h @ w[f"l{i}.q_proj"].T).reshape(T, 2, 16)
+            k = (h @ w[f"l{i}.k_proj"].T).reshape(T, 1, 16)
+            v = (h @ w[f"l{i}.v_proj"].T).reshape(T, 1, 16)
+            q, k = P.rope_neox(q, np.arange(T), 8, 100.0), P.rope_neox(k, np.arange(T), 8, 100.0)
+            x = x + P.attention_scores(q, k, v, 1).reshape(T, 32) @ w[f"l{i}.o_proj"].T
+        h = P.rms_norm(x, w[f"l{i}.n2"], d["eps"])
+        if i == 0:
+            x = x + 0.5 * h
+        else:
+            x = x + (P.silu(h @ w[f"l{i}.gate_proj"].T) * (h @ w[f"l{i}.up_proj"].T)) @ w[f"l{i}.down_proj"].T
+    return P.rms_norm(x, w["fn"], d["eps"]) @ w["head"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32"])
+def test_toy_architecture_with_stateful_mixer(tmp_path, dtype):
+    import plain_qwen3 as P
+    from rustingstrata_b200.config import EngineConfig, unregister_architecture
+    from rustingstrata_b200.engine import ModelRunner, StepEntry
+    from rustingstrata_b200.models import manifest_for
+    from rustingstrata_b200.parts import unregister_part
+    from rustingstrata_b200.weights import write_random_model
+    define_toy()
+    try:
+        d = str(tmp_path / "toy")
+        m = manifest_for(TOY)
+        assert "l0.proj" in m and "l1.q_proj" in m and "l2.proj" in m and "l0.gate_proj" not in m
+        write_random_model(d, TOY, m, seed=3, std=0.15, norm_std=0.1)
+        w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+        runner = ModelRunner.from_dir(d, EngineConfig(dtype=dtype, page_size=4, num_pages=24, max_seqs=4,
+                                                      max_batch_tokens=128, max_logit_rows=128))
+        assert len(runner.states) == 2 and len(runner.model.cache_groups) == 1     # two stateful calls, one cached
+        toks = {r: random_tokens(50, n, 20 + i) for i, (r, n) in enumerate((("a", 40), ("b", 23), ("c", 31)))}
+        ref = {r: plain_toy(w, t) for r, t in toks.items()}
+        # a whole; b and c in portions, mixed with each other, b finishing first and its slot reused by d
+        got = {r: {} for r in list(toks) + ["d"]}
+
+        def step(entries):
+            logits = runner.step([StepEntry(r, toks[r][s:s + n], list(range(n))) for r, s, n in entries]).cpu().numpy()
+            runner.check_status()
+            k = 0
+            for r, s, n in entries:
+                for i in range(n):
+                    got[r][s + i] = logits[k]
+                    k += 1
+        step([("a", 0, 40)])
+        step([("b", 0, 7), ("c", 0, 2)])
+        step([("b", 7, 1), ("c", 2, 17)])
+        step([("c", 19, 1), ("b", 8, 15)])
+        runner.release("b")
+        toks["d"], ref["d"] = toks["b"], ref["b"]
+        step([("d", 0, 5), ("c", 20, 11)])                 # d takes b's state slot: it must start from zero
+        step([("d", 5, 18)])
+        for r in got:
+            rows = np.stack([got[r][i] for i in range(len(toks[r]))])
+            assert rel_err(rows, ref[r]) < 5e-6, r
+        for r in ("a", "c", "d"):
+            runner.release(r)
+        runner.cache.check()
+    finally:
+        unregister_architecture("ToyDecayLM")
+        unregister_part("mixer", "toy_decay_sum")
+        unregister_part("feed_forward", "toy_scale")
