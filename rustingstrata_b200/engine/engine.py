@@ -52,6 +52,8 @@ class Engine:
         self._unif_d = torch.zeros(n, dtype=torch.float32, device=r.device)
         self._picked_d = torch.zeros(n, dtype=torch.int32, device=r.device)
         self._picked_h = torch.zeros(n + 1, dtype=torch.int32).pin_memory()
+        self.h2d_bytes_last_step = 0
+        self.d2h_bytes_last_step = 0
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int = 32, sampling: Optional[SamplingParams] = None,
@@ -110,6 +112,8 @@ class Engine:
         self._picked_h[:R].copy_(self._picked_d[:R], non_blocking=True)
         self._picked_h[R:R + 1].copy_(self.runner.status, non_blocking=True)
         host_logits = {i: logits[i].to("cpu").numpy() for i in host_rows}      # also waits for the stream
+        self.h2d_bytes_last_step = self.runner.h2d_bytes_last_step + 8 * R
+        self.d2h_bytes_last_step = 4 * (R + 1) + 4 * logits.shape[1] * len(host_rows)
         torch.cuda.current_stream().synchronize()
         picked = self._picked_h.numpy()
         if int(picked[R]) != 0:
@@ -146,6 +150,37 @@ class Engine:
                     results[r.rid] = list(r.generated)
         outs = [results[r] for r in rids]
         return outs[0] if single else outs
+
+    # ------------------------------------------------------------------ device-resident greedy decode
+    def decode_steps_device_timed(self, n_steps: int) -> float:
+        """Runs ``n_steps`` greedy decode steps of all running requests with the chosen ids staying on
+        the device between steps (the host only counts lengths), and returns the milliseconds per step
+        measured with CUDA events.  The generated ids are appended to the requests afterwards."""
+        reqs = list(self.scheduler.running)
+        if not reqs or any(r.prefilling for r in reqs) or self.scheduler.waiting:
+            raise RuntimeError("device decode needs every request past its prompt and none waiting")
+        B = len(reqs)
+        r = self.runner
+        first = torch.tensor([q.all_tokens[-1] for q in reqs], dtype=torch.int32).pin_memory()
+        self._picked_d[:B].copy_(first, non_blocking=True)
+        history = torch.zeros((n_steps, B), dtype=torch.int32, device=r.device)
+        entries = [StepEntry(q.rid, [0], [0]) for q in reqs]
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(n_steps):
+            logits = r.step(entries, device_tokens=self._picked_d)
+            ops.sample(logits, B, self._picked_d, r.status)
+            history[i].copy_(self._picked_d[:B], non_blocking=True)
+        ev1.record()
+        torch.cuda.synchronize()
+        r.check_status()
+        ms = ev0.elapsed_time(ev1) / n_steps
+        hist = history.cpu().numpy()
+        for j, q in enumerate(reqs):
+            q.generated.extend(int(t) for t in hist[:, j])
+            q.computed += n_steps
+        return ms
 
     # ------------------------------------------------------------------ replay hook
     def step_raw(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -82,6 +82,7 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.steps_run = 0
+        self.h2d_bytes_last_step = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -156,10 +157,15 @@ class ModelRunner:
             self._meta_event.synchronize()      # the previous upload has left the pinned buffer
         return self._meta_host, self._meta_dev
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None
+             ) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns float32 logits [wanted, vocab] on the device, in the order of the
         entries and of each entry's ``want`` (None when nothing is wanted).  Unknown requests are admitted.
-        On an error nothing advances: pages taken for the step are given back."""
+        On an error nothing advances: pages taken for the step are given back.
+
+        ``device_tokens`` (int32 on the device, one id per token of the step) replaces the entries' token
+        values, which then only give the counts: a decode loop feeds the ids the device chose in the last
+        step without the host waiting for them."""
         eng = self.engine
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -209,6 +215,10 @@ class ModelRunner:
             raise
 
         ctx = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R)
+        if device_tokens is not None:
+            if device_tokens.dtype != torch.int32 or device_tokens.numel() < T or not device_tokens.is_cuda:
+                raise StepError("device_tokens must be int32 on the device with one id per token")
+            ctx.token_ids[:T].copy_(device_tokens[:T], non_blocking=True)
         try:
             logits = self.model.forward(ctx)
         except Exception:
@@ -261,6 +271,7 @@ class ModelRunner:
         for (_, a), off in zip(arrays, offsets):
             hv[off:off + a.size] = a
         dev[:total].copy_(host[:total], non_blocking=True)
+        self.h2d_bytes_last_step = total * 4
         self._meta_event = torch.cuda.Event()
         self._meta_event.record()
         view = {name: dev[off:off + max(1, a.size)] for (name, a), off in zip(arrays, offsets)}

@@ -43,9 +43,19 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(code: int, what: str) -> None:
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far by this process."""
+    return _LAUNCHES
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _LAUNCHES
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code}")
+    _LAUNCHES += kernels
 
 
 def _cuda(*ts):
