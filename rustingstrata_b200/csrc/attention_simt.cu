@@ -253,3 +253,93 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
     if (dt == RS_BF16) return dispatch_hd<__nv_bfloat16, false>(p, n_work, s);
     return (int)cudaErrorInvalidValue;
 }
+
+// =============================================================================================
+// Decode attention without a caller-supplied workspace (see attention_decode_noalloc.h).
+// The array below is the workspace.  In host code its name is only a handle for the runtime,
+// not a device address: the address each device maps it to is asked for once per device with
+// cudaGetSymbolAddress and passed to the kernels like any other pointer.
+// =============================================================================================
+#include "attention_decode_noalloc.h"
+#include <mutex>
+#include <stdio.h>
+
+static __device__ __align__(256) float rs_noalloc_partial[RS_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int RS_NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_address[RS_NOALLOC_MAX_DEVICES] = {nullptr};
+std::mutex g_noalloc_mutex;
+thread_local char g_noalloc_error[256] = "";
+
+int noalloc_fail(int code, const char* fmt, long a = 0, long b = 0) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), fmt, a, b);
+    return code;
+}
+
+// Device address of the array on the current device; looked up at the first call per device.
+int noalloc_address(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return noalloc_fail((int)e, "cudaGetDevice failed with CUDA error %ld", (long)e);
+    if (dev < 0 || dev >= RS_NOALLOC_MAX_DEVICES)
+        return noalloc_fail(RS_NOALLOC_BAD_ARGUMENT, "device index %ld is beyond the %ld devices this entry point tracks",
+                            dev, RS_NOALLOC_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_address[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, rs_noalloc_partial);
+        if (e != cudaSuccess || p == nullptr)
+            return noalloc_fail(e != cudaSuccess ? (int)e : RS_NOALLOC_BAD_ARGUMENT,
+                                "cudaGetSymbolAddress for the built-in workspace failed with CUDA error %ld", (long)e);
+        g_noalloc_address[dev] = p;
+    }
+    *out = g_noalloc_address[dev];
+    return 0;
+}
+}  // namespace
+
+RS_EXPORT long rs_attention_decode_noalloc_capacity(void) { return RS_NOALLOC_MAX_FLOATS; }
+
+RS_EXPORT const char* rs_attention_decode_noalloc_error(void) { return g_noalloc_error; }
+
+RS_EXPORT int rs_attention_decode_noalloc(const void* q, long q_stride, void* out, long out_stride, int dt,
+                                          const void* cache, long page_stride, int num_pages, int page_size,
+                                          const int* block_table, int table_stride, const int* q_start,
+                                          const int* kv_len, const int* work, int n_work, int n_q, int n_kv, int hd,
+                                          int window, float scale, int split_keys, int max_splits,
+                                          const int* split_start, int total_splits, int* status, void* stream) {
+    g_noalloc_error[0] = 0;
+    if (n_work <= 0) return 0;
+    if (hd <= 0 || hd % 16 || hd > 256 || n_kv <= 0 || n_q <= 0 || n_q % n_kv)
+        return noalloc_fail(RS_NOALLOC_BAD_ARGUMENT, "head size %ld must be a multiple of 16 up to 256 and the %ld query "
+                            "heads a multiple of the key/value heads", hd, n_q);
+    if (split_keys <= 0 || split_keys % KT || max_splits <= 0 || total_splits <= 0 || split_start == nullptr)
+        return noalloc_fail(RS_NOALLOC_BAD_ARGUMENT, "split_keys %ld must be a positive multiple of 32 and the split "
+                            "counts positive (total_splits %ld)", split_keys, total_splits);
+    const long need = (long)total_splits * n_q * (hd + 2);
+    if (need > (long)RS_NOALLOC_MAX_FLOATS)
+        return noalloc_fail(RS_NOALLOC_TOO_LARGE, "this call needs %ld float32 values of partial results, the built-in "
+                            "workspace holds %ld; use rs_attention_simt with your own buffer", need,
+                            (long)RS_NOALLOC_MAX_FLOATS);
+    float* partial = nullptr;
+    const int rc = noalloc_address(&partial);
+    if (rc != 0) return rc;
+    AttnParams p;
+    p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
+    p.cache = cache; p.page_stride = page_stride; p.num_pages = num_pages; p.page_size = page_size;
+    p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
+    p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.group = n_q / n_kv;
+    p.heads_per_cta = p.group < ROWS ? p.group : ROWS;
+    p.chunks_per_group = (p.group + p.heads_per_cta - 1) / p.heads_per_cta;
+    p.q_per_cta = 1;
+    p.window = window; p.scale = scale; p.decode = 1; p.split_keys = split_keys; p.max_splits = max_splits;
+    p.split_start = split_start; p.partial = partial; p.status = status;
+    cudaStream_t s = (cudaStream_t)stream;
+    int e;
+    if (dt == RS_F32) e = dispatch_hd<float, true>(p, n_work, s);
+    else if (dt == RS_BF16) e = dispatch_hd<__nv_bfloat16, false>(p, n_work, s);
+    else return noalloc_fail(RS_NOALLOC_BAD_ARGUMENT, "element type code %ld is neither float32 (0) nor bfloat16 (1)", dt);
+    if (e != 0) return noalloc_fail(e, "a kernel launch failed with CUDA error %ld", (long)e);
+    return 0;
+}
