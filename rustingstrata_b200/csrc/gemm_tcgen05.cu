@@ -1,0 +1,467 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (sm_100a only):
+//   C[m, n] (=|+=) sum_k A[m, k] * W[n, k],  A: [M, K] activations, W: [N, K] weight, both K-major.
+//
+// One persistent CTA per SM walks output tiles of 128 x BN.  Inside a CTA:
+//   warp 0 (one elected lane)  - TMA producer: cp.async.bulk.tensor loads of a 128 x 64 tile of A and a
+//                                BN x 64 tile of W per pipeline stage, 128-byte swizzle, completion on an mbarrier;
+//   warp 1 (one elected lane)  - issues tcgen05.mma (M = 128, N = BN, K = 16, four per stage) with the
+//                                accumulator in tensor memory, tcgen05.commit releases the stage;
+//   warps 2-5                  - epilogue: tcgen05.ld of their 32 accumulator lanes, then one of
+//                                  store bf16 | store f32 | f32 += (residual add) | SiLU(gate)*up on interleaved columns.
+// The accumulator is double buffered in tensor memory (2 x BN columns), so the epilogue of one tile runs
+// under the main loop of the next.  No cluster, no multicast: every CTA loads its own tiles.
+//
+// Every wait on an mbarrier is bounded (about two seconds): on expiry the kernel sets
+// RS_STATUS_WAIT_EXPIRED in the status word, stops issuing work, lets copies in flight land, frees its
+// tensor memory and returns, so a logic error cannot hang the device.
+//
+// Reference counterpart: gemm_f32/gemm_bf16 with epilogue modes 0/1/2 (src/cuda/kernels.cu:1062-1231),
+// an mma.sync kernel whose inputs are rounded to f16; there is no Blackwell kernel in the reference.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <string.h>
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                    // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;      // 16 KiB
+constexpr int THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+
+template <int BN> struct Cfg {
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false (and flags the status word, and raises the CTA's abort flag) on expiry.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicOr(status, RS_STATUS_WAIT_EXPIRED);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T, bf16 inputs, f32 accumulate
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart (stride byte offset), leading byte offset 1 (unused for swizzled K-major),
+// descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: f32 accumulator (bits 4-5 = 1), bf16 A and B (bits 7-9, 10-12 = 1), both K-major,
+// N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct GemmParams {
+    void* C; long ldc;
+    int M, N, K;
+    int vec_ok;            // C rows allow 16-byte vector access
+    int* status;
+};
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0) {
+    // r: 32 consecutive accumulator columns [col0, col0 + 32) of output row `row`
+    if (row >= p.M) return;
+    if (EPI == EPI_SWIGLU_BF16) {
+        // columns alternate gate, up: out[row, (col0 + 2j) / 2] = silu(gate_j) * up_j
+        const int half_n = p.N >> 1, oc0 = col0 >> 1;
+        __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + oc0;
+        if (p.vec_ok && oc0 + 16 <= half_n) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float g0 = __uint_as_float(r[4 * j]), u0 = __uint_as_float(r[4 * j + 1]);
+                const float g1 = __uint_as_float(r[4 * j + 2]), u1 = __uint_as_float(r[4 * j + 3]);
+                __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                packed[j] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (oc0 + j < half_n) {
+                    const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
+                    out[j] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+                }
+            }
+        }
+    } else if (EPI == EPI_STORE_BF16) {
+        __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col0;
+        if (p.vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * j]), __uint_as_float(r[8 * q + 2 * j + 1]));
+                    w[j] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                reinterpret_cast<uint4*>(out)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        }
+    } else {   // float32 store or accumulate
+        float* out = (float*)p.C + (size_t)row * p.ldc + col0;
+        if (p.vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                       __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                if (EPI == EPI_ADD_F32) {
+                    const float4 o = reinterpret_cast<float4*>(out)[q];
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                reinterpret_cast<float4*>(out)[q] = v;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) out[j] = (EPI == EPI_ADD_F32 ? out[j] : 0.f) + __uint_as_float(r[j]);
+        }
+    }
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                       // swizzled tiles need 1024-byte alignment
+    uint8_t* aligned = smem_raw + (base - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + C::STAGES * C::STAGE_BYTES);
+    // barrier layout: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
+    const uint32_t bar0 = base + C::STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+    auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * C::STAGES + b); };
+    auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * C::STAGES + 2 + b); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n, num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;       // m fastest: neighbours share W
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                    const uint32_t sa = base + s * C::STAGE_BYTES;
+                    tma_load_2d(sa, &map_a, kb * BK, m0, full_bar(s));
+                    tma_load_2d(sa + A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+                    if (++s == C::STAGES) { s = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BM, BN);
+            int s = 0; uint32_t phase = 0;
+            bool ok = true;
+            int local = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (!mbar_wait(tempty_bar(buf), ((local >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(s), phase, abort_flag, p.status)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * C::STAGE_BYTES;
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)       // advance 32 bytes (>>4 = 2) per K = 16 inside the swizzle row
+                        umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(empty_bar(s));                   // stage free once these MMAs have read it
+                    if (++s == C::STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(tfull_bar(buf));             // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps 2..5
+        const int quarter = warp & 3;                            // TMEM lanes [32 * quarter, +32) belong to this warp
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+            if (!mbar_wait(tfull_bar(buf), (local >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c, r);
+                tmem_ld_wait();
+                if (n0 + c < p.N) epilogue_chunk<EPI>(p, r, row, n0 + c);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
+    }
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // give loads that were already issued time to land before the shared memory is released
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encoder() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols; h = h * 1000003u ^ (size_t)k.ld;
+        return h * 1000003u ^ (size_t)k.box_rows;
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mutex;
+
+// Tensor map of a row-major [rows, cols] bf16 matrix with row pitch ld elements, box = box_rows x 64, 128-byte swizzle.
+int get_map(const void* ptr, long rows, long cols, long ld, int box_rows, CUtensorMap* out) {
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return 0; }
+    EncodeTiledFn enc = get_encoder();
+    if (!enc) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return 0;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, int EPI>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, int max_ctas, cudaStream_t s) {
+    auto kern = gemm_tc_kernel<BN, EPI>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    int grid = tiles < sm_count() ? tiles : sm_count();
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    kern<<<grid, THREADS, Cfg<BN>::SMEM_BYTES, s>>>(ma, mw, p);
+    return rs_launch_result();
+}
+
+template <int BN>
+int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, int max_ctas, cudaStream_t s) {
+    switch (epi) {
+        case EPI_STORE_BF16: return launch<BN, EPI_STORE_BF16>(ma, mw, p, max_ctas, s);
+        case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(ma, mw, p, max_ctas, s);
+        case EPI_ADD_F32: return launch<BN, EPI_ADD_F32>(ma, mw, p, max_ctas, s);
+        case EPI_SWIGLU_BF16: return launch<BN, EPI_SWIGLU_BF16>(ma, mw, p, max_ctas, s);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+// Whether the tensor-core kernel takes this problem (else the caller uses the CUDA-core kernel):
+// K and the row pitches must keep every row 16-byte aligned, and the pointers themselves too.
+RS_EXPORT int rs_gemm_tc_supported(long a_ptr, long lda, long w_ptr, long ldw, int N, int K, int epi) {
+    if (K <= 0 || N <= 0 || K % 8 || lda % 8 || ldw % 8) return 0;
+    if ((a_ptr & 15) || (w_ptr & 15)) return 0;
+    if (epi == EPI_SWIGLU_BF16 && (N & 1)) return 0;
+    return 1;
+}
+
+// C[M, N] (=|+=) A[M, K] . W[N, K]^T with bf16 inputs.  a_rows is the row capacity of A's buffer (>= M): the
+// tensor map covers the whole buffer, rows beyond M are computed and dropped.  epi: 0 bf16 store, 1 f32 store,
+// 2 f32 accumulate, 3 SiLU(gate)*up over interleaved columns into a bf16 [M, N/2] output.  bn: 64, 128, 256 or
+// 0 to choose.  max_ctas > 0 caps the grid (tests use it to force several tiles per CTA).
+RS_EXPORT int rs_gemm_bf16_tc(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M,
+                              int N, int K, int epi, int bn, int max_ctas, int* status, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!rs_gemm_tc_supported((long)A, lda, (long)W, ldw, N, K, epi) || a_rows < M) return (int)cudaErrorInvalidValue;
+    if (bn == 0) {
+        const long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+        bn = (tiles256 >= 2L * sm_count() && N % 256 == 0) ? 256 : (((long)((M + BM - 1) / BM) * ((N + 127) / 128) >= sm_count()) ? 128 : 64);
+    }
+    CUtensorMap ma, mw;
+    int rc = get_map(A, a_rows, K, lda, BM, &ma);
+    if (rc) return rc;
+    rc = get_map(W, N, K, ldw, bn, &mw);
+    if (rc) return rc;
+    GemmParams p;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
+    const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
+    p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (bn == 256) return launch_epi<256>(epi, ma, mw, p, max_ctas, s);
+    if (bn == 128) return launch_epi<128>(epi, ma, mw, p, max_ctas, s);
+    if (bn == 64) return launch_epi<64>(epi, ma, mw, p, max_ctas, s);
+    return (int)cudaErrorInvalidValue;
+}

@@ -32,6 +32,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 # library name → sources (relative to csrc/) and extra link flags
 LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "core": {"sources": ["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "sampling.cu"], "link": []},
+    # tensor-core paths of the bfloat16 engine; the 32-bit engine never loads this library
+    "bf16": {"sources": ["gemm_tcgen05.cu", "gemv_bf16.cu"], "link": []},
 }
 
 

@@ -211,9 +211,120 @@ def linear_simt(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows
                                  1 if accumulate else 0, _stream()), "linear_simt")
 
 
-def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False) -> None:
-    """The engine's matrix product: picks the kernel for the element types and the shape."""
-    linear_simt(a, weight, out, n_rows, accumulate)
+_bf16 = None
+
+
+def bf16lib():
+    global _bf16
+    if _bf16 is None:
+        lib = load_library("bf16")
+        lib.rs_gemm_bf16_tc.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_gemv_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
+                                     c_void_p]
+        _bf16 = lib
+    return _bf16
+
+
+EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
+GEMV_MAX_ROWS = 32
+
+
+def tensor_core_shape_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the bfloat16 tensor-core kernels take this product: both operands bfloat16, every row
+    16-byte aligned (K and the row pitches multiples of 8 elements, base pointers multiples of 16)."""
+    if a.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return False
+    K = weight.shape[1]
+    return (K % 8 == 0 and a.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0)
+
+
+def _epilogue_code(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:
+    if swiglu:
+        if out.dtype != torch.bfloat16 or accumulate:
+            raise KernelError("the fused SiLU(gate)*up epilogue writes bfloat16 and does not accumulate")
+        return EPI_SWIGLU_BF16
+    if out.dtype == torch.bfloat16:
+        if accumulate:
+            raise KernelError("accumulating products go into the float32 residual stream")
+        return EPI_STORE_BF16
+    if out.dtype == torch.float32:
+        return EPI_ADD_F32 if accumulate else EPI_STORE_F32
+    raise KernelError(f"unsupported output element type {out.dtype}")
+
+
+def _check_product(a, weight, out, n_rows, swiglu):
+    _cuda(a, weight, out)
+    _rows_contiguous(a, "a")
+    _rows_contiguous(weight, "weight")
+    _rows_contiguous(out, "out")
+    N, K = weight.shape
+    n_out = N // 2 if swiglu else N
+    if a.shape[1] != K or out.shape[1] != n_out or n_rows > min(a.shape[0], out.shape[0]) or (swiglu and N % 2):
+        raise KernelError(f"linear: a {tuple(a.shape)} x weight {tuple(weight.shape)} -> out {tuple(out.shape)} "
+                          f"for {n_rows} rows does not fit")
+    return N, K
+
+
+def gemm_bf16_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
+                 swiglu: bool = False, status: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0) -> None:
+    """out[:n_rows] (=|+=) a[:n_rows] @ weight.T on the tcgen05 tensor cores (csrc/gemm_tcgen05.cu).
+    ``swiglu``: weight rows alternate gate, up and out[:, j] = silu(gate_j) * up_j."""
+    N, K = _check_product(a, weight, out, n_rows, swiglu)
+    if not tensor_core_shape_ok(a, weight):
+        raise KernelError(f"gemm_bf16_tc refuses a {tuple(a.shape)} {a.dtype} stride {a.stride(0)} x weight "
+                          f"{tuple(weight.shape)} {weight.dtype}: rows must be bfloat16 and 16-byte aligned")
+    if status is None:
+        status = _default_status(a.device)
+    _check(bf16lib().rs_gemm_bf16_tc(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
+                                     out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), bn, max_ctas,
+                                     _ptr(status), _stream()), "gemm_bf16_tc")
+
+
+def gemv_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
+              swiglu: bool = False) -> None:
+    """The same product for n_rows <= 32, organised around reading the weight once (csrc/gemv_bf16.cu)."""
+    N, K = _check_product(a, weight, out, n_rows, swiglu)
+    if n_rows > GEMV_MAX_ROWS or not tensor_core_shape_ok(a, weight):
+        raise KernelError(f"gemv_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
+                          f"{tuple(weight.shape)} {weight.dtype}: at most {GEMV_MAX_ROWS} rows, bfloat16, 16-byte aligned")
+    _check(bf16lib().rs_gemv_bf16(_ptr(a), a.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), n_rows,
+                                  N, K, _epilogue_code(out, accumulate, swiglu), _stream()), "gemv_bf16")
+
+
+_STATUS = {}
+
+
+def _default_status(device) -> torch.Tensor:
+    t = _STATUS.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[device] = t
+    return t
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
+           status: Optional[torch.Tensor] = None) -> None:
+    """The engine's matrix product: the tensor-core kernels for bfloat16 operands whose rows are 16-byte
+    aligned (skinny kernel up to 32 rows, tcgen05 kernel above), the CUDA-core kernel for everything else
+    (the 32-bit engine, float32-stored weights, odd widths)."""
+    if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
+        if n_rows <= GEMV_MAX_ROWS:
+            gemv_bf16(a, weight, out, n_rows, accumulate)
+        else:
+            gemm_bf16_tc(a, weight, out, n_rows, accumulate, status=status)
+    else:
+        linear_simt(a, weight, out, n_rows, accumulate)
+
+
+def linear_swiglu(a: torch.Tensor, weight_interleaved: torch.Tensor, out: torch.Tensor, n_rows: int,
+                  status: Optional[torch.Tensor] = None) -> None:
+    """out[:, j] = silu(a @ w[2j]) * (a @ w[2j+1]) in one kernel; only for shapes ``tensor_core_shape_ok`` takes."""
+    if n_rows <= GEMV_MAX_ROWS:
+        gemv_bf16(a, weight_interleaved, out, n_rows, swiglu=True)
+    else:
+        gemm_bf16_tc(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
 
 
 # ----------------------------------------------------------------------------- attention

@@ -129,5 +129,5 @@ class CausalLM:
         head_in = rt.get_scratch("head_in")[:, : self.spec.hidden_size]
         logits = rt.get_scratch("logits", torch.float32)[:, : self.spec.vocab_size]
         self.final_norm.forward(residual, head_in, R, rows=ctx.logit_rows)
-        self.head.forward(head_in, logits, R)
+        self.head.forward(head_in, logits, R, status=ctx.status)
         return logits[:R]

@@ -135,7 +135,7 @@ class PagedAttention(Mixer):
         width = self.qkv_width if write_kv else self.q_width
         qkv = rt.get_scratch("qkv")[:, :width]
         w = self.w_qkv if write_kv else self.w_qkv[: self.q_width]
-        ops.linear(h, w, qkv, T)
+        ops.linear(h, w, qkv, T, status=ctx.status)
         table = ctx.block_tables[call.cache_group]
         pos = self.position
         ops.qk_norm_rope_kv(qkv, T, self.n_heads, self.n_kv, self.hd, self.q_norm_w, self.k_norm_w, self.eps,
@@ -153,4 +153,4 @@ class PagedAttention(Mixer):
                                max_splits=plan["max_splits"], split_start=plan["split_start"],
                                total_splits=plan["total_splits"],
                                partial=rt.get_scratch("attn_partial", torch.float32), **common)
-        ops.linear(out, self.w_o, residual, T, accumulate=True)
+        ops.linear(out, self.w_o, residual, T, accumulate=True, status=ctx.status)

@@ -46,5 +46,5 @@ class LinearHead(Part):
     def load(self, tensors):
         self.weight = tensors[self.spec.tensors["weight"]]
 
-    def forward(self, h, logits, n_rows):
-        ops.linear(h, self.weight, logits, n_rows)
+    def forward(self, h, logits, n_rows, status=None):
+        ops.linear(h, self.weight, logits, n_rows, status=status)

@@ -41,7 +41,14 @@ class GatedMLP(FeedForward):
         g, u = tensors[t["gate_proj"]], tensors[t["up_proj"]]
         if g.dtype != u.dtype:
             raise ValueError("gated_mlp: gate and up projections must share an element type")
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        # bfloat16 engine with 16-byte aligned rows: gate and up rows alternate, so the product's epilogue
+        # applies SiLU(gate)*up to neighbouring accumulator columns and the [T, 2I] intermediate never
+        # reaches memory.  Otherwise [gate; up] stacked, followed by the separate activation kernel.
+        self.fused = (g.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0)
+        if self.fused:
+            self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = tensors[t["down_proj"]].contiguous()
 
     def forward(self, h, residual, ctx):
@@ -49,6 +56,9 @@ class GatedMLP(FeedForward):
         T = ctx.n_tokens
         gate_up = rt.get_scratch("gate_up")[:, : 2 * self.inter]
         act = rt.get_scratch("ff_act")[:, : self.inter]
-        ops.linear(h, self.w_gate_up, gate_up, T)
-        ops.silu_mul(gate_up, act, T)
-        ops.linear(act, self.w_down, residual, T, accumulate=True)
+        if self.fused:
+            ops.linear_swiglu(h, self.w_gate_up, act, T, status=ctx.status)
+        else:
+            ops.linear(h, self.w_gate_up, gate_up, T)
+            ops.silu_mul(gate_up, act, T)
+        ops.linear(act, self.w_down, residual, T, accumulate=True, status=ctx.status)

@@ -1,0 +1,134 @@
+"""The bfloat16 tensor-core matrix products (tcgen05 kernel and skinny kernel) against a float64
+product of the same bfloat16 inputs, over many shapes: sizes that are no multiple of any tile, every
+epilogue, several tiles per CTA, tile widths 64/128/256."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from rustingstrata_b200.kernels import ops as o
+    return o
+
+
+def make(M, N, K, cap=None, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    a = torch.randn(cap or M, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    return a, w
+
+
+def err(got, want):
+    return ((got.double() - want).abs().max() / want.abs().max()).item()
+
+
+def silu_mul(x):
+    g, u = x[:, 0::2], x[:, 1::2]
+    return g / (1 + torch.exp(-g)) * u
+
+
+SHAPES = [(128, 256, 64), (128, 128, 128), (129, 136, 72), (300, 520, 200), (2048, 1024, 4096), (257, 6144, 4096),
+          (40, 4096, 1024), (1000, 1000, 1000), (33, 24, 8), (512, 8192, 512)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_tcgen05_gemm_store_and_accumulate(M, N, K, bn):
+    o = ops()
+    a, w = make(M, N, K, cap=M + 5)
+    want = a[:M].double() @ w.double().T
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M + 5, N), 3.0, device=DEV, dtype=torch.bfloat16)
+    o.gemm_bf16_tc(a, w, out, M, status=st, bn=bn)
+    assert err(out[:M], want) < 6e-3 and torch.all(out[M:] == 3.0)
+    f = torch.full((M + 5, N), 3.0, device=DEV)
+    o.gemm_bf16_tc(a, w, f, M, status=st, bn=bn)
+    assert err(f[:M], want) < 1e-5 and torch.all(f[M:] == 3.0)
+    base = torch.randn(M + 5, N, device=DEV)
+    acc = base.clone()
+    o.gemm_bf16_tc(a, w, acc, M, accumulate=True, status=st, bn=bn)
+    assert err(acc[:M], base[:M].double() + want) < 1e-5 and torch.equal(acc[M:], base[M:])
+    assert st.item() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (2048, 2048, 1024), (77, 24576, 4096)])
+@pytest.mark.parametrize("max_ctas", [1, 3, 0])
+def test_tcgen05_gemm_swiglu_and_several_tiles_per_cta(M, N, K, max_ctas):
+    if max_ctas == 1 and M * N > 2048 * 2048:
+        pytest.skip("one CTA for a large product is only slow")
+    o = ops()
+    a, w = make(M, N, K, seed=1)
+    want = silu_mul(a.double() @ w.double().T)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.zeros(M, N // 2, device=DEV, dtype=torch.bfloat16)
+    o.gemm_bf16_tc(a, w, out, M, swiglu=True, status=st, max_ctas=max_ctas)
+    assert err(out, want) < 8e-3 and st.item() == 0
+    f = torch.zeros(M, N, device=DEV)
+    o.gemm_bf16_tc(a, w, f, M, status=st, max_ctas=max_ctas, bn=128)
+    assert err(f, a.double() @ w.double().T) < 1e-5 and st.item() == 0
+
+
+def test_tcgen05_gemm_strided_views_and_unaligned_output():
+    o = ops()
+    big_a = torch.randn(200, 512 + 64, device=DEV).to(torch.bfloat16)
+    a = big_a[:, 64:]                                   # row pitch 576, pointer offset 128 bytes
+    w = (torch.randn(300, 512, device=DEV) / 22).to(torch.bfloat16)
+    big_o = torch.zeros(200, 300 + 3, device=DEV)
+    out = big_o[:, 3:]                                  # rows not 16-byte aligned: scalar stores
+    o.gemm_bf16_tc(a, w, out, 150)
+    assert err(out[:150], a[:150].double() @ w.double().T) < 1e-5 and torch.all(big_o[:, :3] == 0) and torch.all(out[150:] == 0)
+
+
+def test_refused_shapes_say_why_and_linear_falls_back():
+    o = ops()
+    a = torch.randn(64, 250, device=DEV).to(torch.bfloat16)          # K = 250: rows are not 16-byte aligned
+    w = torch.randn(96, 250, device=DEV).to(torch.bfloat16)
+    out = torch.zeros(64, 96, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(o.KernelError, match="16-byte aligned"):
+        o.gemm_bf16_tc(a, w, out, 64)
+    with pytest.raises(o.KernelError, match="16-byte aligned"):
+        o.gemv_bf16(a, w, out, 4)
+    o.linear(a, w, out, 64)                                           # the CUDA-core kernel takes it
+    assert err(out, a.double() @ w.double().T) < 6e-3
+    a32 = torch.randn(64, 256, device=DEV)
+    assert not o.tensor_core_shape_ok(a32, torch.randn(96, 256, device=DEV))
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 24, 25, 32])
+@pytest.mark.parametrize("N,K", [(16, 32), (100, 72), (4096, 4096), (6144, 4096), (1000, 1000), (24576, 4096),
+                                 (4096, 12288), (151936, 256)])
+def test_skinny_kernel(M, N, K):
+    o = ops()
+    a, w = make(M, N, K, cap=M + 2, seed=M)
+    want = a[:M].double() @ w.double().T
+    out = torch.full((M + 2, N), 3.0, device=DEV, dtype=torch.bfloat16)
+    o.gemv_bf16(a, w, out, M)
+    assert err(out[:M], want) < 6e-3 and torch.all(out[M:] == 3.0)
+    f = torch.full((M + 2, N), 3.0, device=DEV)
+    o.gemv_bf16(a, w, f, M)
+    assert err(f[:M], want) < 1e-5
+    base = torch.randn(M + 2, N, device=DEV)
+    acc = base.clone()
+    o.gemv_bf16(a, w, acc, M, accumulate=True)
+    assert err(acc[:M], base[:M].double() + want) < 1e-5 and torch.equal(acc[M:], base[M:])
+    if N % 2 == 0:
+        sw = torch.zeros(M + 2, N // 2, device=DEV, dtype=torch.bfloat16)
+        o.gemv_bf16(a, w, sw, M, swiglu=True)
+        assert err(sw[:M], silu_mul(want)) < 8e-3 and torch.all(sw[M:] == 0)
+
+
+def test_skinny_and_tcgen05_agree_and_rows_do_not_depend_on_the_batch():
+    o = ops()
+    a, w = make(32, 2048, 4096, seed=5)
+    g = torch.zeros(32, 2048, device=DEV)
+    t = torch.zeros(32, 2048, device=DEV)
+    o.gemv_bf16(a, w, g, 32)
+    o.gemm_bf16_tc(a, w, t, 32)
+    assert err(g, t.double()) < 2e-5                    # each is within 1e-5 of the exact product
+    one = torch.zeros(1, 2048, device=DEV)
+    o.gemv_bf16(a[5:6].contiguous(), w, one, 1)
+    assert torch.equal(one[0], g[5])                     # same k order whatever the batch
