@@ -222,6 +222,16 @@ def bf16lib():
                                         c_int, c_int, c_int, c_void_p, c_void_p]
         lib.rs_gemv_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
                                      c_void_p]
+        lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
+                                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                 c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                 c_void_p]
+        lib.rs_attention_decode_bf16_supported.argtypes = [c_int, c_int, c_int]
+        lib.rs_attention_prefill_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
+                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                  c_int, c_int, c_float, c_void_p, c_void_p]
+        lib.rs_attention_prefill_bf16_supported.argtypes = [c_int, c_int, c_int]
+        lib.rs_attention_prefill_bf16_q_per_cta.argtypes = [c_int, c_int]
         _bf16 = lib
     return _bf16
 
@@ -368,6 +378,82 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
         n_kv, head_dim, int(window), float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start),
         _ptr(partial),
         _ptr(status), _stream()), "attention_simt")
+
+
+def attention_prefill_fast_ok(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
+    """Whether the tensor-core portion kernel takes this shape (bfloat16, head size 32/64/96/128)."""
+    return dtype == torch.bfloat16 and bool(bf16lib().rs_attention_prefill_bf16_supported(n_q, n_kv, head_dim))
+
+
+def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, force_simt: bool = False) -> int:
+    """Query tokens per work item of the portion form, for the kernel ``attention_prefill`` will pick."""
+    if not force_simt and attention_prefill_fast_ok(dtype, n_q, n_kv, head_dim):
+        return int(bf16lib().rs_attention_prefill_bf16_q_per_cta(n_q, n_kv))
+    return attention_q_per_cta(n_q, n_kv)
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                      q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
+                      head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor,
+                      force_simt: bool = False) -> None:
+    """Attention of prompt portions; ``work`` lists (sequence, first query) tiles of ``attention_prefill_q_per_cta``
+    tokens.  The tensor-core kernel (csrc/attention_prefill_mma.cu) where it takes the shape, else CUDA cores."""
+    if force_simt or not attention_prefill_fast_ok(q.dtype, n_q, n_kv, head_dim):
+        attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
+                       scale, False, status)
+        return
+    _cuda(q, out, cache, block_table, q_start, kv_len, work, status)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not cache.is_contiguous():
+        raise KernelError("attention_prefill: q, out and cache must be bfloat16 and the cache contiguous")
+    if tuple(cache.shape[1:]) != (2, n_kv, page_size, head_dim):
+        raise KernelError(f"attention_prefill: cache shape {tuple(cache.shape)} is not [pages, 2, {n_kv}, {page_size}, {head_dim}]")
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"attention_prefill: {name} must be int32")
+    _check(bf16lib().rs_attention_prefill_bf16(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
+        _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv, head_dim,
+        int(window), float(scale), _ptr(status), _stream()), "attention_prefill_bf16")
+
+
+def attention_decode_fast_ok(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
+    """Whether the tensor-core decode kernel takes this shape (bfloat16, head size 32/64/96/128, group <= 16)."""
+    return dtype == torch.bfloat16 and bool(bf16lib().rs_attention_decode_bf16_supported(n_q, n_kv, head_dim))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                     q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
+                     head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor, split_keys: int,
+                     max_splits: int, split_start: torch.Tensor, total_splits: int, partial: torch.Tensor,
+                     force_simt: bool = False) -> None:
+    """Attention of sequences with one query token each: the tensor-core kernel (csrc/attention_decode_mma.cu)
+    where it takes the shape, else the CUDA-core kernel's split form.  Same partial-workspace layout."""
+    if force_simt or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim):
+        attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
+                       scale, True, status, split_keys=split_keys, max_splits=max_splits, split_start=split_start,
+                       total_splits=total_splits, partial=partial)
+        return
+    _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not cache.is_contiguous():
+        raise KernelError("attention_decode: q, out and cache must be bfloat16 and the cache contiguous")
+    if tuple(cache.shape[1:]) != (2, n_kv, page_size, head_dim):
+        raise KernelError(f"attention_decode: cache shape {tuple(cache.shape)} is not [pages, 2, {n_kv}, {page_size}, {head_dim}]")
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work),
+                    ("split_start", split_start)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"attention_decode: {name} must be int32")
+    need = attention_partial_floats(total_splits, n_q, head_dim)
+    if partial.dtype != torch.float32 or partial.numel() < need:
+        raise KernelError(f"attention_decode: needs {need} float32 values of partial workspace")
+    _check(bf16lib().rs_attention_decode_bf16(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
+        _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv, head_dim,
+        int(window), float(scale), split_keys, max_splits, _ptr(split_start), _ptr(partial), _ptr(status), _stream()),
+        "attention_decode_bf16", 2)
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -105,7 +105,7 @@ class PagedAttention(Mixer):
     # ---------------------------------------------------------------- planning
     def plan_key(self):
         if self.q_per_cta is None:
-            self.q_per_cta = ops.attention_q_per_cta(self.n_heads, self.n_kv)
+            self.q_per_cta = ops.attention_prefill_q_per_cta(self.runtime.dtype, self.n_heads, self.n_kv, self.hd)
         return ("paged_attention", self.q_per_cta, self.window)
 
     def build_plan(self, batch: HostBatch):
@@ -147,10 +147,10 @@ class PagedAttention(Mixer):
                       n_q=self.n_heads, n_kv=self.n_kv, head_dim=self.hd, page_size=rt.page_size, window=self.window,
                       scale=self.scale, status=ctx.status)
         if plan["n_prefill"]:
-            ops.attention_simt(work=plan["prefill_work"], n_work=plan["n_prefill"], decode=False, **common)
+            ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], **common)
         if plan["n_decode"]:
-            ops.attention_simt(work=plan["decode_work"], n_work=plan["n_decode"], decode=True, split_keys=SPLIT_KEYS,
-                               max_splits=plan["max_splits"], split_start=plan["split_start"],
-                               total_splits=plan["total_splits"],
-                               partial=rt.get_scratch("attn_partial", torch.float32), **common)
+            ops.attention_decode(work=plan["decode_work"], n_work=plan["n_decode"], split_keys=SPLIT_KEYS,
+                                 max_splits=plan["max_splits"], split_start=plan["split_start"],
+                                 total_splits=plan["total_splits"],
+                                 partial=rt.get_scratch("attn_partial", torch.float32), **common)
         ops.linear(out, self.w_o, residual, T, accumulate=True, status=ctx.status)

@@ -211,7 +211,7 @@ def ref_attention(q, keys, vals, q_pos, n_kv, window, scale):
     return out
 
 
-def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=None):
+def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=None, force_simt=False):
     """seqs: list of (kv_len, q_len).  Builds a shuffled paged cache, runs the kernels the mixer would
     run (split form for one query, tile form otherwise) and returns (got, want) [T, n_q, hd]."""
     o = ops()
@@ -243,7 +243,7 @@ def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=
     q_start = np.zeros(S + 1, np.int32)
     q_start[1:] = np.cumsum(q_lens)
     from rustingstrata_b200.parts.attention import SPLIT_KEYS, decode_splits
-    qpc = o.attention_q_per_cta(n_q, n_kv)
+    qpc = o.attention_prefill_q_per_cta(dtype, n_q, n_kv, hd, force_simt=force_simt)
     dec = np.nonzero(q_lens == 1)[0].astype(np.int32)
     tiles = [(s, off) for s in np.nonzero(q_lens != 1)[0] for off in range(0, q_lens[s], qpc)]
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)  # noqa: E731
@@ -251,14 +251,14 @@ def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=
     common = dict(q=qd, out=out, cache=cache, block_table=perm.to(DEV), q_start=dev(q_start), kv_len=dev(kv_lens),
                   n_q=n_q, n_kv=n_kv, head_dim=hd, page_size=page, window=window, scale=scale, status=st)
     if tiles:
-        o.attention_simt(work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), decode=False, **common)
+        o.attention_prefill(work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), force_simt=force_simt, **common)
     if len(dec):
         splits = decode_splits(kv_lens[dec], window)
         ss = np.zeros(len(dec) + 1, np.int32)
         ss[1:] = np.cumsum(splits)
         partial = torch.empty(o.attention_partial_floats(int(ss[-1]), n_q, hd), device=DEV)
-        o.attention_simt(work=dev(dec), n_work=len(dec), decode=True, split_keys=SPLIT_KEYS, max_splits=int(splits.max()),
-                         split_start=dev(ss), total_splits=int(ss[-1]), partial=partial, **common)
+        o.attention_decode(work=dev(dec), n_work=len(dec), split_keys=SPLIT_KEYS, max_splits=int(splits.max()),
+                           split_start=dev(ss), total_splits=int(ss[-1]), partial=partial, force_simt=force_simt, **common)
     assert st.item() == 0
     want = torch.zeros(T, n_q, hd, dtype=torch.float64)
     for s, (kv, ql) in enumerate(seqs):
@@ -302,6 +302,38 @@ def test_attention_finds_a_far_key_among_hundreds(dtype, far):
     got, want = run_attention(dtype, 4, 2, hd, 16, seqs, boost=boost)
     close(got, want, tol(dtype, 3e-6, 1.5e-2))
     assert (got[0].double().cpu() - want[0]).abs().max() < 0.05
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (6, 2, 32, 4), (16, 1, 64, 8), (3, 3, 96, 16),
+                                              (9, 1, 64, 16)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_decode_tensor_core_kernel_agrees_with_the_cuda_core_kernel(n_q, n_kv, hd, page, window):
+    from rustingstrata_b200.kernels import ops as o
+    assert o.attention_decode_fast_ok(torch.bfloat16, n_q, n_kv, hd)
+    assert not o.attention_decode_fast_ok(torch.float32, n_q, n_kv, hd)
+    assert not o.attention_decode_fast_ok(torch.bfloat16, 34, 2, 64) and not o.attention_decode_fast_ok(torch.bfloat16, 4, 2, 48)
+    seqs = [(1, 1), (127, 1), (128, 1), (129, 1), (300, 1), (1000, 1), (16, 1), (2048, 1)]
+    torch.manual_seed(3)
+    fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window)
+    torch.manual_seed(3)
+    slow, _ = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, force_simt=True)
+    close(fast, want, 1.5e-2)
+    close(fast, slow.double().cpu(), 1.5e-2)
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (6, 2, 32, 4), (16, 1, 64, 8), (3, 3, 96, 16),
+                                              (10, 2, 64, 16), (40, 1, 64, 16)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_prefill_tensor_core_kernel_agrees_with_the_cuda_core_kernel(n_q, n_kv, hd, page, window):
+    from rustingstrata_b200.kernels import ops as o
+    assert o.attention_prefill_fast_ok(torch.bfloat16, n_q, n_kv, hd) and not o.attention_prefill_fast_ok(torch.float32, n_q, n_kv, hd)
+    seqs = [(37, 37), (300, 2), (65, 20), (64, 64), (129, 128), (200, 33), (128, 2), (700, 257), (2, 2), (1000, 3)]
+    torch.manual_seed(4)
+    fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window)
+    torch.manual_seed(4)
+    slow, _ = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, force_simt=True)
+    close(fast, want, 1.5e-2)
+    close(fast, slow.double().cpu(), 1.5e-2)
 
 
 def test_attention_refuses_unsupported_sizes():
