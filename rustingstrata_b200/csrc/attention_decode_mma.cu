@@ -12,13 +12,13 @@
 //
 // Reference counterparts: attn_decode_gqa_* + attn_merge (src/cuda/kernels.cu:2571-2625): K/V of a group
 // read once with cp.async double buffering, CUDA-core dot products, 32 splits.
-#include "common.cuh"
+#include "mma_helpers.cuh"
 #include <math.h>
 
 namespace {
 constexpr int WARPS = 4;
 constexpr int SPLIT = 128;             // keys per CTA; must equal the split size the host plans with
-constexpr int KEYS_PER_WARP = SPLIT / WARPS;
+constexpr int KEYS_PER_WARP = SPLIT / WARPS;   // 32: one 16-key block in each half of the split
 
 struct DecodeParams {
     const __nv_bfloat16* q; long q_stride;
@@ -35,28 +35,6 @@ struct DecodeParams {
     int* status;
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
 template <int HD>
 __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const DecodeParams p) {
     constexpr int LD = HD + 8;                       // padded row: ldmatrix rows fall into distinct banks
@@ -67,6 +45,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
     __nv_bfloat16* Vs = Ks + SPLIT * LD;                                   // [SPLIT][LD]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int w = blockIdx.x, kvh = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();                                      // the new key and value of this step come from the previous kernel
     const int seq = p.work[w];
     const int kv_len = p.kv_len[seq];
     int key_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
@@ -81,28 +61,32 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
     const int* table = p.block_table + (size_t)seq * p.table_stride;
     constexpr int CHUNKS = HD / 8;                   // 16-byte chunks per row
     const int n_keys = key_hi - k_base;              // rows [0, n_keys) of the tile are real keys (some may be below key_lo)
-    for (int i = tid; i < SPLIT * CHUNKS; i += WARPS * 32) {
-        const int j = i / CHUNKS, c = i % CHUNKS;
-        const uint32_t dk = (uint32_t)__cvta_generic_to_shared(Ks + j * LD + c * 8);
-        const uint32_t dv = (uint32_t)__cvta_generic_to_shared(Vs + j * LD + c * 8);
-        const int kpos = k_base + j;
-        bool live = false;
-        if (j < n_keys && kpos >= key_lo) {
-            const int page = table[kpos / p.page_size];
-            if (page >= 0 && page < p.num_pages) {
-                const __nv_bfloat16* src = p.cache + (size_t)page * p.page_stride +
-                                           ((size_t)kvh * p.page_size + (kpos % p.page_size)) * HD + c * 8;
-                cp_async16(dk, src);
-                cp_async16(dv, src + (size_t)p.n_kv * p.page_size * HD);
-                live = true;
-            } else if (c == 0) {
-                atomicOr(p.status, RS_STATUS_BAD_PAGE);
+    // two halves of SPLIT/2 keys, each its own cp.async group: the first half is computed on while the second lands
+    constexpr int HALF = SPLIT / 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        for (int i = tid; i < HALF * CHUNKS; i += WARPS * 32) {
+            const int j = half * HALF + i / CHUNKS, c = i % CHUNKS;
+            const int kpos = k_base + j;
+            bool live = false;
+            if (j < n_keys && kpos >= key_lo) {
+                const int page = table[kpos / p.page_size];
+                if (page >= 0 && page < p.num_pages) {
+                    const __nv_bfloat16* src = p.cache + (size_t)page * p.page_stride +
+                                               ((size_t)kvh * p.page_size + (kpos % p.page_size)) * HD + c * 8;
+                    cp_async16(smem_addr(Ks + j * LD + c * 8), src);
+                    cp_async16(smem_addr(Vs + j * LD + c * 8), src + (size_t)p.n_kv * p.page_size * HD);
+                    live = true;
+                } else if (c == 0) {
+                    atomicOr(p.status, RS_STATUS_BAD_PAGE);
+                }
+            }
+            if (!live) {                              // masked keys still take part in the MMAs: keep them finite
+                *reinterpret_cast<uint4*>(Ks + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(Vs + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
             }
         }
-        if (!live) {                                  // masked keys still take part in the MMAs: keep them finite
-            *reinterpret_cast<uint4*>(Ks + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(Vs + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
-        }
+        cp_async_commit();
     }
 
     // ---- query fragments (rows = heads of the group, zero beyond the group), loaded while the copies fly
@@ -112,14 +96,11 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
         const int d0 = 16 * ks + 2 * t;
-        qf[ks][0] = g < p.group ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d0) : 0u;
-        qf[ks][1] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d0) : 0u;
-        qf[ks][2] = g < p.group ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d0 + 8) : 0u;
-        qf[ks][3] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d0 + 8) : 0u;
+        qf[ks][0] = g < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d0)) : 0u;
+        qf[ks][1] = g + 8 < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d0)) : 0u;
+        qf[ks][2] = g < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d0 + 8)) : 0u;
+        qf[ks][3] = g + 8 < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d0 + 8)) : 0u;
     }
-    cp_async_wait_all();
-    __syncthreads();
-
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[DT][4];
 #pragma unroll
@@ -127,8 +108,11 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
 
 #pragma unroll
     for (int sub = 0; sub < KEYS_PER_WARP / 16; ++sub) {
-        const int j0 = warp * KEYS_PER_WARP + sub * 16;        // first key row of this 16-key block
-        if (k_base + j0 >= key_hi) break;                       // uniform per warp
+        // sub-block `sub` of a warp lies in half `sub` of the split: keys [sub * HALF + 16 warp, +16)
+        if (sub == 0) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncthreads();
+        const int j0 = sub * HALF + warp * 16;                  // first key row of this 16-key block
+        if (k_base + j0 >= key_hi) continue;                    // uniform per warp; later barriers are still reached
         float s[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
@@ -198,18 +182,18 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
     // ---- combine the warps: (max, sum, O) of each warp → shared memory, then one partial per head
     __syncthreads();                                            // everyone is done reading K and V
     float* Os = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][HD + 2]
-    constexpr int OLD = HD + 2;
+    constexpr int OLD = HD + 8;                                 // row stride = 8 mod 32 floats: 8-byte stores of a half-warp hit distinct banks
+    if (g < p.group) {
+        float* r0 = Os + ((size_t)warp * 16 + g) * OLD;
 #pragma unroll
-    for (int d = 0; d < DT; ++d) {
-        float* r0 = Os + ((size_t)warp * 16 + g) * OLD + 8 * d + 2 * t;
-        float* r1 = Os + ((size_t)warp * 16 + g + 8) * OLD + 8 * d + 2 * t;
-        r0[0] = o[d][0]; r0[1] = o[d][1]; r1[0] = o[d][2]; r1[1] = o[d][3];
+        for (int d = 0; d < DT; ++d) *reinterpret_cast<float2*>(r0 + 8 * d + 2 * t) = make_float2(o[d][0], o[d][1]);
+        if (t == 0) { r0[HD] = m_run[0]; r0[HD + 1] = l_run[0]; }
     }
-    if (t == 0) {
-        Os[((size_t)warp * 16 + g) * OLD + HD] = m_run[0];
-        Os[((size_t)warp * 16 + g) * OLD + HD + 1] = l_run[0];
-        Os[((size_t)warp * 16 + g + 8) * OLD + HD] = m_run[1];
-        Os[((size_t)warp * 16 + g + 8) * OLD + HD + 1] = l_run[1];
+    if (g + 8 < p.group) {
+        float* r1 = Os + ((size_t)warp * 16 + g + 8) * OLD;
+#pragma unroll
+        for (int d = 0; d < DT; ++d) *reinterpret_cast<float2*>(r1 + 8 * d + 2 * t) = make_float2(o[d][2], o[d][3]);
+        if (t == 0) { r1[HD] = m_run[1]; r1[HD + 1] = l_run[1]; }
     }
     __syncthreads();
     const size_t slot = (size_t)p.split_start[w] + blockIdx.z;
@@ -238,6 +222,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
 template <int HD>
 __global__ void decode_merge_kernel(const DecodeParams p) {
     const int w = blockIdx.x, h = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();
     const int seq = p.work[w];
     const int kv_len = p.kv_len[seq];
     const int key_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
@@ -245,15 +231,15 @@ __global__ void decode_merge_kernel(const DecodeParams p) {
     const float* base = p.partial + ((size_t)p.split_start[w] * p.n_q + h) * (HD + 2);
     const size_t stride = (size_t)p.n_q * (HD + 2);
     float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[s * stride + HD]);
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ld_dep(base + s * stride + HD));
     __nv_bfloat16* dst = p.out + (size_t)p.q_start[seq] * p.out_stride + (size_t)h * HD;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float num = 0.f, den = 0.f;
         for (int s = 0; s < n_splits; ++s) {
             const float* ps = base + s * stride;
-            const float e = exp2f(ps[HD] - M);
-            num = fmaf(ps[d], e, num);
-            den = fmaf(ps[HD + 1], e, den);
+            const float e = exp2f(ld_dep(ps + HD) - M);
+            num = fmaf(ld_dep(ps + d), e, num);
+            den = fmaf(ld_dep(ps + HD + 1), e, den);
         }
         dst[d] = __float2bfloat16_rn(num / den);
     }
@@ -263,7 +249,7 @@ template <int HD>
 int launch(const DecodeParams& p, int n_work, int max_splits, cudaStream_t s) {
     constexpr int LD = HD + 8;
     constexpr size_t kv_bytes = (size_t)2 * SPLIT * LD * 2;
-    constexpr size_t o_bytes = (size_t)WARPS * 16 * (HD + 2) * 4;
+    constexpr size_t o_bytes = (size_t)WARPS * 16 * (HD + 8) * 4;
     constexpr size_t smem = kv_bytes > o_bytes ? kv_bytes : o_bytes;
     auto kern = decode_attention_kernel<HD>;
     static bool attr_set = false;
@@ -272,11 +258,9 @@ int launch(const DecodeParams& p, int n_work, int max_splits, cudaStream_t s) {
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    kern<<<dim3(n_work, p.n_kv, max_splits), WARPS * 32, smem, s>>>(p);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
-    decode_merge_kernel<HD><<<dim3(n_work, p.n_q), HD >= 128 ? 128 : 64, 0, s>>>(p);
-    return rs_launch_result();
+    int rc = rs_launch_pdl(kern, dim3(n_work, p.n_kv, max_splits), dim3(WARPS * 32), smem, s, p);
+    if (rc != 0) return rc;
+    return rs_launch_pdl(decode_merge_kernel<HD>, dim3(n_work, p.n_q), dim3(HD >= 128 ? 128 : 64), 0, s, p);
 }
 }  // namespace
 

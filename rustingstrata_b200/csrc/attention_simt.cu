@@ -198,8 +198,13 @@ template <typename T, int HDL, bool PRECISE>
 int launch_attention(const AttnParams& p, int n_work, cudaStream_t s) {
     const size_t smem = ((size_t)2 * KT * (p.hd + 1) + (size_t)ROWS * p.hd) * sizeof(float);
     auto kern = paged_attention_kernel<T, HDL, PRECISE>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static size_t smem_allowed = 0;              // raised once per size: not allowed while a stream is capturing
+    cudaError_t e;
+    if (smem > smem_allowed) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        smem_allowed = smem;
+    }
     dim3 grid(n_work, p.n_kv * p.chunks_per_group, p.decode ? p.max_splits : 1);
     kern<<<grid, WARPS * 32, smem, s>>>(p);
     e = cudaGetLastError();

@@ -69,3 +69,35 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     } while (0)
 
 static inline int rs_launch_result() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch -----------------------------------------------------------------
+// Kernels of the decode step are launched so that a kernel may begin (be scheduled, read weights and other
+// data no earlier kernel writes) while its predecessor in the stream is still running.  The contract of every
+// kernel launched with rs_launch_pdl: it executes pdl_wait() before it reads anything an earlier kernel
+// produced and before it writes anything at all; after pdl_wait() every earlier kernel has completed and its
+// writes are visible.  pdl_launch_dependents() lets the next kernel start being scheduled.  Launched without
+// the attribute (or with the switch off) both instructions do nothing and the stream order is the usual one.
+// Data written by an earlier kernel of the step must not be read through the non-coherent path (ld.global.nc,
+// which the compiler may choose for `const __restrict__` pointers) nor be served from a stale L1 line: a kernel
+// that started early shares its SM with kernels that ran before the data was written.  Read it from L2.
+template <typename T> __device__ __forceinline__ T ld_dep(const T* p) { return __ldcg(p); }
+__device__ __forceinline__ float ld_dep_f32(const __nv_bfloat16* p) {
+    return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(p))));
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// one switch per shared library (an inline function's static is shared by its translation units)
+inline int& rs_pdl_switch() { static int on = 1; return on; }
+
+template <typename... KArgs, typename... Args>
+static inline int rs_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = rs_pdl_switch() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}

@@ -12,8 +12,10 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int H, int V, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
-    int id = ids[t];
+    int id = ld_dep(ids + t);
     if (id < 0 || id >= V) {
         if (threadIdx.x == 0) atomicOr(status, RS_STATUS_BAD_TOKEN);
         id = 0;
@@ -27,8 +29,9 @@ RS_EXPORT int rs_embed(const void* table, int table_dt, const int* ids, float* o
                        int* status, void* stream) {
     if (T_ <= 0) return 0;
     RS_DISPATCH_DTYPE(table_dt, T,
-        embed_kernel<T><<<T_, 256, 0, (cudaStream_t)stream>>>((const T*)table, ids, out, H, V, status));
-    return rs_launch_result();
+        return rs_launch_pdl(embed_kernel<T>, dim3(T_), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, out, H, V,
+                             status));
+    return 0;
 }
 
 // --------------------------------------------------------------------------- RMSNorm
@@ -41,14 +44,16 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, long x_stride, const
                                const void* __restrict__ w, int w_dt, float eps, TO* __restrict__ out, long out_stride,
                                int n) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = ld_dep(xr + i); ss = fmaf(v, v, ss); }
     ss = block_sum(ss, scratch);
     const float s = 1.0f / sqrtf(ss / (float)n + eps);
     TO* o = out + (size_t)r * out_stride;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * s * load_any(w, w_dt, i));
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(ld_dep(xr + i) * s * load_any(w, w_dt, i));
 }
 
 RS_EXPORT int rs_rmsnorm(const float* x, long x_stride, const int* rows, const void* w, int w_dt, float eps,
@@ -56,9 +61,9 @@ RS_EXPORT int rs_rmsnorm(const float* x, long x_stride, const int* rows, const v
     if (n_rows <= 0) return 0;
     const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
     RS_DISPATCH_DTYPE(out_dt, TO,
-        rmsnorm_kernel<TO><<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, x_stride, rows, w, w_dt, eps, (TO*)out,
-                                                                        out_stride, n));
-    return rs_launch_result();
+        return rs_launch_pdl(rmsnorm_kernel<TO>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x, x_stride, rows, w,
+                             w_dt, eps, (TO*)out, out_stride, n));
+    return 0;
 }
 
 // --------------------------------------------------------------------------- QK-norm + RoPE + KV write
@@ -77,6 +82,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int
                                        const int* __restrict__ block_table, int table_stride, int page_size,
                                        T* __restrict__ cache, long page_stride, int num_pages, int write_kv,
                                        int n_tokens, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -140,10 +147,11 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
     const int threads = 256;
     const long blocks = (warps * 32 + threads - 1) / threads;
     RS_DISPATCH_DTYPE(dt, T,
-        qk_norm_rope_kv_kernel<T><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
-            (T*)qkv, row_stride, n_q, n_kv, hd, q_w, k_w, w_dt, eps, cos_sin, n_rot, positions, seq_of_token,
-            block_table, table_stride, page_size, (T*)cache, page_stride, num_pages, write_kv, n_tokens, status));
-    return rs_launch_result();
+        return rs_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
+                             (T*)qkv, row_stride, n_q, n_kv, hd, q_w, k_w, w_dt, eps, cos_sin, n_rot, positions,
+                             seq_of_token, block_table, table_stride, page_size, (T*)cache, page_stride, num_pages,
+                             write_kv, n_tokens, status));
+    return 0;
 }
 
 // --------------------------------------------------------------------------- SiLU(gate) * up
@@ -183,3 +191,6 @@ RS_EXPORT int rs_residual_add(float* x, const void* delta, int dt, long n, void*
         residual_add_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, (const T*)delta, n));
     return rs_launch_result();
 }
+
+// Turns programmatic dependent launch on or off for every kernel of this library (default on).
+RS_EXPORT void rs_core_set_pdl(int on) { rs_pdl_switch() = on ? 1 : 0; }

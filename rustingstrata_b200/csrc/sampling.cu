@@ -26,7 +26,7 @@ __device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
 
 __device__ __forceinline__ ArgPair block_argmax(const float* __restrict__ row, int V, ArgPair* sh) {
     ArgPair best{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += THREADS) best = better(best, ArgPair{row[i], i});
+    for (int i = threadIdx.x; i < V; i += THREADS) best = better(best, ArgPair{ld_dep(row + i), i});
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     __shared__ ArgPair sha[32];
     __shared__ float warp_tot[32];
     __shared__ float total_sh;
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * stride;
     const ArgPair best = block_argmax(row, V, sha);
@@ -74,7 +76,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     const int lo = threadIdx.x * per, hi = min(V, lo + per);
     float mine = 0.f;
     for (int i = lo; i < hi; ++i) {
-        const float x = (row[i] - mx) * inv_temp;
+        const float x = (ld_dep(row + i) - mx) * inv_temp;
         mine += (x > -20.0f) ? expf(x) : 0.f;
     }
     // exclusive prefix over threads: warp scan, then scan of warp totals
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         float acc = before;
         int pick = -1, last = -1;
         for (int i = lo; i < hi; ++i) {
-            const float x = (row[i] - mx) * inv_temp;
+            const float x = (ld_dep(row + i) - mx) * inv_temp;
             const float w = (x > -20.0f) ? expf(x) : 0.f;
             if (w > 0.f) {
                 last = i;
@@ -122,6 +124,6 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
 RS_EXPORT int rs_sample(const float* logits, long stride, int rows, int V, const float* temps, const float* uniforms,
                         int* out, int* status, void* stream) {
     if (rows <= 0) return 0;
-    sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, stride, V, temps, uniforms, out, status);
-    return rs_launch_result();
+    return rs_launch_pdl(sample_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, stride, V, temps, uniforms,
+                         out, status);
 }

@@ -1,0 +1,345 @@
+// Skinny bfloat16 matrix product for decode batches (M <= 64 rows of activations), built around one job:
+// stream the weight W[N, K] from HBM exactly once at full bandwidth.
+//
+//   C[m, n] (=|+=) sum_k A[m, k] * W[n, k]
+//
+// Persistent CTAs, one per SM.  The product is cut into units of (64 rows of W) x (128 of k); the units, in
+// row-tile-major order, are dealt to the CTAs in equal contiguous shares ("stream-K"), so every SM reads the
+// same number of bytes whatever N and K are.  In a CTA
+//   warp 4 (one elected lane) - producer: for each unit two TMA loads of 64 x 64 tiles of W (16 KiB) and two
+//                               of the matching [rows of A] x 64 tiles, 128-byte swizzle, into a ring of stages
+//                               that keeps well over 100 KiB in flight per SM independent of the math.  The
+//                               kernel is launched so that it may start while its predecessor still runs:
+//                               the producer fills the whole ring with W (which no kernel writes) at once and
+//                               asks for the A tiles only after the predecessor has finished;
+//   warps 0-3                 - consumers: each owns 16 of the unit's 64 rows; 16-byte shared-memory reads feed
+//                               mma.sync m16n8k16 (W rows are the 16-row operand, up to eight groups of 8
+//                               activation rows the 8-column operand).  W and A are read with the same
+//                               lane-to-k assignment, so no shuffle is needed: the sum over k does not care
+//                               in which order k is visited.
+// A row tile whose k range is shared by several CTAs is completed without anyone waiting: each contributor
+// writes its float32 partial (same thread-to-element mapping everywhere) to a workspace and bumps the tile's
+// counter; the contributor that arrives last adds the partials in CTA order and applies the epilogue, then
+// resets the counter.  The order of the additions is fixed by the shape alone.
+// Epilogues: store bf16 | store f32 | f32 += (residual add) | SiLU(gate)*up over interleaved rows of W.
+// Waits on mbarriers are bounded (tma_helpers.cuh).
+//
+// Reference counterpart: gemv_bf16 / gemvn_bf16 (src/cuda/kernels.cu:307-329,826-853): one warp per row on CUDA
+// cores, each weight read once for up to 4 inputs.
+#include "tma_helpers.cuh"
+#include "mma_helpers.cuh"
+
+namespace {
+constexpr int TILE_N = 64;                 // rows of W per unit
+constexpr int BOX_K = 64;                  // k per TMA box (one 128-byte swizzle row)
+constexpr int BOXES = 2;                   // boxes per unit
+constexpr int TILE_K = BOX_K * BOXES;      // k per unit
+constexpr int W_BOX_BYTES = TILE_N * BOX_K * 2;
+constexpr int W_BYTES = W_BOX_BYTES * BOXES;
+constexpr int CONSUMER_WARPS = 4;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+
+struct SkinnyParams {
+    void* C; long ldc;
+    int M, N, K;
+    int stages;
+    float* workspace;          // [grid][2][CONSUMER_WARPS][NT * 4][32] float32 partials
+    int* counters;             // [row tiles], zero between launches
+    int* status;
+};
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
+
+// first unit of CTA c when U units are dealt to G CTAs as evenly as possible
+__device__ __forceinline__ int first_unit(int c, int U, int G) { return c * (U / G) + (c < U % G ? c : U % G); }
+__device__ __forceinline__ int cta_of_unit(int u, int U, int G) {
+    const int base = U / G, rem = U % G;
+    return u < rem * (base + 1) ? u / (base + 1) : rem + (u - rem * (base + 1)) / base;
+}
+
+template <int NT, int EPI>
+__device__ __forceinline__ void store_tile(const SkinnyParams& p, const float (&acc)[NT][4], int tile, int warp, int g, int t) {
+    const int na = tile * TILE_N + 16 * warp + g, nb = na + 8;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int m0 = 8 * j + 2 * t;
+        if (EPI == EPI_SWIGLU_BF16) {
+            // rows of W alternate gate, up: lanes g and g ^ 1 hold a pair; the even one writes
+            float partner[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) partner[i] = __shfl_xor_sync(0xffffffffu, acc[j][i], 4);
+            if ((g & 1) == 0) {
+                __nv_bfloat16* out = (__nv_bfloat16*)p.C;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int m = m0 + (i & 1), n = (i >> 1) ? nb : na;
+                    if (m < p.M && n + 1 < p.N) {
+                        const float gate = acc[j][i], up = partner[i];
+                        out[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int m = m0 + (i & 1), n = (i >> 1) ? nb : na;
+                if (m < p.M && n < p.N) {
+                    const size_t o = (size_t)m * p.ldc + n;
+                    if (EPI == EPI_STORE_BF16) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(acc[j][i]);
+                    else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = acc[j][i];
+                    else ((float*)p.C)[o] += acc[j][i];
+                }
+            }
+        }
+    }
+}
+
+template <int NT, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const SkinnyParams p) {
+    constexpr int MP = 8 * NT;                               // activation rows per stage
+    constexpr int X_BOX_BYTES = MP * BOX_K * 2;                 // >= 1024: every tile stays 1024-byte aligned
+    constexpr int X_BYTES = X_BOX_BYTES * BOXES;
+    constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const int stages = p.stages;
+    const uint32_t bar0 = base + stages * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (base - raw) + stages * STAGE_BYTES + 16 * stages);
+    int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = (p.K + TILE_K - 1) / TILE_K;
+    const int tiles = (p.N + TILE_N - 1) / TILE_N;
+    const int U = tiles * KB, G = gridDim.x;
+    const int u0 = first_unit(blockIdx.x, U, G), u1 = first_unit(blockIdx.x + 1, U, G);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), CONSUMER_WARPS); }
+        *abort_flag = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            pdl_launch_dependents();
+            auto load_w = [&](int s, int tile, int kb) {
+                const uint32_t dst = base + s * STAGE_BYTES;
+#pragma unroll
+                for (int b = 0; b < BOXES; ++b)
+                    tma_load_2d(dst + b * W_BOX_BYTES, &map_w, kb * TILE_K + b * BOX_K, tile * TILE_N, full_bar(s));
+            };
+            auto load_x = [&](int s, int kb) {
+                const uint32_t dst = base + s * STAGE_BYTES + W_BYTES;
+#pragma unroll
+                for (int b = 0; b < BOXES; ++b)
+                    tma_load_2d(dst + b * X_BOX_BYTES, &map_a, kb * TILE_K + b * BOX_K, 0, full_bar(s));
+            };
+            // fill the ring with weights before waiting for the kernel that writes A
+            const int ahead = min(stages, u1 - u0);
+            int tile = u0 / KB, kb = u0 % KB;
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(full_bar(i), W_BYTES + X_BYTES);
+                load_w(i, tile, kb);
+                if (++kb == KB) { kb = 0; ++tile; }
+            }
+            pdl_wait();
+            kb = u0 % KB;
+            for (int i = 0; i < ahead; ++i) {
+                load_x(i, kb);
+                if (++kb == KB) kb = 0;
+            }
+            int s = ahead == stages ? 0 : ahead; uint32_t phase = ahead == stages ? 1u : 0u;
+            for (int u = u0 + ahead; u < u1; ++u) {
+                if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status)) break;
+                mbar_expect_tx(full_bar(s), W_BYTES + X_BYTES);
+                load_w(s, tile, kb);
+                load_x(s, kb);
+                if (++s == stages) { s = 0; phase ^= 1u; }
+                if (++kb == KB) { kb = 0; ++tile; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ consumers
+        const int g = lane >> 2, t = lane & 3;
+        pdl_wait();                                            // C and the workspace belong to earlier kernels until now
+        float acc[NT][4], acc2[NT][4];                         // one set per box: two independent MMA chains
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+            acc2[j][0] = acc2[j][1] = acc2[j][2] = acc2[j][3] = 0.f;
+        }
+        int s = 0; uint32_t phase = 0;
+        bool ok = true;
+        int seg_start = u0;                                    // first unit of the current tile segment
+        int tile = u0 / KB, kb = u0 % KB;
+        for (int u = u0; u < u1 && ok; ++u) {
+            if (!mbar_wait(full_bar(s), phase, abort_flag, p.status)) { ok = false; break; }
+            const uint32_t wst = base + s * STAGE_BYTES, xst = wst + W_BYTES;
+#pragma unroll
+            for (int b = 0; b < BOXES; ++b) {
+                const uint32_t row_a = wst + b * W_BOX_BYTES + (16 * warp + g) * 128, row_b = row_a + 8 * 128;
+                const uint32_t xb = xst + b * X_BOX_BYTES;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    // lane t takes the 16-byte chunks 2t and 2t+1 of the row (the same for W and A, whatever g is:
+                    // the k slots of the MMA pair lane (g, t) of one operand with lane (g', t) of the other);
+                    // with the swizzle the 8 lanes of a quarter-warp then fall into 8 different bank groups
+                    const uint32_t chunk = (uint32_t)(((2 * t + half) ^ g) << 4);
+                    const uint4 wa = lds128(row_a + chunk), wb = lds128(row_b + chunk);
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const uint4 x = lds128(xb + (8 * j + g) * 128 + chunk);
+                        const uint32_t a0[4] = {wa.x, wb.x, wa.y, wb.y}, a1[4] = {wa.z, wb.z, wa.w, wb.w};
+                        if (b == 0) { mma16816(acc[j], a0, x.x, x.y); mma16816(acc[j], a1, x.z, x.w); }
+                        else { mma16816(acc2[j], a0, x.x, x.y); mma16816(acc2[j], a1, x.z, x.w); }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(s));
+            if (++s == stages) { s = 0; phase ^= 1u; }
+
+            if (kb == KB - 1 || u == u1 - 1) {
+                // ---- the CTA's share of this row tile ends here
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { acc[j][i] += acc2[j][i]; acc2[j][i] = 0.f; }
+                const int tile_first = tile * KB;
+                const bool whole = seg_start == tile_first && kb == KB - 1;
+                if (whole) {
+                    store_tile<NT, EPI>(p, acc, tile, warp, g, t);
+                } else {
+                    const int c_first = cta_of_unit(tile_first, U, G), c_last = cta_of_unit(tile_first + KB - 1, U, G);
+                    const int slot = (u0 >= tile_first) ? 0 : 1;            // 0: the tile my range starts in
+                    float* mine = p.workspace + ((((size_t)blockIdx.x * 2 + slot) * CONSUMER_WARPS + warp) * (NT * 4)) * 32;
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) __stcg(mine + (j * 4 + i) * 32 + lane, acc[j][i]);
+                    __threadfence();
+                    consumer_sync();
+                    if (threadIdx.x == 0) {
+                        const int seen = atomicAdd(p.counters + tile, 1);
+                        *last_flag = (seen == c_last - c_first) ? 1 : 0;
+                    }
+                    consumer_sync();
+                    if (*last_flag) {
+                        __threadfence();
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+                        for (int c = c_first; c <= c_last; ++c) {
+                            const int cslot = (first_unit(c, U, G) >= tile_first) ? 0 : 1;
+                            const float* src = p.workspace + ((((size_t)c * 2 + cslot) * CONSUMER_WARPS + warp) * (NT * 4)) * 32;
+#pragma unroll
+                            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) acc[j][i] += __ldcg(src + (j * 4 + i) * 32 + lane);
+                        }
+                        store_tile<NT, EPI>(p, acc, tile, warp, g, t);
+                        if (threadIdx.x == 0) p.counters[tile] = 0;
+                    }
+                    consumer_sync();                                         // last_flag may be rewritten next time
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+                seg_start = u + 1;
+            }
+            if (++kb == KB) { kb = 0; ++tile; }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);          // let loads already issued land
+    }
+    __syncthreads();
+}
+
+template <int NT> constexpr int stage_bytes() { return W_BYTES + 8 * NT * TILE_K * 2; }
+
+template <int NT, int EPI>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, SkinnyParams p, int max_ctas, cudaStream_t s) {
+    constexpr int SB = stage_bytes<NT>();
+    int stages = SMEM_BUDGET / SB;
+    if (stages > 24) stages = 24;
+    const int smem = stages * SB + 1024 + 16 * stages + 64;
+    auto kern = skinny_gemm_kernel<NT, EPI>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    p.stages = stages;
+    const long U = (long)((p.N + TILE_N - 1) / TILE_N) * ((p.K + TILE_K - 1) / TILE_K);
+    long grid = rs_tma::sm_count();
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    if (grid > U) grid = U;
+    return rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
+}
+
+template <int NT>
+int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const SkinnyParams& p, int max_ctas, cudaStream_t s) {
+    switch (epi) {
+        case EPI_STORE_BF16: return launch<NT, EPI_STORE_BF16>(mw, ma, p, max_ctas, s);
+        case EPI_STORE_F32: return launch<NT, EPI_STORE_F32>(mw, ma, p, max_ctas, s);
+        case EPI_ADD_F32: return launch<NT, EPI_ADD_F32>(mw, ma, p, max_ctas, s);
+        case EPI_SWIGLU_BF16: return launch<NT, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, s);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+RS_EXPORT int rs_skinny_gemm_max_rows() { return 64; }
+
+// float32 values of workspace and ints of counters a launch needs (for any M <= 64 and this N).
+RS_EXPORT long rs_skinny_gemm_workspace_floats() { return (long)rs_tma::sm_count() * 2 * CONSUMER_WARPS * 8 * 4 * 32; }
+RS_EXPORT long rs_skinny_gemm_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
+
+// C[M, N] (=|+=) A[M, K] . W[N, K]^T for M <= 64, bf16 inputs; same epilogue codes as rs_gemm_bf16_tc.  a_rows is the
+// row capacity of A's buffer.  workspace/counters as sized above; counters must be zero before the first launch and
+// are left zero.  Launches that share a workspace must not overlap on the GPU.
+RS_EXPORT int rs_skinny_gemm_bf16(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M,
+                                  int N, int K, int epi, float* workspace, int* counters, int max_ctas, int* status,
+                                  void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
+        workspace == nullptr || counters == nullptr)
+        return (int)cudaErrorInvalidValue;
+    if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
+    const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+    CUtensorMap mw, ma;
+    int rc = rs_tma::get_map(W, N, K, ldw, TILE_N, &mw);
+    if (rc) return rc;
+    rc = rs_tma::get_map(A, a_rows, K, lda, 8 * nt, &ma);
+    if (rc) return rc;
+    SkinnyParams p;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.counters = counters;
+    p.status = status;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (nt) {
+        case 1: return launch_epi<1>(epi, mw, ma, p, max_ctas, s);
+        case 2: return launch_epi<2>(epi, mw, ma, p, max_ctas, s);
+        case 4: return launch_epi<4>(epi, mw, ma, p, max_ctas, s);
+        default: return launch_epi<8>(epi, mw, ma, p, max_ctas, s);
+    }
+}
+
+// Turns programmatic dependent launch on or off for every kernel of this library (default on).
+RS_EXPORT void rs_bf16_set_pdl(int on) { rs_pdl_switch() = on ? 1 : 0; }

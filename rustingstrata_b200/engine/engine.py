@@ -81,34 +81,47 @@ class Engine:
                 self.scheduler.step_index += 1     # nothing could run (arrivals in the future): time passes
             return []
         entries = [StepEntry(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
-        logits = self.runner.step(entries)
-        chosen = self._choose(batch, logits)
+        sampled = [s for s in batch if s.samples]
+        host_rows = self._prepare_sampling(sampled)
+        logits = self.runner.step(entries, post=self._sample_post if sampled else None)
+        chosen = self._collect(sampled, host_rows, logits)
         done = self.scheduler.advance(batch, chosen)
         for r in done:
             self._samplers.pop(r.rid, None)
         return done
 
-    def _choose(self, batch: Sequence[Scheduled], logits: Optional[torch.Tensor]) -> Dict[Hashable, int]:
-        sampled = [s for s in batch if s.samples]
-        if not sampled:
-            self.runner.check_status()
-            return {}
+    def _prepare_sampling(self, sampled: Sequence[Scheduled]) -> List[int]:
+        """Uploads temperatures and uniforms of the rows the device will sample; returns the rows that
+        need the host sampler instead (cuts or penalties)."""
         R = len(sampled)
+        if not R:
+            return []
         th, uh = self._temps_h.numpy(), self._unif_h.numpy()
         host_rows = []
         for i, s in enumerate(sampled):
             sp: SamplingParams = s.request.sampling
-            smp = self._samplers[s.request.rid]
             if sp.needs_host():
                 host_rows.append(i)
                 th[i] = 0.0
                 uh[i] = 0.0
             else:
                 th[i] = sp.temp
-                uh[i] = smp.rng.uniform() if sp.temp > 0 else 0.0
+                uh[i] = self._samplers[s.request.rid].rng.uniform() if sp.temp > 0 else 0.0
         self._temps_d[:R].copy_(self._temps_h[:R], non_blocking=True)
         self._unif_d[:R].copy_(self._unif_h[:R], non_blocking=True)
-        ops.sample(logits, R, self._picked_d, self.runner.status, self._temps_d, self._unif_d)
+        return host_rows
+
+    def _sample_post(self, logits: torch.Tensor, n_rows: int) -> None:
+        """The device's token choice, run right after the forward pass (inside the graph of a captured step)."""
+        ops.sample(logits, n_rows, self._picked_d, self.runner.status, self._temps_d, self._unif_d)
+
+    def _collect(self, sampled: Sequence[Scheduled], host_rows: List[int], logits: Optional[torch.Tensor]
+                 ) -> Dict[Hashable, int]:
+        """Brings the chosen ids (and the logits of host-sampled rows) back and records them."""
+        if not sampled:
+            self.runner.check_status()
+            return {}
+        R = len(sampled)
         self._picked_h[:R].copy_(self._picked_d[:R], non_blocking=True)
         self._picked_h[R:R + 1].copy_(self.runner.status, non_blocking=True)
         host_logits = {i: logits[i].to("cpu").numpy() for i in host_rows}      # also waits for the stream
@@ -168,9 +181,10 @@ class Engine:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         ev0.record()
+        self._temps_h[:B].zero_()
+        self._temps_d[:B].copy_(self._temps_h[:B], non_blocking=True)
         for i in range(n_steps):
-            logits = r.step(entries, device_tokens=self._picked_d)
-            ops.sample(logits, B, self._picked_d, r.status)
+            r.step(entries, device_tokens=self._picked_d, post=self._sample_post)
             history[i].copy_(self._picked_d[:B], non_blocking=True)
         ev1.record()
         torch.cuda.synchronize()

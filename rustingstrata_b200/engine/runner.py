@@ -12,6 +12,7 @@ every row stored before attention reads it, the head run on the wanted rows only
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Mapping, Optional, Sequence
 
@@ -83,6 +84,10 @@ class ModelRunner:
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.steps_run = 0
         self.h2d_bytes_last_step = 0
+        # pure-decode steps (one token per request) are captured once per shape and replayed
+        self.use_graphs = True
+        self._graphs: Dict = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -148,7 +153,8 @@ class ModelRunner:
     # ------------------------------------------------------------------ the step function
     def _meta_buffers(self, n_ints: int):
         if self._meta_host is None or self._meta_host.numel() < n_ints:
-            cap = max(n_ints, 1 << 14)
+            cap = max(n_ints, 1 << 18)
+            self._graphs.clear()                    # captured steps point into the old buffer
             cap = 1 << (cap - 1).bit_length()
             self._meta_host = torch.empty(cap, dtype=torch.int32).pin_memory()
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
@@ -157,7 +163,7 @@ class ModelRunner:
             self._meta_event.synchronize()      # the previous upload has left the pinned buffer
         return self._meta_host, self._meta_dev
 
-    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None, post=None
              ) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns float32 logits [wanted, vocab] on the device, in the order of the
         entries and of each entry's ``want`` (None when nothing is wanted).  Unknown requests are admitted.
@@ -165,7 +171,14 @@ class ModelRunner:
 
         ``device_tokens`` (int32 on the device, one id per token of the step) replaces the entries' token
         values, which then only give the counts: a decode loop feeds the ids the device chose in the last
-        step without the host waiting for them."""
+        step without the host waiting for them.  ``post(logits, n_rows)`` is called after the forward pass
+        (the engine's sampling kernel); in a captured step it becomes part of the graph, so it must only
+        launch kernels on buffers that stay where they are.
+
+        A step of single tokens only is captured in a CUDA graph the first time its shape occurs (number of
+        requests and logit rows, block-table width and attention splits rounded up to buckets) and replayed
+        afterwards: the per-step index arrays live at fixed places of one device buffer that is refreshed
+        before every replay."""
         eng = self.engine
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -214,13 +227,46 @@ class ModelRunner:
                 self.cache.release(rid)
             raise
 
-        ctx = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R)
-        if device_tokens is not None:
-            if device_tokens.dtype != torch.int32 or device_tokens.numel() < T or not device_tokens.is_cuda:
-                raise StepError("device_tokens must be int32 on the device with one id per token")
-            ctx.token_ids[:T].copy_(device_tokens[:T], non_blocking=True)
+        if device_tokens is not None and (device_tokens.dtype != torch.int32 or device_tokens.numel() < T
+                                          or not device_tokens.is_cuda):
+            raise StepError("device_tokens must be int32 on the device with one id per token")
+        graphable = self.use_graphs and bool((q_lens == 1).all())
         try:
-            logits = self.model.forward(ctx)
+            ctx, layout = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R, graphable)
+
+            def run():
+                if device_tokens is not None:
+                    ctx.token_ids[:T].copy_(device_tokens[:T], non_blocking=True)
+                out = self.model.forward(ctx)
+                if post is not None:
+                    post(out, R)
+                return out
+            if not graphable:
+                logits = run()
+            else:
+                key = (layout, None if device_tokens is None else device_tokens.data_ptr(), post)
+                entry = self._graphs.get(key)
+                if entry is None:
+                    logits = run()                        # first time: eagerly (allocates every scratch buffer) ...
+                    self._graphs[key] = "warm"
+                elif entry == "warm":                     # ... second time: capture (the capture also runs nothing)
+                    graph = torch.cuda.CUDAGraph()
+                    # Python's cyclic collector must not run while the stream is capturing: freeing another
+                    # engine's pinned buffers or graphs there is "not permitted" and invalidates the capture
+                    gc_was_on = gc.isenabled()
+                    gc.disable()
+                    try:
+                        with torch.cuda.graph(graph):
+                            logits = run()
+                    finally:
+                        if gc_was_on:
+                            gc.enable()
+                    self._graphs[key] = (graph, logits)
+                    graph.replay()
+                else:
+                    graph, logits = entry
+                    graph.replay()
+                    self.graph_replays += 1
         except Exception:
             for rid in reserved:
                 self.cache.rollback(rid)
@@ -232,7 +278,10 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
-    def _build_context(self, entries, tokens, q_lens, old, kv_lens, T, R) -> StepContext:
+    def _build_context(self, entries, tokens, q_lens, old, kv_lens, T, R, bucketed=False):
+        """The step's index arrays in one pinned buffer, uploaded with one copy.  Returns the context and a
+        hashable description of the layout (sizes and host scalars): equal layouts put every array at the
+        same device address, which is what lets a captured step be replayed."""
         S = len(entries)
         q_start = np.zeros(S + 1, dtype=np.int32)
         np.cumsum(q_lens, out=q_start[1:])
@@ -246,13 +295,15 @@ class ModelRunner:
         for g in range(n_groups):
             rows = [self.cache.table(e.rid, g) for e in entries]
             width = max(1, max(len(r) for r in rows))
+            if bucketed:
+                width = (width + 63) // 64 * 64
             tab = np.full((S, width), -1, dtype=np.int32)
             for i, r in enumerate(rows):
                 tab[i, :len(r)] = r
             tables.append(tab)
         batch = HostBatch(n_tokens=T, n_seqs=S, q_lens=q_lens, kv_lens=kv_lens.astype(np.int32), q_start=q_start,
                           state_slots=slots, first_step=(old == 0).astype(np.int32), page_size=self.page_size,
-                          max_blocks=[t.shape[1] for t in tables])
+                          max_blocks=[t.shape[1] for t in tables], bucketed=bucketed)
         plans = self.model.plan(batch)
 
         arrays = [("token_ids", tokens.astype(np.int32)), ("positions", positions), ("seq_of_token", seq_of_token),
@@ -281,10 +332,14 @@ class ModelRunner:
                               for name, val in plan.items()}
         block_tables = [view[("table", g)][: S * tables[g].shape[1]].view(S, tables[g].shape[1])
                         for g in range(n_groups)]
-        return StepContext(n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=view["token_ids"],
-                           positions=view["positions"], seq_of_token=view["seq_of_token"], q_start=view["q_start"],
-                           kv_len=view["kv_len"], state_slots=view["state_slots"], logit_rows=view["logit_rows"],
-                           block_tables=block_tables, status=self.status, host=batch, plans=dev_plans)
+        ctx = StepContext(n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=view["token_ids"],
+                          positions=view["positions"], seq_of_token=view["seq_of_token"], q_start=view["q_start"],
+                          kv_len=view["kv_len"], state_slots=view["state_slots"], logit_rows=view["logit_rows"],
+                          block_tables=block_tables, status=self.status, host=batch, plans=dev_plans)
+        scalars = tuple((repr(key), name, val) for key, plan in plans.items() for name, val in sorted(plan.items())
+                        if not isinstance(val, np.ndarray))
+        layout = (dev.data_ptr(), tuple(a.size for _, a in arrays), scalars)
+        return ctx, layout
 
     def check_status(self) -> None:
         """Waits for the device and raises if a kernel of an earlier step flagged a bad input."""

@@ -46,6 +46,12 @@ def _stream() -> c_void_p:
 _LAUNCHES = 0
 
 
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the decode-path kernels (default on); off gives plain stream order."""
+    core().rs_core_set_pdl(1 if on else 0)
+    bf16lib().rs_bf16_set_pdl(1 if on else 0)
+
+
 def launch_count() -> int:
     """Kernels of this package launched so far by this process."""
     return _LAUNCHES
@@ -220,8 +226,9 @@ def bf16lib():
         lib = load_library("bf16")
         lib.rs_gemm_bf16_tc.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_void_p, c_void_p]
-        lib.rs_gemv_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
-                                     c_void_p]
+        lib.rs_skinny_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                            c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        lib.rs_skinny_gemm_workspace_floats.restype = c_long
         lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -237,7 +244,6 @@ def bf16lib():
 
 
 EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
-GEMV_MAX_ROWS = 32
 
 
 def tensor_core_shape_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -292,15 +298,36 @@ def gemm_bf16_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
                                      _ptr(status), _stream()), "gemm_bf16_tc")
 
 
-def gemv_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
-              swiglu: bool = False) -> None:
-    """The same product for n_rows <= 32, organised around reading the weight once (csrc/gemv_bf16.cu)."""
+SKINNY_MAX_ROWS = 64     # what the kernel takes
+SKINNY_ROWS = 32         # up to here the engine prefers it to the tcgen05 kernel
+_SKINNY_SCRATCH = {}
+
+
+def _skinny_scratch(device):
+    """Workspace and tile counters of the skinny product, one pair per device, made at the first call
+    (before any graph capture: the engine runs every shape once eagerly first)."""
+    sc = _SKINNY_SCRATCH.get(device)
+    if sc is None:
+        ws = torch.empty(int(bf16lib().rs_skinny_gemm_workspace_floats()), dtype=torch.float32, device=device)
+        counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        sc = _SKINNY_SCRATCH[device] = (ws, counters)
+    return sc
+
+
+def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
+                     swiglu: bool = False, status: Optional[torch.Tensor] = None, max_ctas: int = 0) -> None:
+    """out[:n_rows] (=|+=) a[:n_rows] @ weight.T for n_rows <= 64: persistent CTAs stream the weight through a
+    TMA-fed ring of shared-memory stages (csrc/skinny_gemm_tma.cu)."""
     N, K = _check_product(a, weight, out, n_rows, swiglu)
-    if n_rows > GEMV_MAX_ROWS or not tensor_core_shape_ok(a, weight):
-        raise KernelError(f"gemv_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
-                          f"{tuple(weight.shape)} {weight.dtype}: at most {GEMV_MAX_ROWS} rows, bfloat16, 16-byte aligned")
-    _check(bf16lib().rs_gemv_bf16(_ptr(a), a.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), n_rows,
-                                  N, K, _epilogue_code(out, accumulate, swiglu), _stream()), "gemv_bf16")
+    if n_rows > SKINNY_MAX_ROWS or not tensor_core_shape_ok(a, weight) or N > 64 * (1 << 16):
+        raise KernelError(f"skinny_gemm_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
+                          f"{tuple(weight.shape)} {weight.dtype}: at most {SKINNY_MAX_ROWS} rows, bfloat16, 16-byte aligned")
+    if status is None:
+        status = _default_status(a.device)
+    ws, counters = _skinny_scratch(a.device)
+    _check(bf16lib().rs_skinny_gemm_bf16(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
+                                         out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), _ptr(ws),
+                                         _ptr(counters), max_ctas, _ptr(status), _stream()), "skinny_gemm_bf16")
 
 
 _STATUS = {}
@@ -320,8 +347,8 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int
     aligned (skinny kernel up to 32 rows, tcgen05 kernel above), the CUDA-core kernel for everything else
     (the 32-bit engine, float32-stored weights, odd widths)."""
     if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
-        if n_rows <= GEMV_MAX_ROWS:
-            gemv_bf16(a, weight, out, n_rows, accumulate)
+        if n_rows <= SKINNY_ROWS:
+            skinny_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)
         else:
             gemm_bf16_tc(a, weight, out, n_rows, accumulate, status=status)
     else:
@@ -331,8 +358,8 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int
 def linear_swiglu(a: torch.Tensor, weight_interleaved: torch.Tensor, out: torch.Tensor, n_rows: int,
                   status: Optional[torch.Tensor] = None) -> None:
     """out[:, j] = silu(a @ w[2j]) * (a @ w[2j+1]) in one kernel; only for shapes ``tensor_core_shape_ok`` takes."""
-    if n_rows <= GEMV_MAX_ROWS:
-        gemv_bf16(a, weight_interleaved, out, n_rows, swiglu=True)
+    if n_rows <= SKINNY_ROWS:
+        skinny_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
     else:
         gemm_bf16_tc(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
 

@@ -26,6 +26,7 @@ from .registry import register_part
 from .spec import CacheNeed, TensorNeed
 
 SPLIT_KEYS = 128     # keys per split of the decode form; fixed so a position's reduction order never changes
+SPLIT_BUCKET = 8     # captured steps round the number of splits launched up to a multiple of this
 
 
 def decode_splits(kv_len: np.ndarray, window: int) -> np.ndarray:
@@ -65,7 +66,9 @@ class PagedAttention(Mixer):
         rt = runtime
         rt.scratch("qkv", rt.max_batch_tokens, self.q_width + 2 * self.kv_width)
         rt.scratch("attn_out", rt.max_batch_tokens, self.q_width)
-        max_total_splits = rt.pool_tokens // SPLIT_KEYS + rt.max_seqs + 1
+        # every live sequence may have one partly filled split, and a captured step launches its splits
+        # rounded up to SPLIT_BUCKET
+        max_total_splits = rt.pool_tokens // SPLIT_KEYS + rt.max_seqs * (SPLIT_BUCKET + 1) + 1
         rt.scratch("attn_partial", 1, max_total_splits * self.n_heads * (self.hd + 2), torch.float32)
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
 
@@ -121,9 +124,15 @@ class PagedAttention(Mixer):
             offs = np.arange(0, batch.q_lens[s], qpc, dtype=np.int32)
             tiles.append(np.stack([np.full_like(offs, s), offs], axis=1))
         pre = np.concatenate(tiles, axis=0).astype(np.int32) if tiles else np.zeros((0, 2), np.int32)
+        max_splits = int(splits.max()) if len(dec) else 0
+        total_splits = int(split_start[-1])
+        if batch.bucketed and len(dec):
+            # launch shapes of a captured step: splits beyond a sequence's own count exit at once
+            max_splits = (max_splits + SPLIT_BUCKET - 1) // SPLIT_BUCKET * SPLIT_BUCKET
+            total_splits = len(dec) * max_splits
         return {"decode_work": dec, "split_start": split_start, "prefill_work": pre.reshape(-1),
                 "n_decode": int(len(dec)), "n_prefill": int(pre.shape[0]),
-                "max_splits": int(splits.max()) if len(dec) else 0, "total_splits": int(split_start[-1])}
+                "max_splits": max_splits, "total_splits": total_splits}
 
     # ---------------------------------------------------------------- the step
     def forward(self, h, residual, ctx: StepContext, call: CallInfo):

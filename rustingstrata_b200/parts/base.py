@@ -85,6 +85,8 @@ class HostBatch:
     first_step: np.ndarray        # 1 where the sequence has no earlier tokens
     page_size: int
     max_blocks: List[int]         # per cache group: width of the block tables of this step
+    bucketed: bool = False        # the step may be captured in a CUDA graph: host scalars that become launch
+                                  # shapes must be rounded up to buckets so that later steps can replay it
 
 
 @dataclass

@@ -1,4 +1,4 @@
-"""The bfloat16 tensor-core matrix products (tcgen05 kernel and skinny kernel) against a float64
+"""The bfloat16 tensor-core matrix products (tcgen05 kernel and streaming skinny kernel) against a float64
 product of the same bfloat16 inputs, over many shapes: sizes that are no multiple of any tile, every
 epilogue, several tiles per CTA, tile widths 64/128/256."""
 import math
@@ -91,34 +91,51 @@ def test_refused_shapes_say_why_and_linear_falls_back():
     with pytest.raises(o.KernelError, match="16-byte aligned"):
         o.gemm_bf16_tc(a, w, out, 64)
     with pytest.raises(o.KernelError, match="16-byte aligned"):
-        o.gemv_bf16(a, w, out, 4)
+        o.skinny_gemm_bf16(a, w, out, 4)
     o.linear(a, w, out, 64)                                           # the CUDA-core kernel takes it
     assert err(out, a.double() @ w.double().T) < 6e-3
     a32 = torch.randn(64, 256, device=DEV)
     assert not o.tensor_core_shape_ok(a32, torch.randn(96, 256, device=DEV))
 
 
-@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 24, 25, 32])
-@pytest.mark.parametrize("N,K", [(16, 32), (100, 72), (4096, 4096), (6144, 4096), (1000, 1000), (24576, 4096),
-                                 (4096, 12288), (151936, 256)])
-def test_skinny_kernel(M, N, K):
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 31, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(64, 64), (100, 72), (4096, 4096), (6144, 4096), (1000, 1000), (24576, 4096),
+                                 (4096, 12288), (151936, 256), (70, 8)])
+def test_streaming_skinny_kernel(M, N, K):
     o = ops()
     a, w = make(M, N, K, cap=M + 2, seed=M)
     want = a[:M].double() @ w.double().T
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
     out = torch.full((M + 2, N), 3.0, device=DEV, dtype=torch.bfloat16)
-    o.gemv_bf16(a, w, out, M)
+    o.skinny_gemm_bf16(a, w, out, M, status=st)
     assert err(out[:M], want) < 6e-3 and torch.all(out[M:] == 3.0)
     f = torch.full((M + 2, N), 3.0, device=DEV)
-    o.gemv_bf16(a, w, f, M)
+    o.skinny_gemm_bf16(a, w, f, M, status=st)
     assert err(f[:M], want) < 1e-5
     base = torch.randn(M + 2, N, device=DEV)
     acc = base.clone()
-    o.gemv_bf16(a, w, acc, M, accumulate=True)
+    o.skinny_gemm_bf16(a, w, acc, M, accumulate=True, status=st)
     assert err(acc[:M], base[:M].double() + want) < 1e-5 and torch.equal(acc[M:], base[M:])
     if N % 2 == 0:
         sw = torch.zeros(M + 2, N // 2, device=DEV, dtype=torch.bfloat16)
-        o.gemv_bf16(a, w, sw, M, swiglu=True)
+        o.skinny_gemm_bf16(a, w, sw, M, swiglu=True, status=st)
         assert err(sw[:M], silu_mul(want)) < 8e-3 and torch.all(sw[M:] == 0)
+    assert st.item() == 0
+
+
+@pytest.mark.parametrize("max_ctas", [1, 2, 3, 7, 50, 147])
+def test_streaming_skinny_kernel_any_split_of_the_work(max_ctas):
+    """However the units are dealt to CTAs (row tiles shared by 2..many CTAs, CTAs spanning several tiles),
+    the result is the same product, and the same bits on a second run."""
+    o = ops()
+    for (M, N, K) in ((8, 320, 1024), (64, 200, 4096), (3, 4096, 640)):
+        a, w = make(M, N, K, seed=7)
+        want = a.double() @ w.double().T
+        f1 = torch.zeros(M, N, device=DEV)
+        f2 = torch.zeros(M, N, device=DEV)
+        o.skinny_gemm_bf16(a, w, f1, M, max_ctas=max_ctas)
+        o.skinny_gemm_bf16(a, w, f2, M, max_ctas=max_ctas)
+        assert err(f1, want) < 1e-5 and torch.equal(f1, f2)
 
 
 def test_skinny_and_tcgen05_agree_and_rows_do_not_depend_on_the_batch():
@@ -126,9 +143,9 @@ def test_skinny_and_tcgen05_agree_and_rows_do_not_depend_on_the_batch():
     a, w = make(32, 2048, 4096, seed=5)
     g = torch.zeros(32, 2048, device=DEV)
     t = torch.zeros(32, 2048, device=DEV)
-    o.gemv_bf16(a, w, g, 32)
+    o.skinny_gemm_bf16(a, w, g, 32)
     o.gemm_bf16_tc(a, w, t, 32)
     assert err(g, t.double()) < 2e-5                    # each is within 1e-5 of the exact product
     one = torch.zeros(1, 2048, device=DEV)
-    o.gemv_bf16(a[5:6].contiguous(), w, one, 1)
+    o.skinny_gemm_bf16(a[5:6].contiguous(), w, one, 1)
     assert torch.equal(one[0], g[5])                     # same k order whatever the batch
