@@ -16,9 +16,9 @@
 #include <math.h>
 
 namespace {
-constexpr int WARPS = 4;
+constexpr int WARPS = 8;
 constexpr int SPLIT = 128;             // keys per CTA; must equal the split size the host plans with
-constexpr int KEYS_PER_WARP = SPLIT / WARPS;   // 32: one 16-key block in each half of the split
+constexpr int KEYS_PER_WARP = SPLIT / WARPS;   // 16: warps 0-3 work on the first half of the split, 4-7 on the second
 
 struct DecodeParams {
     const __nv_bfloat16* q; long q_stride;
@@ -65,23 +65,22 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
     constexpr int HALF = SPLIT / 2;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-        for (int i = tid; i < HALF * CHUNKS; i += WARPS * 32) {
-            const int j = half * HALF + i / CHUNKS, c = i % CHUNKS;
-            const int kpos = k_base + j;
-            bool live = false;
-            if (j < n_keys && kpos >= key_lo) {
-                const int page = table[kpos / p.page_size];
-                if (page >= 0 && page < p.num_pages) {
-                    const __nv_bfloat16* src = p.cache + (size_t)page * p.page_stride +
-                                               ((size_t)kvh * p.page_size + (kpos % p.page_size)) * HD + c * 8;
-                    cp_async16(smem_addr(Ks + j * LD + c * 8), src);
-                    cp_async16(smem_addr(Vs + j * LD + c * 8), src + (size_t)p.n_kv * p.page_size * HD);
-                    live = true;
-                } else if (c == 0) {
-                    atomicOr(p.status, RS_STATUS_BAD_PAGE);
-                }
-            }
-            if (!live) {                              // masked keys still take part in the MMAs: keep them finite
+        // 256 threads, 64 key rows per half: 4 threads share a row, each taking a quarter of its chunks
+        const int j = half * HALF + (tid >> 2);
+        const int kpos = k_base + j;
+        const __nv_bfloat16* src = nullptr;
+        if (j < n_keys && kpos >= key_lo) {
+            const int page = table[kpos / p.page_size];
+            if (page >= 0 && page < p.num_pages)
+                src = p.cache + (size_t)page * p.page_stride + ((size_t)kvh * p.page_size + (kpos % p.page_size)) * HD;
+            else if ((tid & 3) == 0)
+                atomicOr(p.status, RS_STATUS_BAD_PAGE);
+        }
+        for (int c = (tid & 3); c < CHUNKS; c += 4) {
+            if (src != nullptr) {
+                cp_async16(smem_addr(Ks + j * LD + c * 8), src + c * 8);
+                cp_async16(smem_addr(Vs + j * LD + c * 8), src + (size_t)p.n_kv * p.page_size * HD + c * 8);
+            } else {                                  // masked keys still take part in the MMAs: keep them finite
                 *reinterpret_cast<uint4*>(Ks + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
                 *reinterpret_cast<uint4*>(Vs + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
             }
@@ -106,13 +105,12 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
 #pragma unroll
     for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
 
-#pragma unroll
-    for (int sub = 0; sub < KEYS_PER_WARP / 16; ++sub) {
-        // sub-block `sub` of a warp lies in half `sub` of the split: keys [sub * HALF + 16 warp, +16)
-        if (sub == 0) cp_async_wait<1>(); else cp_async_wait<0>();
-        __syncthreads();
-        const int j0 = sub * HALF + warp * 16;                  // first key row of this 16-key block
-        if (k_base + j0 >= key_hi) continue;                    // uniform per warp; later barriers are still reached
+    cp_async_wait<0>();
+    __syncthreads();                                            // the whole split has landed
+    {
+        const int j0 = warp * 16;                               // first key row of this warp's 16-key block
+        const bool warp_has_keys = k_base + j0 < key_hi;
+        if (warp_has_keys) {
         float s[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
@@ -177,7 +175,9 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
             mma16816(o[d], pf, v00, v01);
             mma16816(o[d + 1], pf, v10, v11);
         }
+        }
     }
+    cp_async_wait<0>();
 
     // ---- combine the warps: (max, sum, O) of each warp → shared memory, then one partial per head
     __syncthreads();                                            // everyone is done reading K and V
