@@ -60,28 +60,33 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
     const int blk_lo = key_lo / BKV, blk_hi = (key_hi + BKV - 1) / BKV;
     const int* table = p.block_table + (size_t)seq * p.table_stride;
 
+    // 128 threads, 64 key rows per block: two threads share a row (one page lookup each), each copies half of its chunks
     auto load_block = [&](int blk, int stage) {
-        __nv_bfloat16* kd = Ks + stage * BKV * LD;
-        __nv_bfloat16* vd = Vs + stage * BKV * LD;
-        for (int i = tid; i < BKV * CHUNKS; i += WARPS * 32) {
-            const int j = i / CHUNKS, c = i % CHUNKS;
-            const int kpos = blk * BKV + j;
-            bool live = false;
-            if (kpos >= key_lo && kpos < key_hi) {
-                const int page = table[kpos / p.page_size];
-                if (page >= 0 && page < p.num_pages) {
-                    const __nv_bfloat16* src = p.cache + (size_t)page * p.page_stride +
-                                               ((size_t)kvh * p.page_size + (kpos % p.page_size)) * HD + c * 8;
-                    cp_async16(smem_addr(kd + j * LD + c * 8), src);
-                    cp_async16(smem_addr(vd + j * LD + c * 8), src + (size_t)p.n_kv * p.page_size * HD);
-                    live = true;
-                } else if (c == 0) {
-                    atomicOr(p.status, RS_STATUS_BAD_PAGE);
-                }
+        const int j = tid >> 1;
+        __nv_bfloat16* kd = Ks + stage * BKV * LD + j * LD;
+        __nv_bfloat16* vd = Vs + stage * BKV * LD + j * LD;
+        const int kpos = blk * BKV + j;
+        const __nv_bfloat16* src = nullptr;
+        if (kpos >= key_lo && kpos < key_hi) {
+            const int page = table[kpos / p.page_size];
+            if (page >= 0 && page < p.num_pages)
+                src = p.cache + (size_t)page * p.page_stride + ((size_t)kvh * p.page_size + (kpos % p.page_size)) * HD;
+            else if ((tid & 1) == 0)
+                atomicOr(p.status, RS_STATUS_BAD_PAGE);
+        }
+        const int c0 = (tid & 1) * (CHUNKS / 2);
+        if (src != nullptr) {
+            const __nv_bfloat16* vsrc = src + (size_t)p.n_kv * p.page_size * HD;
+#pragma unroll
+            for (int c = 0; c < CHUNKS / 2; ++c) {
+                cp_async16(smem_addr(kd + (c0 + c) * 8), src + (c0 + c) * 8);
+                cp_async16(smem_addr(vd + (c0 + c) * 8), vsrc + (c0 + c) * 8);
             }
-            if (!live) {
-                *reinterpret_cast<uint4*>(kd + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(vd + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
+        } else {
+#pragma unroll
+            for (int c = 0; c < CHUNKS / 2; ++c) {
+                *reinterpret_cast<uint4*>(kd + (c0 + c) * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd + (c0 + c) * 8) = make_uint4(0, 0, 0, 0);
             }
         }
         cp_async_commit();

@@ -96,7 +96,7 @@ def bench_decode_attention(B, S, n_q, n_kv, hd, page, iters, once):
 def bench_prefill_attention(S, n_q, n_kv, hd, page, iters, once):
     caches, common, d = paged_problem(1, S, S, n_q, n_kv, hd, page, 1)
     qpc = ops.attention_prefill_q_per_cta(torch.bfloat16, n_q, n_kv, hd)
-    tiles = np.array([(0, o) for o in range(0, S, qpc)], np.int32).reshape(-1)
+    tiles = np.array([(0, o) for o in range(0, S, qpc)][::-1], np.int32).reshape(-1)     # longest first, as the mixer plans
     args = dict(work=d(tiles), n_work=len(tiles) // 2, **common)
     us = timed(lambda i: ops.attention_prefill(cache=caches[0], **args), 1, iters, once)
     print(f"prefill_attention S={S} heads {n_q}/{n_kv} hd={hd}: {us:.1f} us, {4.0 * n_q * hd * S * S / 2 / us / 1e6:.1f} "

@@ -124,6 +124,10 @@ class PagedAttention(Mixer):
             offs = np.arange(0, batch.q_lens[s], qpc, dtype=np.int32)
             tiles.append(np.stack([np.full_like(offs, s), offs], axis=1))
         pre = np.concatenate(tiles, axis=0).astype(np.int32) if tiles else np.zeros((0, 2), np.int32)
+        if len(pre) > 1:
+            # tiles with the most keys to walk first: the last wave of CTAs then holds the short ones
+            last_pos = batch.kv_lens[pre[:, 0]] - batch.q_lens[pre[:, 0]] + pre[:, 1]
+            pre = pre[np.argsort(-last_pos, kind="stable")]
         max_splits = int(splits.max()) if len(dec) else 0
         total_splits = int(split_start[-1])
         if batch.bucketed and len(dec):
