@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m_run[r], mx[r]);
-            corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new);
+            corr[r] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[r] - m_new);
             m_run[r] = m_new;
         }
         float rs[2] = {0.f, 0.f};
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float mm = m_run[i >> 1];
-                e[i] = (mm == -INFINITY) ? 0.f : exp2f(s[nt][i] - mm);
+                e[i] = (mm == -INFINITY) ? 0.f : fast_exp2(s[nt][i] - mm);
                 rs[i >> 1] += e[i];
             }
             pf[2 * nt] = pack_bf16(e[0], e[1]);         // a0 / a2: row g
@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const Deco
 #pragma unroll
             for (int ww = 0; ww < WARPS; ++ww) {
                 const float mw = Os[((size_t)ww * 16 + r) * OLD + HD];
-                const float e = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+                const float e = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
                 val += Os[((size_t)ww * 16 + r) * OLD + (d < HD ? d : HD + 1)] * e;
             }
         }
@@ -237,7 +237,7 @@ __global__ void decode_merge_kernel(const DecodeParams p) {
         float num = 0.f, den = 0.f;
         for (int s = 0; s < n_splits; ++s) {
             const float* ps = base + s * stride;
-            const float e = exp2f(ld_dep(ps + HD) - M);
+            const float e = fast_exp2(ld_dep(ps + HD) - M);
             num = fmaf(ld_dep(ps + d), e, num);
             den = fmaf(ld_dep(ps + HD + 1), e, den);
         }

@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new);
+                corr[r] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[r] - m_new);
                 m_run[r] = m_new;
             }
             float rs[2] = {0.f, 0.f};
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float mm = m_run[i >> 1];
-                    e[i] = (mm == -INFINITY) ? 0.f : exp2f(s[nt][i] - mm);
+                    e[i] = (mm == -INFINITY) ? 0.f : fast_exp2(s[nt][i] - mm);
                     rs[i >> 1] += e[i];
                 }
                 pf[nt >> 1][(nt & 1) * 2] = pack_bf16(e[0], e[1]);

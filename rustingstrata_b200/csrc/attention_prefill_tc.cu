@@ -1,0 +1,440 @@
+// Attention of prompt portions on the 5th-generation tensor cores (sm_100a), head sizes 64 and 128.
+//
+// A CTA owns 128 rows; a row is (query token, query head) with P heads of one kv group packed side by side,
+// so a key/value tile in shared memory serves P heads.  Keys are walked in blocks of 128 at absolute
+// positions.  Per block
+//   S = Q K^T      tcgen05.mma, Q (128 x hd) and the K block (128 keys x hd) both K-major in shared memory
+//                  (TMA, 128-byte swizzle, one box per cache page and 64-wide half of the head), S in tensor memory;
+//   softmax        eight warps, two threads per row (each half of the block's keys): tcgen05.ld the scores, mask
+//                  (causal, window, length), running max and sum in float32 with exp2, P rounded to bfloat16 and
+//                  written back over S with tcgen05.st (two values per 32-bit column);
+//   O_blk = P V    tcgen05.mma with P as the tensor-memory operand and the V block (keys x hd, hd contiguous =
+//                  MN-major) in shared memory; the row's thread adds O_blk into its float32 accumulator, scaled
+//                  by the change of the running max.
+// Warp 8 issues the MMAs (one elected lane) and owns the tensor-memory allocation, warp 9 issues the TMA loads.
+// S is double buffered, so Q K^T of the next block runs under the softmax of this one.  Every mbarrier wait is
+// bounded (tma_helpers.cuh).  Cache pages a block does not own (beyond the sequence, given back by a window)
+// are replaced by page 0: their keys are masked, and their values only have to be finite.
+//
+// Reference counterpart: attn_prefill_* (src/cuda/kernels.cu:2813-3156), an mma.sync kernel with f16 inputs.
+#include "tma_helpers.cuh"
+#include <math.h>
+
+namespace {
+constexpr int ROWS = 128;              // rows per CTA = TMEM lanes
+constexpr int BKV = 128;               // keys per block
+constexpr int THREADS = 320;             // warps 0-7 softmax, warp 8 MMA issuer, warp 9 TMA producer
+constexpr int KV_STAGES = 2;
+
+struct TcParams {
+    __nv_bfloat16* out; long out_stride;
+    int page_size, num_pages;
+    const int* block_table; int table_stride;
+    const int* q_start; const int* kv_len; const int* work;
+    int n_q, n_kv, group, pack, tokens_per_cta;
+    int window;
+    float scale_log2;
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// MN-major operand tile (the contiguous direction is N), 128-byte swizzle: 64 elements of N contiguous per row of
+// 128 bytes, 8 rows of K per 1024-byte group (stride byte offset), blocks of 64 N-elements `lbo` bytes apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams p) {
+    constexpr int HALVES = HD / 64;                      // 64-wide (128-byte) column blocks of a head
+    constexpr int HALF_BYTES = 128 * 128;                // 128 rows x 128 bytes
+    constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // one Q, K or V tile
+    constexpr int TMEM_COLS = 512;                       // S0 | S1 | O0 | O1  (128 + 128 + 2 * HD columns)
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t q_smem = base, k_smem = base + TILE_BYTES, v_smem = k_smem + KV_STAGES * TILE_BYTES;
+    const uint32_t bar0 = v_smem + KV_STAGES * TILE_BYTES;
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full, o_free
+    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_FULL = 13, O_FREE = 15, NBAR = 17 };
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+    uint8_t* aligned = smem_raw + (base - raw);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xchg = reinterpret_cast<float*>(tmem_slot + 4);     // [2 blocks parity][2 halves][ROWS] maxima, then [2][ROWS] sums
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = p.work[2 * blockIdx.x], q_off = p.work[2 * blockIdx.x + 1];
+    const int chunks_per_group = p.group / p.pack;
+    const int kvh = blockIdx.y / chunks_per_group;
+    const int head0 = kvh * p.group + (blockIdx.y % chunks_per_group) * p.pack;
+    const int row0 = p.q_start[seq];
+    const int q_len = p.q_start[seq + 1] - row0;
+    const int kv_len = p.kv_len[seq];
+    const int n_tok = min(p.tokens_per_cta, q_len - q_off);
+    const int n_rows = n_tok * p.pack;
+    const int qpos0 = kv_len - q_len + q_off;
+    const int key_lo = p.window > 0 ? max(0, qpos0 - p.window + 1) : 0;
+    const int key_hi = min(kv_len, qpos0 + n_tok);
+    const int blk_lo = key_lo / BKV, blk_hi = (key_hi + BKV - 1) / BKV;
+    const int n_blocks = blk_hi - blk_lo;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1);
+            mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1);
+            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), 8);
+            mbar_init(bar(O_FULL + s), 1); mbar_init(bar(O_FREE + s), 8);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 9) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_3d(q_smem + h * HALF_BYTES, &map_q, h * 64, head0, row0 + q_off, bar(Q_FULL));
+            const int* table = p.block_table + (size_t)seq * p.table_stride;
+            const int pages_per_block = BKV / p.page_size;
+            bool ok = true;
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t par = ((j >> 1) & 1) ^ 1u;
+                const int k0 = (blk_lo + j) * BKV;
+                for (int kv = 0; kv < 2 && ok; ++kv) {
+                    if (!mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status)) { ok = false; break; }
+                    const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
+                    mbar_expect_tx(full, TILE_BYTES);
+                    const uint32_t dst = (kv ? v_smem : k_smem) + s * TILE_BYTES;
+                    for (int pg = 0; pg < pages_per_block; ++pg) {
+                        const int kpos = k0 + pg * p.page_size;
+                        int page = 0;
+                        if (kpos < key_hi && kpos + p.page_size > key_lo) {
+                            page = table[kpos / p.page_size];
+                            if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
+                        }
+                        const int row = ((page * 2 + kv) * p.n_kv + kvh) * p.page_size;
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h)
+                            tma_load_2d(dst + h * HALF_BYTES + pg * p.page_size * 128, &map_kv, h * 64, row, full);
+                    }
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_blocks > 0) {
+            const uint32_t idesc_qk = idesc_bf16(ROWS, BKV, 0), idesc_pv = idesc_bf16(ROWS, HD, 1);
+            bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, p.status);
+            auto issue_qk = [&](int j) {
+                const int s = j & 1;
+                if (!mbar_wait(bar(K_FULL + s), (j >> 1) & 1, abort_flag, p.status)) return false;
+                tc_fence_after();
+                const uint32_t d = tmem_base + s * 128;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+                    umma_ss(d, desc_kmajor(q_smem + off), desc_kmajor(k_smem + s * TILE_BYTES + off), idesc_qk, ks ? 1u : 0u);
+                }
+                umma_commit(bar(K_EMPTY + s));           // the K stage is free once these have read it
+                umma_commit(bar(S_FULL + s));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int s = j & 1;
+                if (j + 1 < n_blocks) ok = issue_qk(j + 1);
+                if (!ok) break;
+                if (!mbar_wait(bar(P_READY + s), (j >> 1) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(bar(O_FREE + s), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk)
+                    umma_ts(tmem_base + 256 + s * HD, tmem_base + s * 128 + kk * 8,
+                            desc_mnmajor(v_smem + s * TILE_BYTES + kk * 16 * 128, HALF_BYTES), idesc_pv, kk ? 1u : 0u);
+                umma_commit(bar(V_EMPTY + s));
+                umma_commit(bar(O_FULL + s));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps 0..7: two threads per row
+        // warps w and w + 4 own the same 32 rows (tensor-memory lanes 32 (w & 3) ..): the first takes the keys
+        // [0, 64) of a block and the head dims [0, hd/2) of O, the second the other halves.  The two exchange
+        // their row maxima through shared memory once per block; their partial sums meet at the end.
+        constexpr int HK = BKV / 2, HO = HD / 2;
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int qpos = qpos0 + r / p.pack;
+        float m_run = -INFINITY, l_run = 0.f;
+        float o_acc[HO];
+#pragma unroll
+        for (int d = 0; d < HO; ++d) o_acc[d] = 0.f;
+        bool ok = true;
+        float corr_prev = 1.f;
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
+        // O_blk of block j is added one block late (with the scale of its own block), so the P V product of
+        // block j runs under the softmax of block j + 1
+        auto add_o = [&](int j, float corr) {
+            const int s = j & 1;
+            if (!mbar_wait(bar(O_FULL + s), (j >> 1) & 1, abort_flag, p.status)) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HO; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(lane_base + 256 + s * HD + half * HO + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], corr, __uint_as_float(v[i]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(O_FREE + s));
+            return true;
+        };
+        for (int j = 0; j < n_blocks && ok; ++j) {
+            const int s = j & 1;
+            const int k0 = (blk_lo + j) * BKV + half * HK;           // first key of this thread's half block
+            if (!mbar_wait(bar(S_FULL + s), (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t s_addr = lane_base + s * 128 + half * HK;
+            const int kb0 = (blk_lo + j) * BKV;
+            const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
+                                   (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
+            // the row's scores of this half block, once, into registers (scaled to log2 units, masked)
+            float x[HK];
+#pragma unroll
+            for (int c = 0; c < HK; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(s_addr + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x[c + i] = __uint_as_float(v[i]) * p.scale_log2;
+            }
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < HK; ++i) {
+                    const int kpos = k0 + i;
+                    const bool vis = kpos <= qpos && kpos < key_hi && kpos >= key_lo && (p.window <= 0 || kpos > qpos - p.window);
+                    x[i] = vis ? x[i] : -INFINITY;
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < HK; i += 4) {
+                mx0 = fmaxf(mx0, x[i]); mx1 = fmaxf(mx1, x[i + 1]); mx2 = fmaxf(mx2, x[i + 2]); mx3 = fmaxf(mx3, x[i + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            xchg[((j & 1) * 2 + half) * ROWS + r] = mx;
+            pair_sync();
+            const float m_new = fmaxf(m_run, fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * ROWS + r]));
+            const float corr = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run - m_new);
+            m_run = m_new;
+            // P = 2^(x - m), its sum, and P as bfloat16 pairs written over S
+            const float sub = (m_new == -INFINITY) ? 0.f : m_new;     // all keys masked so far: every x is -inf, P = 0
+            float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < HK; c += 32) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float e0 = fast_exp2(x[c + i] - sub), e1 = fast_exp2(x[c + i + 1] - sub);
+                    rs0 += e0; rs1 += e1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
+                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                tmem_st16(lane_base + s * 128 + ((half * HK + c) >> 1), pk);
+            }
+            tmem_st_wait();
+            l_run = l_run * corr + (rs0 + rs1);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(P_READY + s));
+            if (j > 0) ok = add_o(j - 1, corr_prev);
+            corr_prev = corr;
+        }
+        if (ok) ok = add_o(n_blocks - 1, corr_prev);
+        // the row's sum: both halves saw the same maxima, so their partial sums simply add
+        xchg[(4 + half) * ROWS + r] = l_run;
+        pair_sync();
+        l_run += xchg[(4 + (half ^ 1)) * ROWS + r];
+        if (ok && r < n_rows) {
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + q_off + r / p.pack) * p.out_stride + (size_t)(head0 + r % p.pack) * HD +
+                                 half * HO;
+#pragma unroll
+            for (int d = 0; d < HO; d += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    __nv_bfloat162 b = __floats2bfloat162_rn(o_acc[d + 2 * u] * inv, o_acc[d + 2 * u + 1] * inv);
+                    w[u] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+__host__ __device__ inline int pack_of(int group) {
+    int p = 1;
+    while (p < 16 && group % (2 * p) == 0) p *= 2;
+    return p;
+}
+
+// 3-D map of the query part of the projection buffer: (head dim, head, token), box 64 x pack x (128 / pack).
+int q_map(const void* q, long q_stride, long tokens, int n_q, int hd, int pack, CUtensorMap* out) {
+    using namespace rs_tma;
+    EncodeTiledFn enc = get_encoder();
+    if (!enc) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)n_q, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)pack, (cuuint32_t)(ROWS / pack)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+struct QMapKey { const void* q; long stride, tokens; int n_q, hd, pack; };
+std::vector<std::pair<QMapKey, CUtensorMap>> g_qmaps;
+std::mutex g_qmaps_mutex;
+
+int cached_q_map(const void* q, long q_stride, long tokens, int n_q, int hd, int pack, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_qmaps_mutex);
+    for (auto& e : g_qmaps)
+        if (e.first.q == q && e.first.stride == q_stride && e.first.tokens == tokens && e.first.n_q == n_q && e.first.hd == hd &&
+            e.first.pack == pack) { *out = e.second; return 0; }
+    CUtensorMap m;
+    int rc = q_map(q, q_stride, tokens, n_q, hd, pack, &m);
+    if (rc) return rc;
+    if (g_qmaps.size() > 64) g_qmaps.clear();
+    g_qmaps.push_back({QMapKey{q, q_stride, tokens, n_q, hd, pack}, m});
+    *out = m;
+    return 0;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int n_work, cudaStream_t s) {
+    constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 17 + 64 + 6 * ROWS * 4;
+    auto kern = prefill_attention_tc_kernel<HD>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    kern<<<dim3(n_work, p.n_kv * (p.group / p.pack)), THREADS, smem, s>>>(mq, mkv, p);
+    return rs_launch_result();
+}
+}  // namespace
+
+RS_EXPORT int rs_attention_prefill_tc_supported(int n_q, int n_kv, int hd, int page_size) {
+    if (n_kv <= 0 || n_q % n_kv) return 0;
+    if (hd != 64 && hd != 128) return 0;
+    return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+}
+
+// Query tokens per CTA: the host cuts each sequence's queries into tiles of this many.
+RS_EXPORT int rs_attention_prefill_tc_q_per_cta(int n_q, int n_kv) { return ROWS / pack_of(n_q / n_kv); }
+
+// q: the projection buffer [q_rows, q_stride] whose first n_q * hd columns of every row are the queries.
+RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows, void* out, long out_stride, const void* cache,
+                                      long page_stride, int num_pages, int page_size, const int* block_table,
+                                      int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
+                                      int n_q, int n_kv, int hd, int window, float scale, int* status, void* stream) {
+    if (n_work <= 0) return 0;
+    if (!rs_attention_prefill_tc_supported(n_q, n_kv, hd, page_size) || (q_stride % 8) || (out_stride % 8) || ((long)q & 15) ||
+        ((long)out & 15) || ((long)cache & 15) || page_stride != (long)2 * n_kv * page_size * hd)
+        return (int)cudaErrorInvalidValue;
+    TcParams p;
+    p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.page_size = page_size; p.num_pages = num_pages;
+    p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
+    p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.pack = pack_of(p.group); p.tokens_per_cta = ROWS / p.pack;
+    p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    CUtensorMap mq, mkv;
+    int rc = cached_q_map(q, q_stride, q_rows, n_q, hd, p.pack, &mq);
+    if (rc) return rc;
+    rc = rs_tma::get_map(cache, (long)num_pages * 2 * n_kv * page_size, hd, hd, page_size, &mkv);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64) return launch<64>(mq, mkv, p, n_work, s);
+    return launch<128>(mq, mkv, p, n_work, s);
+}

@@ -34,6 +34,14 @@ __device__ __forceinline__ float load_any(const void* p, int dt, size_t i) {
                         : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
 
+// 2^x on the special-function unit (ex2.approx.ftz): one instruction, no range branches.  Its relative error
+// (2^-22) is far below the bfloat16 rounding of the probabilities it feeds; exp2f() compiles to branchy code.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 constexpr unsigned long long RS_WAIT_LIMIT_NS = 2000000000ull;
 constexpr int RS_TMA_BOX_K = 64;          // 64 bf16 = 128 bytes = one swizzle row

@@ -93,13 +93,14 @@ def bench_decode_attention(B, S, n_q, n_kv, hd, page, iters, once):
     print(f"decode_attention B={B} S={S} heads {n_q}/{n_kv} hd={hd}: {us:.1f} us, cache {byts / us / 1e6:.2f} TB/s")
 
 
-def bench_prefill_attention(S, n_q, n_kv, hd, page, iters, once):
+def bench_prefill_attention(S, n_q, n_kv, hd, page, iters, once, force=""):
     caches, common, d = paged_problem(1, S, S, n_q, n_kv, hd, page, 1)
-    qpc = ops.attention_prefill_q_per_cta(torch.bfloat16, n_q, n_kv, hd)
+    qpc = ops.attention_prefill_q_per_cta(torch.bfloat16, n_q, n_kv, hd, page, force)
     tiles = np.array([(0, o) for o in range(0, S, qpc)][::-1], np.int32).reshape(-1)     # longest first, as the mixer plans
     args = dict(work=d(tiles), n_work=len(tiles) // 2, **common)
-    us = timed(lambda i: ops.attention_prefill(cache=caches[0], **args), 1, iters, once)
-    print(f"prefill_attention S={S} heads {n_q}/{n_kv} hd={hd}: {us:.1f} us, {4.0 * n_q * hd * S * S / 2 / us / 1e6:.1f} "
+    us = timed(lambda i: ops.attention_prefill(cache=caches[0], force=force, **args), 1, iters, once)
+    kind = ops.attention_prefill_kernel(torch.bfloat16, n_q, n_kv, hd, page, force)
+    print(f"prefill_attention [{kind}] S={S} heads {n_q}/{n_kv} hd={hd}: {us:.1f} us, {4.0 * n_q * hd * S * S / 2 / us / 1e6:.1f} "
           f"TFLOP/s (causal half counted)")
 
 
@@ -120,6 +121,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--iters", type=int, default=40)
+    ap.add_argument("--force", default="", help="prefill_attention: tc | mma | simt instead of the default choice")
     ap.add_argument("--once", action="store_true", help="a few plain launches, no graph and no timing (for profilers)")
     a = ap.parse_args(argv)
     if a.kernel in ("skinny", "gemm"):
@@ -127,7 +129,7 @@ def main(argv=None) -> int:
     elif a.kernel == "decode_attention":
         bench_decode_attention(a.batch, a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size, a.iters, a.once)
     elif a.kernel == "prefill_attention":
-        bench_prefill_attention(a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size, a.iters, a.once)
+        bench_prefill_attention(a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size, a.iters, a.once, a.force)
     elif a.kernel == "rmsnorm":
         x = torch.randn(a.m, a.k, device=DEV)
         w = torch.ones(a.k, device=DEV, dtype=torch.bfloat16)

@@ -237,6 +237,11 @@ def bf16lib():
         lib.rs_attention_prefill_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                   c_int, c_int, c_float, c_void_p, c_void_p]
+        lib.rs_attention_prefill_tc.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
+                                                c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                c_int, c_float, c_void_p, c_void_p]
+        lib.rs_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
+        lib.rs_attention_prefill_tc_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_attention_prefill_bf16_supported.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16_q_per_cta.argtypes = [c_int, c_int]
         _bf16 = lib
@@ -407,14 +412,31 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
         _ptr(status), _stream()), "attention_simt")
 
 
+def attention_prefill_kernel(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int, force: str = "") -> str:
+    """Which kernel ``attention_prefill`` runs for this shape: "tc" (tcgen05, head 64/128, page size a power of
+    two from 8 to 128), "mma" (mma.sync, head 32/64/96/128) or "simt" (everything else, and float32)."""
+    if force:
+        return force
+    if dtype == torch.bfloat16:
+        if bf16lib().rs_attention_prefill_tc_supported(n_q, n_kv, head_dim, page_size):
+            return "tc"
+        if bf16lib().rs_attention_prefill_bf16_supported(n_q, n_kv, head_dim):
+            return "mma"
+    return "simt"
+
+
 def attention_prefill_fast_ok(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
-    """Whether the tensor-core portion kernel takes this shape (bfloat16, head size 32/64/96/128)."""
+    """Whether a tensor-core portion kernel takes this shape (bfloat16, head size 32/64/96/128)."""
     return dtype == torch.bfloat16 and bool(bf16lib().rs_attention_prefill_bf16_supported(n_q, n_kv, head_dim))
 
 
-def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, force_simt: bool = False) -> int:
+def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int = 16,
+                                force: str = "") -> int:
     """Query tokens per work item of the portion form, for the kernel ``attention_prefill`` will pick."""
-    if not force_simt and attention_prefill_fast_ok(dtype, n_q, n_kv, head_dim):
+    kind = attention_prefill_kernel(dtype, n_q, n_kv, head_dim, page_size, force)
+    if kind == "tc":
+        return int(bf16lib().rs_attention_prefill_tc_q_per_cta(n_q, n_kv))
+    if kind == "mma":
         return int(bf16lib().rs_attention_prefill_bf16_q_per_cta(n_q, n_kv))
     return attention_q_per_cta(n_q, n_kv)
 
@@ -422,23 +444,31 @@ def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_di
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                       head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor,
-                      force_simt: bool = False) -> None:
+                      force: str = "") -> None:
     """Attention of prompt portions; ``work`` lists (sequence, first query) tiles of ``attention_prefill_q_per_cta``
-    tokens.  The tensor-core kernel (csrc/attention_prefill_mma.cu) where it takes the shape, else CUDA cores."""
-    if force_simt or not attention_prefill_fast_ok(q.dtype, n_q, n_kv, head_dim):
+    tokens.  tcgen05 kernel (csrc/attention_prefill_tc.cu), mma.sync kernel (csrc/attention_prefill_mma.cu) or
+    CUDA cores, whichever takes the shape; ``force`` names one."""
+    kind = attention_prefill_kernel(q.dtype, n_q, n_kv, head_dim, page_size, force)
+    if kind == "simt":
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, False, status)
         return
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
-    if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not cache.is_contiguous():
+    if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or not cache.is_contiguous():
         raise KernelError("attention_prefill: q, out and cache must be bfloat16 and the cache contiguous")
     if tuple(cache.shape[1:]) != (2, n_kv, page_size, head_dim):
         raise KernelError(f"attention_prefill: cache shape {tuple(cache.shape)} is not [pages, 2, {n_kv}, {page_size}, {head_dim}]")
     for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
         if t.dtype != torch.int32:
             raise KernelError(f"attention_prefill: {name} must be int32")
+    if kind == "tc":
+        _check(bf16lib().rs_attention_prefill_tc(
+            _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0],
+            page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv,
+            head_dim, int(window), float(scale), _ptr(status), _stream()), "attention_prefill_tc")
+        return
     _check(bf16lib().rs_attention_prefill_bf16(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
         _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv, head_dim,

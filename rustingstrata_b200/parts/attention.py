@@ -108,7 +108,8 @@ class PagedAttention(Mixer):
     # ---------------------------------------------------------------- planning
     def plan_key(self):
         if self.q_per_cta is None:
-            self.q_per_cta = ops.attention_prefill_q_per_cta(self.runtime.dtype, self.n_heads, self.n_kv, self.hd)
+            self.q_per_cta = ops.attention_prefill_q_per_cta(self.runtime.dtype, self.n_heads, self.n_kv, self.hd,
+                                                              self.runtime.page_size)
         return ("paged_attention", self.q_per_cta, self.window)
 
     def build_plan(self, batch: HostBatch):

@@ -211,7 +211,7 @@ def ref_attention(q, keys, vals, q_pos, n_kv, window, scale):
     return out
 
 
-def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=None, force_simt=False):
+def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=None, force_simt=False, prefill=""):
     """seqs: list of (kv_len, q_len).  Builds a shuffled paged cache, runs the kernels the mixer would
     run (split form for one query, tile form otherwise) and returns (got, want) [T, n_q, hd]."""
     o = ops()
@@ -243,7 +243,8 @@ def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=
     q_start = np.zeros(S + 1, np.int32)
     q_start[1:] = np.cumsum(q_lens)
     from rustingstrata_b200.parts.attention import SPLIT_KEYS, decode_splits
-    qpc = o.attention_prefill_q_per_cta(dtype, n_q, n_kv, hd, force_simt=force_simt)
+    prefill = "simt" if force_simt else prefill
+    qpc = o.attention_prefill_q_per_cta(dtype, n_q, n_kv, hd, page, prefill)
     dec = np.nonzero(q_lens == 1)[0].astype(np.int32)
     tiles = [(s, off) for s in np.nonzero(q_lens != 1)[0] for off in range(0, q_lens[s], qpc)]
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)  # noqa: E731
@@ -251,7 +252,7 @@ def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=
     common = dict(q=qd, out=out, cache=cache, block_table=perm.to(DEV), q_start=dev(q_start), kv_len=dev(kv_lens),
                   n_q=n_q, n_kv=n_kv, head_dim=hd, page_size=page, window=window, scale=scale, status=st)
     if tiles:
-        o.attention_prefill(work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), force_simt=force_simt, **common)
+        o.attention_prefill(work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), force=prefill, **common)
     if len(dec):
         splits = decode_splits(kv_lens[dec], window)
         ss = np.zeros(len(dec) + 1, np.int32)
@@ -329,11 +330,25 @@ def test_prefill_tensor_core_kernel_agrees_with_the_cuda_core_kernel(n_q, n_kv, 
     assert o.attention_prefill_fast_ok(torch.bfloat16, n_q, n_kv, hd) and not o.attention_prefill_fast_ok(torch.float32, n_q, n_kv, hd)
     seqs = [(37, 37), (300, 2), (65, 20), (64, 64), (129, 128), (200, 33), (128, 2), (700, 257), (2, 2), (1000, 3)]
     torch.manual_seed(4)
-    fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window)
+    fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, prefill="mma")
     torch.manual_seed(4)
     slow, _ = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, force_simt=True)
     close(fast, want, 1.5e-2)
     close(fast, slow.double().cpu(), 1.5e-2)
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (16, 1, 64, 8), (10, 2, 64, 16), (3, 3, 128, 32),
+                                              (4, 1, 64, 128)])
+@pytest.mark.parametrize("window", [0, 70, 200])
+def test_prefill_tcgen05_kernel(n_q, n_kv, hd, page, window):
+    from rustingstrata_b200.kernels import ops as o
+    assert o.attention_prefill_kernel(torch.bfloat16, n_q, n_kv, hd, page) == "tc"
+    assert o.attention_prefill_kernel(torch.bfloat16, n_q, n_kv, hd, 4) == "mma"
+    assert o.attention_prefill_kernel(torch.float32, n_q, n_kv, hd, page) == "simt"
+    seqs = [(37, 37), (300, 2), (65, 20), (128, 128), (129, 128), (200, 33), (256, 2), (700, 257), (2, 2), (1000, 3), (513, 200)]
+    torch.manual_seed(6)
+    fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, prefill="tc")
+    close(fast, want, 1.5e-2)
 
 
 def test_attention_refuses_unsupported_sizes():
