@@ -56,9 +56,62 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, long x_stride, const
     for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(ld_dep(xr + i) * s * load_any(w, w_dt, i));
 }
 
+// The same for a bfloat16 output when the row fits the block's registers (n <= 512 * 4 * VPT, n % 4 == 0, 16-byte
+// aligned rows): one read of x with float4 loads, the row kept in registers between the sum and the scaling.
+template <int VPT>
+__global__ void __launch_bounds__(512) rmsnorm_bf16_vec_kernel(const float* x, long x_stride, const int* __restrict__ rows,
+                                                               const void* __restrict__ w, int w_dt, float eps,
+                                                               __nv_bfloat16* __restrict__ out, long out_stride, int n) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * x_stride);
+    const int n4 = n >> 2;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = threadIdx.x + u * 512;
+        v[u] = i < n4 ? ld_dep(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss); ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float s = 1.0f / sqrtf(ss / (float)n + eps);
+    __nv_bfloat16* o = out + (size_t)r * out_stride;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = threadIdx.x + u * 512;
+        if (i < n4) {
+            float w0, w1, w2, w3;
+            if (w_dt == RS_F32) {
+                const float4 wv = reinterpret_cast<const float4*>(w)[i];
+                w0 = wv.x; w1 = wv.y; w2 = wv.z; w3 = wv.w;
+            } else {
+                const uint2 wv = reinterpret_cast<const uint2*>(w)[i];
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&wv.x), b = *reinterpret_cast<const __nv_bfloat162*>(&wv.y);
+                w0 = __low2float(a); w1 = __high2float(a); w2 = __low2float(b); w3 = __high2float(b);
+            }
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * s * w0, v[u].y * s * w1);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * s * w2, v[u].w * s * w3);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(o)[i] = pk;
+        }
+    }
+}
+
 RS_EXPORT int rs_rmsnorm(const float* x, long x_stride, const int* rows, const void* w, int w_dt, float eps,
                          void* out, int out_dt, long out_stride, int n_rows, int n, void* stream) {
     if (n_rows <= 0) return 0;
+    if (out_dt == RS_BF16 && n % 4 == 0 && n <= 512 * 4 * 4 && x_stride % 4 == 0 && out_stride % 4 == 0 && ((long)x & 15) == 0 &&
+        ((long)out & 7) == 0 && ((long)w & 15) == 0) {
+        auto* o = (__nv_bfloat16*)out;
+        cudaStream_t s = (cudaStream_t)stream;
+        if (n <= 512 * 4) return rs_launch_pdl(rmsnorm_bf16_vec_kernel<1>, dim3(n_rows), dim3(512), 0, s, x, x_stride, rows, w, w_dt, eps, o, out_stride, n);
+        if (n <= 512 * 8) return rs_launch_pdl(rmsnorm_bf16_vec_kernel<2>, dim3(n_rows), dim3(512), 0, s, x, x_stride, rows, w, w_dt, eps, o, out_stride, n);
+        return rs_launch_pdl(rmsnorm_bf16_vec_kernel<4>, dim3(n_rows), dim3(512), 0, s, x, x_stride, rows, w, w_dt, eps, o, out_stride, n);
+    }
     const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
     RS_DISPATCH_DTYPE(out_dt, TO,
         return rs_launch_pdl(rmsnorm_kernel<TO>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x, x_stride, rows, w,
@@ -136,6 +189,82 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int
     }
 }
 
+// bfloat16 fast path: whole head rotated (n_rot == hd), bfloat16 norm weights (or none), 8-byte aligned rows.
+// A lane owns 4 consecutive elements of the lower half of a head and the 4 it pairs with in the upper half.
+__global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride, int n_q, int n_kv, int hd,
+                                            const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w,
+                                            float eps, const float* __restrict__ cos_sin,
+                                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                            const int* __restrict__ block_table, int table_stride, int page_size,
+                                            __nv_bfloat16* __restrict__ cache, long page_stride, int num_pages, int write_kv,
+                                            int n_tokens, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n_tokens * heads_per_token) return;
+    const int t = warp / heads_per_token, h = warp % heads_per_token;
+    const int pos = positions[t];
+    __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
+    __nv_bfloat16* dst = src;
+    if (h >= n_q) {
+        const int kvh = (h - n_q) % n_kv, is_v = (h - n_q) / n_kv;
+        const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicOr(status, RS_STATUS_BAD_PAGE);
+            return;
+        }
+        dst = cache + (size_t)page * page_stride + ((size_t)(is_v * n_kv + kvh) * page_size + (pos % page_size)) * hd;
+        if (is_v) {
+            for (int i = lane * 4; i < hd; i += 128) *reinterpret_cast<uint2*>(dst + i) = *reinterpret_cast<const uint2*>(src + i);
+            return;
+        }
+    }
+    const __nv_bfloat16* w = h < n_q ? q_w : k_w;
+    const int half = hd >> 1;
+    auto unpack = [](uint2 u, float* f) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(b); f[3] = __high2float(b);
+    };
+    auto pack = [](const float* f) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&b);
+        return u;
+    };
+    // hd <= 256: a lane has at most one group of 4 + 4
+    const int i = lane * 4;
+    const bool mine = i < half;
+    float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+    if (mine) { unpack(*reinterpret_cast<const uint2*>(src + i), a); unpack(*reinterpret_cast<const uint2*>(src + half + i), b); }
+    float scale = 1.f;
+    if (w != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { ss = fmaf(a[u], a[u], ss); ss = fmaf(b[u], b[u], ss); }
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    if (mine) {
+        float wa[4] = {1.f, 1.f, 1.f, 1.f}, wb[4] = {1.f, 1.f, 1.f, 1.f};
+        if (w != nullptr) { unpack(*reinterpret_cast<const uint2*>(w + i), wa); unpack(*reinterpret_cast<const uint2*>(w + half + i), wb); }
+        const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i);
+        const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+        float ra[4], rb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float x = a[u] * scale, y = b[u] * scale;
+            if (w != nullptr) { x *= wa[u]; y *= wb[u]; }
+            ra[u] = x * cc[u] - y * sv[u];
+            rb[u] = x * sv[u] + y * cc[u];
+        }
+        *reinterpret_cast<uint2*>(dst + i) = pack(ra);
+        *reinterpret_cast<uint2*>(dst + half + i) = pack(rb);
+    }
+}
+
 RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, int n_kv, int hd, const void* q_w,
                                  const void* k_w, int w_dt, float eps, const float* cos_sin, int n_rot,
                                  const int* positions, const int* seq_of_token, const int* block_table,
@@ -146,6 +275,14 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
     const long warps = (long)n_tokens * (n_q + (write_kv ? 2 * n_kv : 0));
     const int threads = 256;
     const long blocks = (warps * 32 + threads - 1) / threads;
+    const bool weights_ok = (q_w == nullptr && k_w == nullptr) || (w_dt == RS_BF16 && (q_w == nullptr) == (k_w == nullptr || !write_kv) &&
+                                                                  ((long)q_w & 7) == 0 && ((long)k_w & 7) == 0);
+    if (dt == RS_BF16 && cos_sin != nullptr && n_rot == hd && hd % 8 == 0 && hd <= 256 && row_stride % 4 == 0 && page_stride % 4 == 0 &&
+        ((long)qkv & 7) == 0 && ((long)cache & 7) == 0 && ((long)cos_sin & 15) == 0 && weights_ok && (q_w != nullptr || k_w == nullptr))
+        return rs_launch_pdl(qk_norm_rope_kv_bf16_kernel, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
+                             (__nv_bfloat16*)qkv, row_stride, n_q, n_kv, hd, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, eps,
+                             cos_sin, positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16*)cache,
+                             page_stride, num_pages, write_kv, n_tokens, status);
     RS_DISPATCH_DTYPE(dt, T,
         return rs_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
                              (T*)qkv, row_stride, n_q, n_kv, hd, q_w, k_w, w_dt, eps, cos_sin, n_rot, positions,
