@@ -190,35 +190,37 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int
 }
 
 // bfloat16 fast path: whole head rotated (n_rot == hd), bfloat16 norm weights (or none), 8-byte aligned rows.
-// A lane owns 4 consecutive elements of the lower half of a head and the 4 it pairs with in the upper half.
+// A lane owns 4 consecutive elements of the lower half of a head and the 4 it pairs with in the upper half, so a
+// head takes L = hd / 8 lanes; when L is a power of two a warp serves 32 / L heads side by side.
 __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride, int n_q, int n_kv, int hd,
                                             const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w,
                                             float eps, const float* __restrict__ cos_sin,
                                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                             const int* __restrict__ block_table, int table_stride, int page_size,
                                             __nv_bfloat16* __restrict__ cache, long page_stride, int num_pages, int write_kv,
-                                            int n_tokens, int* status) {
+                                            int n_tokens, int lanes_per_head, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int heads_per_warp = 32 / lanes_per_head;
     const int lane = threadIdx.x & 31;
-    if (warp >= n_tokens * heads_per_token) return;
-    const int t = warp / heads_per_token, h = warp % heads_per_token;
+    const long unit = (((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * heads_per_warp + lane / lanes_per_head;
+    const int sub = lane % lanes_per_head;
+    const bool live = unit < (long)n_tokens * heads_per_token;
+    const int t = live ? (int)(unit / heads_per_token) : 0, h = live ? (int)(unit % heads_per_token) : 0;
     const int pos = positions[t];
     __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
     __nv_bfloat16* dst = src;
+    bool is_v = false, ok = live;
     if (h >= n_q) {
-        const int kvh = (h - n_q) % n_kv, is_v = (h - n_q) / n_kv;
+        const int kvh = (h - n_q) % n_kv;
+        is_v = (h - n_q) / n_kv != 0;
         const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
         if (page < 0 || page >= num_pages) {
-            if (lane == 0) atomicOr(status, RS_STATUS_BAD_PAGE);
-            return;
-        }
-        dst = cache + (size_t)page * page_stride + ((size_t)(is_v * n_kv + kvh) * page_size + (pos % page_size)) * hd;
-        if (is_v) {
-            for (int i = lane * 4; i < hd; i += 128) *reinterpret_cast<uint2*>(dst + i) = *reinterpret_cast<const uint2*>(src + i);
-            return;
+            if (sub == 0 && live) atomicOr(status, RS_STATUS_BAD_PAGE);
+            ok = false;
+        } else {
+            dst = cache + (size_t)page * page_stride + ((size_t)((is_v ? 1 : 0) * n_kv + kvh) * page_size + (pos % page_size)) * hd;
         }
     }
     const __nv_bfloat16* w = h < n_q ? q_w : k_w;
@@ -233,36 +235,37 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
         u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&b);
         return u;
     };
-    // hd <= 256: a lane has at most one group of 4 + 4
-    const int i = lane * 4;
-    const bool mine = i < half;
-    float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
-    if (mine) { unpack(*reinterpret_cast<const uint2*>(src + i), a); unpack(*reinterpret_cast<const uint2*>(src + half + i), b); }
-    float scale = 1.f;
-    if (w != nullptr) {
-        float ss = 0.f;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) { ss = fmaf(a[u], a[u], ss); ss = fmaf(b[u], b[u], ss); }
-        ss = warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)hd + eps);
+    const int i = sub * 4;
+    const bool mine = ok && i < half;
+    uint2 ua = make_uint2(0, 0), ub = make_uint2(0, 0);
+    if (mine) { ua = *reinterpret_cast<const uint2*>(src + i); ub = *reinterpret_cast<const uint2*>(src + half + i); }
+    if (is_v) {                                    // values are copied as they are
+        if (mine) { *reinterpret_cast<uint2*>(dst + i) = ua; *reinterpret_cast<uint2*>(dst + half + i) = ub; }
+        ua = make_uint2(0, 0); ub = make_uint2(0, 0);
     }
-    if (mine) {
-        float wa[4] = {1.f, 1.f, 1.f, 1.f}, wb[4] = {1.f, 1.f, 1.f, 1.f};
-        if (w != nullptr) { unpack(*reinterpret_cast<const uint2*>(w + i), wa); unpack(*reinterpret_cast<const uint2*>(w + half + i), wb); }
-        const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i);
-        const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i);
-        const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-        float ra[4], rb[4];
+    float a[4], b[4];
+    unpack(ua, a); unpack(ub, b);
+    float ss = 0.f;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            float x = a[u] * scale, y = b[u] * scale;
-            if (w != nullptr) { x *= wa[u]; y *= wb[u]; }
-            ra[u] = x * cc[u] - y * sv[u];
-            rb[u] = x * sv[u] + y * cc[u];
-        }
-        *reinterpret_cast<uint2*>(dst + i) = pack(ra);
-        *reinterpret_cast<uint2*>(dst + half + i) = pack(rb);
+    for (int u = 0; u < 4; ++u) { ss = fmaf(a[u], a[u], ss); ss = fmaf(b[u], b[u], ss); }
+    for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // within the head's lanes
+    if (!mine || is_v) return;
+    const float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;
+    float wa[4] = {1.f, 1.f, 1.f, 1.f}, wb[4] = {1.f, 1.f, 1.f, 1.f};
+    if (w != nullptr) { unpack(*reinterpret_cast<const uint2*>(w + i), wa); unpack(*reinterpret_cast<const uint2*>(w + half + i), wb); }
+    const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i);
+    const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i);
+    const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+    float ra[4], rb[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        float x = a[u] * scale, y = b[u] * scale;
+        if (w != nullptr) { x *= wa[u]; y *= wb[u]; }
+        ra[u] = x * cc[u] - y * sv[u];
+        rb[u] = x * sv[u] + y * cc[u];
     }
+    *reinterpret_cast<uint2*>(dst + i) = pack(ra);
+    *reinterpret_cast<uint2*>(dst + half + i) = pack(rb);
 }
 
 RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, int n_kv, int hd, const void* q_w,
@@ -278,11 +281,17 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
     const bool weights_ok = (q_w == nullptr && k_w == nullptr) || (w_dt == RS_BF16 && (q_w == nullptr) == (k_w == nullptr || !write_kv) &&
                                                                   ((long)q_w & 7) == 0 && ((long)k_w & 7) == 0);
     if (dt == RS_BF16 && cos_sin != nullptr && n_rot == hd && hd % 8 == 0 && hd <= 256 && row_stride % 4 == 0 && page_stride % 4 == 0 &&
-        ((long)qkv & 7) == 0 && ((long)cache & 7) == 0 && ((long)cos_sin & 15) == 0 && weights_ok && (q_w != nullptr || k_w == nullptr))
-        return rs_launch_pdl(qk_norm_rope_kv_bf16_kernel, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
+        ((long)qkv & 7) == 0 && ((long)cache & 7) == 0 && ((long)cos_sin & 15) == 0 && weights_ok && (q_w != nullptr || k_w == nullptr)) {
+        int lanes = hd / 8;                                   // lanes a head needs; a power of two packs several heads per warp
+        if (lanes & (lanes - 1)) lanes = 32;
+        const long heads_per_warp = 32 / lanes;
+        const long nwarps = (warps + heads_per_warp - 1) / heads_per_warp;
+        const long nblocks = (nwarps * 32 + threads - 1) / threads;
+        return rs_launch_pdl(qk_norm_rope_kv_bf16_kernel, dim3((unsigned)nblocks), dim3(threads), 0, (cudaStream_t)stream,
                              (__nv_bfloat16*)qkv, row_stride, n_q, n_kv, hd, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, eps,
                              cos_sin, positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16*)cache,
-                             page_stride, num_pages, write_kv, n_tokens, status);
+                             page_stride, num_pages, write_kv, n_tokens, lanes, status);
+    }
     RS_DISPATCH_DTYPE(dt, T,
         return rs_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
                              (T*)qkv, row_stride, n_q, n_kv, hd, q_w, k_w, w_dt, eps, cos_sin, n_rot, positions,
