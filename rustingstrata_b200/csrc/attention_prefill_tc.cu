@@ -8,9 +8,10 @@
 //   softmax        eight warps, two threads per row (each half of the block's keys): tcgen05.ld the scores, mask
 //                  (causal, window, length), running max and sum in float32 with exp2, P rounded to bfloat16 and
 //                  written back over S with tcgen05.st (two values per 32-bit column);
-//   O_blk = P V    tcgen05.mma with P as the tensor-memory operand and the V block (keys x hd, hd contiguous =
-//                  MN-major) in shared memory; the row's thread adds O_blk into its float32 accumulator, scaled
-//                  by the change of the running max.
+//   O += P V       tcgen05.mma with P as the tensor-memory operand and the V block (keys x hd, hd contiguous =
+//                  MN-major) in shared memory, accumulated in tensor memory over all blocks.  The reference maximum
+//                  of a row only moves when a block exceeds it by more than 2^8; only then are the row's sum and
+//                  its O (loaded, scaled, stored back) corrected, which after the first blocks is rare.
 // Warp 8 issues the MMAs (one elected lane) and owns the tensor-memory allocation, warp 9 issues the TMA loads.
 // S is double buffered, so Q K^T of the next block runs under the softmax of this one.  Every mbarrier wait is
 // bounded (tma_helpers.cuh).  Cache pages a block does not own (beyond the sequence, given back by a window)
@@ -102,14 +103,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int HALVES = HD / 64;                      // 64-wide (128-byte) column blocks of a head
     constexpr int HALF_BYTES = 128 * 128;                // 128 rows x 128 bytes
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // one Q, K or V tile
-    constexpr int TMEM_COLS = 512;                       // S0 | S1 | O0 | O1  (128 + 128 + 2 * HD columns)
+    constexpr int TMEM_COLS = 512;                       // S0 | S1 | O  (128 + 128 + HD columns)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     const uint32_t q_smem = base, k_smem = base + TILE_BYTES, v_smem = k_smem + KV_STAGES * TILE_BYTES;
     const uint32_t bar0 = v_smem + KV_STAGES * TILE_BYTES;
-    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full, o_free
-    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_FULL = 13, O_FREE = 15, NBAR = 17 };
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full
+    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_FULL = 13, NBAR = 14 };
     auto bar = [&](int i) { return bar0 + 8u * i; };
     uint8_t* aligned = smem_raw + (base - raw);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
@@ -138,8 +139,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1);
             mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), 8);
-            mbar_init(bar(O_FULL + s), 1); mbar_init(bar(O_FREE + s), 8);
         }
+        mbar_init(bar(O_FULL), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -212,14 +213,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!ok) break;
                 if (!mbar_wait(bar(P_READY + s), (j >> 1) & 1, abort_flag, p.status)) break;
                 if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag, p.status)) break;
-                if (!mbar_wait(bar(O_FREE + s), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk)
-                    umma_ts(tmem_base + 256 + s * HD, tmem_base + s * 128 + kk * 8,
-                            desc_mnmajor(v_smem + s * TILE_BYTES + kk * 16 * 128, HALF_BYTES), idesc_pv, kk ? 1u : 0u);
+                    umma_ts(tmem_base + 256, tmem_base + s * 128 + kk * 8,
+                            desc_mnmajor(v_smem + s * TILE_BYTES + kk * 16 * 128, HALF_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
                 umma_commit(bar(V_EMPTY + s));
-                umma_commit(bar(O_FULL + s));
+                umma_commit(bar(O_FULL));                 // completion j of this barrier: O holds blocks 0..j
             }
         }
     } else {
@@ -228,36 +228,15 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // [0, 64) of a block and the head dims [0, hd/2) of O, the second the other halves.  The two exchange
         // their row maxima through shared memory once per block; their partial sums meet at the end.
         constexpr int HK = BKV / 2, HO = HD / 2;
+        constexpr float RESCALE_ABOVE = 8.f;         // log2 units: keep the old maximum while the new one is within 2^8 of it
         const int quarter = warp & 3, half = warp >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t o_addr = lane_base + 256 + half * HO;
         const int qpos = qpos0 + r / p.pack;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o_acc[HO];
-#pragma unroll
-        for (int d = 0; d < HO; ++d) o_acc[d] = 0.f;
+        float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
-        float corr_prev = 1.f;
         auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
-        // O_blk of block j is added one block late (with the scale of its own block), so the P V product of
-        // block j runs under the softmax of block j + 1
-        auto add_o = [&](int j, float corr) {
-            const int s = j & 1;
-            if (!mbar_wait(bar(O_FULL + s), (j >> 1) & 1, abort_flag, p.status)) return false;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HO; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(lane_base + 256 + s * HD + half * HO + c, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], corr, __uint_as_float(v[i]));
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(O_FREE + s));
-            return true;
-        };
         for (int j = 0; j < n_blocks && ok; ++j) {
             const int s = j & 1;
             const int k0 = (blk_lo + j) * BKV + half * HK;           // first key of this thread's half block
@@ -293,11 +272,33 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             xchg[((j & 1) * 2 + half) * ROWS + r] = mx;
             pair_sync();
-            const float m_new = fmaxf(m_run, fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * ROWS + r]));
-            const float corr = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run - m_new);
-            m_run = m_new;
+            const float m_blk = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * ROWS + r]);
+            // The reference maximum only moves when the block's maximum exceeds it by more than 2^8 (or it was
+            // still -inf): then everything accumulated so far, O in tensor memory included, is rescaled.  Both
+            // threads of a row see the same numbers and take the same decision.
+            const bool move = m_blk > m_used + RESCALE_ABOVE || (m_used == -INFINITY && m_blk > -INFINITY);
+            if (__any_sync(0xffffffffu, move)) {
+                const float corr = move ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_blk)) : 1.f;
+                if (j > 0) {                                          // O holds the products of blocks 0..j-1
+                    if (!mbar_wait(bar(O_FULL), (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < HO; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(o_addr + c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tmem_st16(o_addr + c, v);
+                        tmem_st16(o_addr + c + 16, v + 16);
+                    }
+                    tmem_st_wait();
+                }
+                l_run *= corr;
+                if (move) m_used = m_blk;
+            }
             // P = 2^(x - m), its sum, and P as bfloat16 pairs written over S
-            const float sub = (m_new == -INFINITY) ? 0.f : m_new;     // all keys masked so far: every x is -inf, P = 0
+            const float sub = (m_used == -INFINITY) ? 0.f : m_used;     // nothing visible yet: every x is -inf, P = 0
             float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
             for (int c = 0; c < HK; c += 32) {
@@ -312,31 +313,38 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tmem_st16(lane_base + s * 128 + ((half * HK + c) >> 1), pk);
             }
             tmem_st_wait();
-            l_run = l_run * corr + (rs0 + rs1);
+            l_run += rs0 + rs1;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_READY + s));
-            if (j > 0) ok = add_o(j - 1, corr_prev);
-            corr_prev = corr;
         }
-        if (ok) ok = add_o(n_blocks - 1, corr_prev);
-        // the row's sum: both halves saw the same maxima, so their partial sums simply add
+        // the row's sum: both halves used the same reference maxima, so their partial sums simply add
         xchg[(4 + half) * ROWS + r] = l_run;
         pair_sync();
         l_run += xchg[(4 + (half ^ 1)) * ROWS + r];
-        if (ok && r < n_rows) {
+        if (ok) ok = mbar_wait(bar(O_FULL), (n_blocks - 1) & 1, abort_flag, p.status);
+        tc_fence_after();
+        if (ok) {
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
             __nv_bfloat16* dst = p.out + (size_t)(row0 + q_off + r / p.pack) * p.out_stride + (size_t)(head0 + r % p.pack) * HD +
                                  half * HO;
 #pragma unroll
-            for (int d = 0; d < HO; d += 8) {
-                uint32_t w[4];
+            for (int c = 0; c < HO; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(o_addr + c, v);                              // warp-collective: rows beyond the tile load too
+                tmem_ld_wait();
+                if (r < n_rows) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    __nv_bfloat162 b = __floats2bfloat162_rn(o_acc[d + 2 * u] * inv, o_acc[d + 2 * u + 1] * inv);
-                    w[u] = *reinterpret_cast<uint32_t*>(&b);
+                    for (int d = 0; d < 32; d += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[d + 2 * u]) * inv, __uint_as_float(v[d + 2 * u + 1]) * inv);
+                            w[u] = *reinterpret_cast<uint32_t*>(&b);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
-                *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
