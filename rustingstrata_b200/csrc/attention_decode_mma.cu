@@ -1,29 +1,47 @@
 // Decode attention of the bfloat16 engine: one query token per sequence over its paged keys and values.
 //
-// grid = (sequences, kv heads, splits); a CTA takes one split of SPLIT keys (fixed, at absolute positions)
-// of one kv head and serves all query heads of that group at once, so K and V are read from HBM exactly
-// once per group.  The CTA brings its whole split into shared memory with 16-byte cp.async copies through
-// the block table (all loads in flight together), then each of its 4 warps takes a quarter of the keys:
-// scores S = Q K^T and the weighted sum O += P V run as mma.sync m16n8k16 (the group's heads are the 16-row
-// operand, padded with zero rows), softmax is float32 with exp2 on pre-scaled scores.  The warps' (max, sum,
-// O) are combined through shared memory and written as one un-normalised partial per (sequence, split,
-// head); the merge kernel adds the splits in ascending order.  Keys of a split are visited in the same
-// order whatever the batch holds, so a row's result does not depend on its neighbours.
+// Work items are (sequence, kv head, split of SPLIT keys at absolute positions); an item serves all query
+// heads of its group at once, so K and V are read from HBM exactly once per group.  Persistent CTAs (one per
+// SM) walk the items round-robin; inside a CTA the live items go to G consumer groups in turn, and every
+// group owns `depth` stages of shared memory (K tile, V tile, the group's query rows):
+//   warp 4G (producer)   - lane i looks page i of the item up in the block table and issues ONE 5-d TMA load for
+//                          it: (64 dims, tokens of the page, 64-wide halves of the head, K|V, block), 128-byte
+//                          swizzle.  The TMA unit spends a fixed time on every load, so few large loads stream
+//                          faster than many small ones.  (If the driver refuses the 5-d map, one 2-d load per
+//                          K/V and half goes to the same places.)  All lanes copy the query rows.  Table entry
+//                          and query of the next item are fetched before the wait for a free stage, so their
+//                          latency hides behind the loads in flight.
+//   warps 4g .. 4g+3     - consumer group g.  Each warp takes 32 keys of the item in one pass: scores
+//                          S = Q K^T (mma.sync m16n8k16, the group's query heads are the 16-row operand, padded
+//                          with zero rows), float32 softmax with exp2 on pre-scaled scores, then O = P V.  Its
+//                          (O, max, sum) go over its own rows of the K and V tiles, which nobody reads any more;
+//                          the four warps' results meet there and leave as one un-normalised partial per
+//                          (sequence, split, head).  Then the stage goes back to the producer.
+// With few warps per SM every dependent instruction's latency shows, so the consumers do as little as they
+// can (one pass, no running maximum) and three groups overlap one another's chains.
+// The merge kernel adds the splits of a head in ascending order.  Keys of a split are visited in the same
+// order whatever the batch holds, so a row's result does not depend on its neighbours.  Pages an item does
+// not own (beyond the sequence, given back by a window) are replaced by page 0: their keys are masked and
+// their values only have to be finite.  Waits on mbarriers are bounded (tma_helpers.cuh).
 //
 // Reference counterparts: attn_decode_gqa_* + attn_merge (src/cuda/kernels.cu:2571-2625): K/V of a group
 // read once with cp.async double buffering, CUDA-core dot products, 32 splits.
+#include "tma_helpers.cuh"
 #include "mma_helpers.cuh"
 #include <math.h>
 
 namespace {
-constexpr int WARPS = 8;
-constexpr int SPLIT = 128;             // keys per CTA; must equal the split size the host plans with
-constexpr int KEYS_PER_WARP = SPLIT / WARPS;   // 16: warps 0-3 work on the first half of the split, 4-7 on the second
+constexpr int GROUP_WARPS = 4;
+constexpr int MAX_GROUPS = 3;
+constexpr int MAX_THREADS = (MAX_GROUPS * GROUP_WARPS + 1) * 32;
+constexpr int SPLIT = 128;             // keys per item; must equal the split size the host plans with
+constexpr int KEYS_PER_WARP = SPLIT / GROUP_WARPS;
+constexpr int Q_ROWS = 16;             // rows of the query operand
+static_assert(KEYS_PER_WARP == 32, "a warp's pass covers two 16-key blocks");
 
 struct DecodeParams {
     const __nv_bfloat16* q; long q_stride;
     __nv_bfloat16* out; long out_stride;
-    const __nv_bfloat16* cache; long page_stride;
     int num_pages, page_size;
     const int* block_table; int table_stride;
     const int* q_start; const int* kv_len; const int* work;
@@ -33,189 +51,303 @@ struct DecodeParams {
     const int* split_start;
     float* partial;                    // [slot][n_q][hd + 2]: acc, max (log2 units), sum
     int* status;
+    int n_work, max_splits, total;     // total = n_work * n_kv * max_splits items, dead ones included
+    int groups, depth;                 // consumer groups and stages per group
+    int one_load_per_page;             // the 5-d map is in use
 };
 
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
+}
+
+struct Item { int w, kvh, split_local, seq, key_lo, key_hi, k_base; bool live; };
+
+// The metadata arrays are uploaded before the step's first kernel, so the read-only path is safe for them.
+__device__ __forceinline__ Item decode_item(const DecodeParams& p, int id) {
+    Item it;
+    it.split_local = id % p.max_splits;
+    const int r = id / p.max_splits;
+    it.kvh = r % p.n_kv;
+    it.w = r / p.n_kv;
+    it.seq = __ldg(p.work + it.w);
+    const int kv_len = __ldg(p.kv_len + it.seq);
+    const int lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
+    const int split = lo / SPLIT + it.split_local;
+    it.key_lo = max(lo, split * SPLIT);
+    it.key_hi = min(kv_len, (split + 1) * SPLIT);
+    it.k_base = split * SPLIT;
+    it.live = it.key_lo < it.key_hi;
+    return it;
+}
+
+// next live item of this CTA at or after id; p.total when there is none
+__device__ __forceinline__ int next_live(const DecodeParams& p, int id, Item& it) {
+    for (; id < p.total; id += gridDim.x) {
+        it = decode_item(p, id);
+        if (it.live) return id;
+    }
+    return p.total;
+}
+
 template <int HD>
-__global__ void __launch_bounds__(WARPS * 32) decode_attention_kernel(const DecodeParams p) {
-    constexpr int LD = HD + 8;                       // padded row: ldmatrix rows fall into distinct banks
-    constexpr int KS = HD / 16;                      // k-steps of Q K^T
-    constexpr int DT = HD / 8;                       // 8-wide output tiles of P V
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [SPLIT][LD]
-    __nv_bfloat16* Vs = Ks + SPLIT * LD;                                   // [SPLIT][LD]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int w = blockIdx.x, kvh = blockIdx.y;
+__global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const __grid_constant__ CUtensorMap map_kv, const DecodeParams p) {
+    // A stage holds the item's pages one after the other; a page's block is [K | V][half of the head][token][64 dims],
+    // every (K|V, half) piece a multiple of 1 KiB, so a token's swizzle phase is its index mod 8.
+    constexpr int HALVES = HD / 64;                  // 64-wide (128-byte) column blocks of a head
+    constexpr int STAGE_BYTES = 2 * HALVES * SPLIT * 128;
+    constexpr int WARP_BYTES = 2 * HALVES * KEYS_PER_WARP * 128;
+    constexpr int Q_BYTES = Q_ROWS * HD * 2;
+    constexpr int KS = HD / 16, DT = HD / 8, VEC = HD / 8;
+    constexpr int OLD = HD + 8;                      // float row stride = 8 mod 32: 8-byte stores of a half-warp hit distinct banks
+    constexpr int CHUNK_BYTES = KEYS_PER_WARP * 128; // a warp's tokens of one (K|V, half) piece
+    constexpr int ROWS_PER_CHUNK = CHUNK_BYTES / (OLD * 4);
+    static_assert(ROWS_PER_CHUNK * 2 * HALVES >= Q_ROWS && Q_ROWS * OLD * 4 <= WARP_BYTES, "a warp's K and V rows hold its results");
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - raw);
+    const int stages = p.groups * p.depth;
+    const uint32_t q0 = base + stages * STAGE_BYTES;
+    const uint32_t bar0 = q0 + stages * Q_BYTES;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + (size_t)stages * (STAGE_BYTES + Q_BYTES + 16));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int piece = p.page_size * 128;             // bytes of one (K|V, half) piece of a page
+    const int page_block = 2 * HALVES * piece;
+    const int page_shift = __ffs(p.page_size) - 1;
+    const int producer_warp = p.groups * GROUP_WARPS;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), GROUP_WARPS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // query rows past the group stay zero for the whole kernel
+    for (int i = threadIdx.x; i < stages * Q_BYTES / 16; i += blockDim.x)
+        *reinterpret_cast<uint4*>(aligned + (size_t)stages * STAGE_BYTES + (size_t)i * 16) = make_uint4(0, 0, 0, 0);
+    __syncthreads();
     pdl_launch_dependents();
-    pdl_wait();                                      // the new key and value of this step come from the previous kernel
-    const int seq = p.work[w];
-    const int kv_len = p.kv_len[seq];
-    int key_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
-    const int first_split = key_lo / SPLIT;
-    const int split = first_split + blockIdx.z;
-    key_lo = max(key_lo, split * SPLIT);
-    const int key_hi = min(kv_len, (split + 1) * SPLIT);
-    if (key_lo >= key_hi) return;
-    const int k_base = split * SPLIT;
+    pdl_wait();                                      // the query and the new key and value come from the previous kernel
 
-    // ---- bring the split's keys and values in: one 16-byte chunk per cp.async
-    const int* table = p.block_table + (size_t)seq * p.table_stride;
-    constexpr int CHUNKS = HD / 8;                   // 16-byte chunks per row
-    const int n_keys = key_hi - k_base;              // rows [0, n_keys) of the tile are real keys (some may be below key_lo)
-    // two halves of SPLIT/2 keys, each its own cp.async group: the first half is computed on while the second lands
-    constexpr int HALF = SPLIT / 2;
+    if (warp == producer_warp) {
+        // ------------------------------------------------------------ producer
+        const int pages_per_item = SPLIT / p.page_size;
+        const int nvec = p.group * VEC;              // 16-byte pieces of an item's query rows
+        constexpr int QV = Q_ROWS * VEC / 32;
+        auto fetch = [&](const Item& it, int& page, uint4 (&qv)[QV]) {
+            const int kpos = it.k_base + lane * p.page_size;
+            page = 0;
+            if (lane < pages_per_item && kpos < it.key_hi && kpos + p.page_size > it.key_lo)
+                page = __ldg(p.block_table + (size_t)it.seq * p.table_stride + kpos / p.page_size);
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)__ldg(p.q_start + it.seq) * p.q_stride +
+                                                              (size_t)it.kvh * p.group * HD);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        // 256 threads, 64 key rows per half: 4 threads share a row, each taking a quarter of its chunks
-        const int j = half * HALF + (tid >> 2);
-        const int kpos = k_base + j;
-        const __nv_bfloat16* src = nullptr;
-        if (j < n_keys && kpos >= key_lo) {
-            const int page = table[kpos / p.page_size];
-            if (page >= 0 && page < p.num_pages)
-                src = p.cache + (size_t)page * p.page_stride + ((size_t)kvh * p.page_size + (kpos % p.page_size)) * HD;
-            else if ((tid & 3) == 0)
-                atomicOr(p.status, RS_STATUS_BAD_PAGE);
+            for (int i = 0; i < QV; ++i)
+                if (lane + 32 * i < nvec) qv[i] = ld_dep(src + lane + 32 * i);
+        };
+        Item cur, nxt;
+        int page, page_n = 0;
+        uint4 qv[QV], qn[QV];
+        int id = next_live(p, blockIdx.x, cur);
+        if (id < p.total) fetch(cur, page, qv);
+        for (int n = 0; id < p.total; ++n) {
+            const int id_n = next_live(p, id + gridDim.x, nxt);
+            if (id_n < p.total) fetch(nxt, page_n, qn);
+            const int k = n / p.groups;
+            const int s = (n % p.groups) * p.depth + k % p.depth;
+            const uint32_t parity = (uint32_t)(k / p.depth) & 1u;
+            if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(empty_bar(s), parity ^ 1u, abort_flag, p.status) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            const uint32_t qdst = q0 + s * Q_BYTES;
+#pragma unroll
+            for (int i = 0; i < QV; ++i) {
+                const int v = lane + 32 * i;
+                if (v < nvec) {
+                    const int r = v / VEC, c = v % VEC;
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(qdst + r * (HD * 2) + ((c ^ (r & 7)) << 4)),
+                                 "r"(qv[i].x), "r"(qv[i].y), "r"(qv[i].z), "r"(qv[i].w) : "memory");
+                }
+            }
+            __syncwarp();                            // every lane's query rows are written before lane 0 arrives
+            if (lane == 0) mbar_expect_tx(full_bar(s), STAGE_BYTES);
+            __syncwarp();                            // ... and the byte count is expected before any lane's load can land
+            if (lane < pages_per_item) {
+                const uint32_t dst = base + s * STAGE_BYTES + lane * page_block;
+                if (p.one_load_per_page) {
+                    tma_load_5d(dst, &map_kv, 0, 0, 0, 0, page * 2 * p.n_kv + cur.kvh, full_bar(s));
+                } else {
+#pragma unroll
+                    for (int kv = 0; kv < 2; ++kv) {
+                        const int row = ((page * 2 + kv) * p.n_kv + cur.kvh) * p.page_size;
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h)
+                            tma_load_2d(dst + (kv * HALVES + h) * piece, &map_kv, h * 64, row, full_bar(s));
+                    }
+                }
+            }
+            id = id_n; cur = nxt; page = page_n;
+#pragma unroll
+            for (int i = 0; i < QV; ++i) qv[i] = qn[i];
         }
-        for (int c = (tid & 3); c < CHUNKS; c += 4) {
-            if (src != nullptr) {
-                cp_async16(smem_addr(Ks + j * LD + c * 8), src + c * 8);
-                cp_async16(smem_addr(Vs + j * LD + c * 8), src + (size_t)p.n_kv * p.page_size * HD + c * 8);
-            } else {                                  // masked keys still take part in the MMAs: keep them finite
-                *reinterpret_cast<uint4*>(Ks + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(Vs + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
+    } else if (warp < producer_warp) {
+        // ------------------------------------------------------------ consumers: group g takes live items g, g + G, ...
+        const int grp = warp / GROUP_WARPS, gw = warp % GROUP_WARPS;
+        const int g = lane >> 2, t = lane & 3;
+        auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_WARPS * 32) : "memory"); };
+        // A warp whose wait ran out keeps walking its items without touching them, so that the group's named
+        // barrier below always finds all four warps.
+        bool ok = true;
+        Item it;
+        int n = 0;
+        for (int id = next_live(p, blockIdx.x, it); id < p.total; id = next_live(p, id + gridDim.x, it), ++n) {
+            if (n % p.groups != grp) continue;
+            const int k = n / p.groups;
+            const int s = grp * p.depth + k % p.depth;
+            const uint32_t parity = (uint32_t)(k / p.depth) & 1u;
+            const uint32_t st_smem = base + s * STAGE_BYTES, q_smem = q0 + s * Q_BYTES;
+            // where warp ww leaves row r of its result: over its own tokens' keys and values
+            auto result_row = [&](int ww, int r) {
+                if (p.page_size <= KEYS_PER_WARP) return st_smem + ww * WARP_BYTES + r * (OLD * 4);   // whole pages, contiguous
+                const int c = r / ROWS_PER_CHUNK, row = ww * KEYS_PER_WARP;
+                return st_smem + (row >> page_shift) * page_block + c * piece + (row & (p.page_size - 1)) * 128 +
+                       (r % ROWS_PER_CHUNK) * (OLD * 4);
+            };
+            if (ok) ok = mbar_wait(full_bar(s), parity, abort_flag, p.status);
+            if (ok) {
+                // address of the 16-byte chunk holding dims [col, col + 8) of token `row`'s key (kv = 0) or value (kv = 1)
+                auto chunk_addr = [&](int kv, int row, int col) {
+                    return st_smem + (row >> page_shift) * page_block + (kv * HALVES + (col >> 6)) * piece +
+                           (row & (p.page_size - 1)) * 128 + (((((col & 63) >> 3) ^ row) & 7) << 4);
+                };
+                const int j0 = gw * KEYS_PER_WARP;
+                float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+                float o[DT][4];
+#pragma unroll
+                for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+                if (it.k_base + j0 < it.key_hi && it.k_base + j0 + KEYS_PER_WARP > it.key_lo) {      // uniform per warp
+                    float sc[4][4];
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        uint32_t qa[4], b0[4], b1[4];
+                        {
+                            const int mi = lane >> 3, row = (lane & 7) + (mi & 1) * 8, c = 2 * ks + (mi >> 1);
+                            ldmatrix_x4(q_smem + row * (HD * 2) + ((c ^ (row & 7)) << 4), qa[0], qa[1], qa[2], qa[3]);
+                        }
+                        const int row = j0 + (lane >> 4) * 8 + (lane & 7);
+                        const int col = 16 * ks + ((lane >> 3) & 1) * 8;
+                        ldmatrix_x4(chunk_addr(0, row, col), b0[0], b0[1], b0[2], b0[3]);
+                        ldmatrix_x4(chunk_addr(0, row + 16, col), b1[0], b1[1], b1[2], b1[3]);
+                        mma16816(sc[0], qa, b0[0], b0[1]);
+                        mma16816(sc[1], qa, b0[2], b0[3]);
+                        mma16816(sc[2], qa, b1[0], b1[1]);
+                        mma16816(sc[3], qa, b1[2], b1[3]);
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int kpos = it.k_base + j0 + 8 * nt + 2 * t + (i & 1);
+                            const bool vis = kpos >= it.key_lo && kpos < it.key_hi;
+                            sc[nt][i] = vis ? sc[nt][i] * p.scale_log2 : -INFINITY;
+                            m_row[i >> 1] = fmaxf(m_row[i >> 1], sc[nt][i]);
+                        }
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        m_row[r] = fmaxf(m_row[r], __shfl_xor_sync(0xffffffffu, m_row[r], 1));
+                        m_row[r] = fmaxf(m_row[r], __shfl_xor_sync(0xffffffffu, m_row[r], 2));
+                    }
+                    // the warp's range holds a visible key, so both maxima are finite
+                    uint32_t pf[2][4];
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        float e[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            e[i] = fast_exp2(sc[nt][i] - m_row[i >> 1]);
+                            l_row[i >> 1] += e[i];
+                        }
+                        pf[nt >> 1][2 * (nt & 1)] = pack_bf16(e[0], e[1]);
+                        pf[nt >> 1][2 * (nt & 1) + 1] = pack_bf16(e[2], e[3]);
+                    }
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
+                        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+                    }
+#pragma unroll
+                    for (int d = 0; d < DT; d += 2) {
+                        uint32_t v0[4], v1[4];
+                        const int row = j0 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                        const int col = 8 * (d + (lane >> 4));
+                        ldmatrix_x4_trans(chunk_addr(1, row, col), v0[0], v0[1], v0[2], v0[3]);
+                        ldmatrix_x4_trans(chunk_addr(1, row + 16, col), v1[0], v1[1], v1[2], v1[3]);
+                        mma16816(o[d], pf[0], v0[0], v0[1]);
+                        mma16816(o[d + 1], pf[0], v0[2], v0[3]);
+                        mma16816(o[d], pf[1], v1[0], v1[1]);
+                        mma16816(o[d + 1], pf[1], v1[2], v1[3]);
+                    }
+                }
+                __syncwarp();                        // all lanes are done reading the warp's key and value rows
+                if (g < p.group) {
+                    const uint32_t r0 = result_row(gw, g);
+#pragma unroll
+                    for (int d = 0; d < DT; ++d)
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(r0 + (8 * d + 2 * t) * 4), "f"(o[d][0]), "f"(o[d][1]) : "memory");
+                    if (t == 0)
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(r0 + HD * 4), "f"(m_row[0]), "f"(l_row[0]) : "memory");
+                }
+                if (g + 8 < p.group) {
+                    const uint32_t r1 = result_row(gw, g + 8);
+#pragma unroll
+                    for (int d = 0; d < DT; ++d)
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(r1 + (8 * d + 2 * t) * 4), "f"(o[d][2]), "f"(o[d][3]) : "memory");
+                    if (t == 0)
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(r1 + HD * 4), "f"(m_row[1]), "f"(l_row[1]) : "memory");
+                }
+            }
+            group_sync();
+            if (ok) {
+                // one partial per head: the four warps' sums on a common maximum
+                const size_t slot = (size_t)__ldg(p.split_start + it.w) + it.split_local;
+                float* dst = p.partial + (slot * p.n_q + (size_t)it.kvh * p.group) * (HD + 2);
+                auto lds = [&](uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; };
+                for (int i = gw * 32 + lane; i < p.group * (HD + 2); i += GROUP_WARPS * 32) {
+                    const int r = i / (HD + 2), d = i % (HD + 2);
+                    float mw[GROUP_WARPS], M = -INFINITY;
+#pragma unroll
+                    for (int ww = 0; ww < GROUP_WARPS; ++ww) { mw[ww] = lds(result_row(ww, r) + HD * 4); M = fmaxf(M, mw[ww]); }
+                    float val = M;
+                    if (d != HD) {
+                        val = 0.f;
+#pragma unroll
+                        for (int ww = 0; ww < GROUP_WARPS; ++ww) {
+                            const float e = (mw[ww] == -INFINITY) ? 0.f : fast_exp2(mw[ww] - M);
+                            val = fmaf(lds(result_row(ww, r) + (d < HD ? d : HD + 1) * 4), e, val);
+                        }
+                    }
+                    dst[i] = val;
+                }
+                // the next writes to these rows come from TMA
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(s));
             }
         }
-        cp_async_commit();
-    }
-
-    // ---- query fragments (rows = heads of the group, zero beyond the group), loaded while the copies fly
-    const int head0 = kvh * p.group;
-    const __nv_bfloat16* qrow = p.q + (size_t)p.q_start[seq] * p.q_stride + (size_t)head0 * HD;
-    uint32_t qf[KS][4];
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-        const int d0 = 16 * ks + 2 * t;
-        qf[ks][0] = g < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d0)) : 0u;
-        qf[ks][1] = g + 8 < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d0)) : 0u;
-        qf[ks][2] = g < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d0 + 8)) : 0u;
-        qf[ks][3] = g + 8 < p.group ? ld_dep(reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d0 + 8)) : 0u;
-    }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    float o[DT][4];
-#pragma unroll
-    for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
-
-    cp_async_wait<0>();
-    __syncthreads();                                            // the whole split has landed
-    {
-        const int j0 = warp * 16;                               // first key row of this warp's 16-key block
-        const bool warp_has_keys = k_base + j0 < key_hi;
-        if (warp_has_keys) {
-        float s[2][4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            uint32_t b00, b01, b10, b11;
-            const int row = j0 + (lane >> 4) * 8 + (lane & 7);
-            const int col = 16 * ks + ((lane >> 3) & 1) * 8;
-            ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Ks + row * LD + col), b00, b01, b10, b11);
-            mma16816(s[0], qf[ks], b00, b01);
-            mma16816(s[1], qf[ks], b10, b11);
-        }
-        // mask and scale (log2 units); key of s[nt][i]: j0 + 8 nt + 2 t + (i & 1)
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int kpos = k_base + j0 + 8 * nt + 2 * t + (i & 1);
-                const bool ok = kpos >= key_lo && kpos < key_hi;
-                s[nt][i] = ok ? s[nt][i] * p.scale_log2 : -INFINITY;
-                mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
-            }
-        float corr[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);
-            corr[r] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[r] - m_new);
-            m_run[r] = m_new;
-        }
-        float rs[2] = {0.f, 0.f};
-        uint32_t pf[4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            float e[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float mm = m_run[i >> 1];
-                e[i] = (mm == -INFINITY) ? 0.f : fast_exp2(s[nt][i] - mm);
-                rs[i >> 1] += e[i];
-            }
-            pf[2 * nt] = pack_bf16(e[0], e[1]);         // a0 / a2: row g
-            pf[2 * nt + 1] = pack_bf16(e[2], e[3]);     // a1 / a3: row g + 8
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
-            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
-            l_run[r] = l_run[r] * corr[r] + rs[r];
-        }
-#pragma unroll
-        for (int d = 0; d < DT; ++d) { o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1]; }
-        // O += P V: V^T fragments through ldmatrix.trans, two 8-wide output tiles per instruction
-#pragma unroll
-        for (int d = 0; d < DT; d += 2) {
-            uint32_t v00, v01, v10, v11;
-            const int row = j0 + ((lane >> 3) & 1) * 8 + (lane & 7);
-            const int col = 8 * (d + (lane >> 4));
-            ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(Vs + row * LD + col), v00, v01, v10, v11);
-            mma16816(o[d], pf, v00, v01);
-            mma16816(o[d + 1], pf, v10, v11);
-        }
-        }
-    }
-    cp_async_wait<0>();
-
-    // ---- combine the warps: (max, sum, O) of each warp → shared memory, then one partial per head
-    __syncthreads();                                            // everyone is done reading K and V
-    float* Os = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][HD + 2]
-    constexpr int OLD = HD + 8;                                 // row stride = 8 mod 32 floats: 8-byte stores of a half-warp hit distinct banks
-    if (g < p.group) {
-        float* r0 = Os + ((size_t)warp * 16 + g) * OLD;
-#pragma unroll
-        for (int d = 0; d < DT; ++d) *reinterpret_cast<float2*>(r0 + 8 * d + 2 * t) = make_float2(o[d][0], o[d][1]);
-        if (t == 0) { r0[HD] = m_run[0]; r0[HD + 1] = l_run[0]; }
-    }
-    if (g + 8 < p.group) {
-        float* r1 = Os + ((size_t)warp * 16 + g + 8) * OLD;
-#pragma unroll
-        for (int d = 0; d < DT; ++d) *reinterpret_cast<float2*>(r1 + 8 * d + 2 * t) = make_float2(o[d][2], o[d][3]);
-        if (t == 0) { r1[HD] = m_run[1]; r1[HD + 1] = l_run[1]; }
     }
     __syncthreads();
-    const size_t slot = (size_t)p.split_start[w] + blockIdx.z;
-    for (int i = tid; i < p.group * (HD + 2); i += WARPS * 32) {
-        const int r = i / (HD + 2), d = i % (HD + 2);
-        float M = -INFINITY;
-#pragma unroll
-        for (int ww = 0; ww < WARPS; ++ww) M = fmaxf(M, Os[((size_t)ww * 16 + r) * OLD + HD]);
-        float val;
-        if (d == HD) {
-            val = M;
-        } else {
-            val = 0.f;
-#pragma unroll
-            for (int ww = 0; ww < WARPS; ++ww) {
-                const float mw = Os[((size_t)ww * 16 + r) * OLD + HD];
-                const float e = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-                val += Os[((size_t)ww * 16 + r) * OLD + (d < HD ? d : HD + 1)] * e;
-            }
-        }
-        p.partial[(slot * p.n_q + head0 + r) * (HD + 2) + d] = val;
+    if (*abort_flag && threadIdx.x == 0) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);      // let loads already issued land
     }
+    __syncthreads();
 }
 
 // out[token of seq, head, :] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in ascending order
@@ -245,32 +377,77 @@ __global__ void decode_merge_kernel(const DecodeParams p) {
     }
 }
 
+// 5-d map of the cache: (64 dims, token of the page, half of the head, K|V, block = page * 2 * n_kv + kv head); one
+// box is everything an item needs of a page.  Returns non-zero if the driver does not take it.
+int page_map(const void* cache, int num_pages, int n_kv, int page_size, int hd, CUtensorMap* out) {
+    using namespace rs_tma;
+    EncodeTiledFn enc = get_encoder();
+    if (!enc) return 1;
+    const cuuint64_t row = (cuuint64_t)hd * 2;
+    cuuint64_t dims[5] = {64, (cuuint64_t)page_size, (cuuint64_t)(hd / 64), 2, (cuuint64_t)num_pages * 2 * n_kv - n_kv};
+    cuuint64_t strides[4] = {row, 128, (cuuint64_t)n_kv * page_size * row, (cuuint64_t)page_size * row};
+    cuuint32_t box[5] = {64, (cuuint32_t)page_size, (cuuint32_t)(hd / 64), 2, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1;
+}
+
+struct PageMapKey { const void* cache; int num_pages, n_kv, page_size, hd; };
+struct PageMapEntry { PageMapKey key; int refused; CUtensorMap map; };
+std::vector<PageMapEntry> g_page_maps;
+std::mutex g_page_maps_mutex;
+int g_last_loads_per_page = 0;
+
+int cached_page_map(const void* cache, int num_pages, int n_kv, int page_size, int hd, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_page_maps_mutex);
+    for (auto& e : g_page_maps)
+        if (e.key.cache == cache && e.key.num_pages == num_pages && e.key.n_kv == n_kv && e.key.page_size == page_size &&
+            e.key.hd == hd) { *out = e.map; return e.refused; }
+    PageMapEntry e{PageMapKey{cache, num_pages, n_kv, page_size, hd}, 0, {}};
+    e.refused = page_map(cache, num_pages, n_kv, page_size, hd, &e.map);
+    if (g_page_maps.size() > 64) g_page_maps.clear();
+    g_page_maps.push_back(e);
+    *out = e.map;
+    return e.refused;
+}
+
 template <int HD>
-int launch(const DecodeParams& p, int n_work, int max_splits, cudaStream_t s) {
-    constexpr int LD = HD + 8;
-    constexpr size_t kv_bytes = (size_t)2 * SPLIT * LD * 2;
-    constexpr size_t o_bytes = (size_t)WARPS * 16 * (HD + 8) * 4;
-    constexpr size_t smem = kv_bytes > o_bytes ? kv_bytes : o_bytes;
+int launch(const CUtensorMap& mkv, DecodeParams p, cudaStream_t s) {
+    constexpr size_t stage_bytes = (size_t)2 * (HD / 64) * SPLIT * 128 + Q_ROWS * HD * 2 + 16;
+    constexpr size_t budget = 225 * 1024 - 1024 - 16;
+    const int stages = (int)(budget / stage_bytes);
+    p.groups = stages < MAX_GROUPS ? stages : MAX_GROUPS;
+    p.depth = stages / p.groups < 2 ? stages / p.groups : 2;
+    const size_t smem = (size_t)p.groups * p.depth * stage_bytes + 1024 + 16;
     auto kern = decode_attention_kernel<HD>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static size_t smem_allowed = 0;
+    if (smem > smem_allowed) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        smem_allowed = smem;
     }
-    int rc = rs_launch_pdl(kern, dim3(n_work, p.n_kv, max_splits), dim3(WARPS * 32), smem, s, p);
+    const int sms = rs_tma::sm_count();
+    const int grid = p.total < sms ? p.total : sms;
+    int rc = rs_launch_pdl(kern, dim3(grid), dim3((p.groups * GROUP_WARPS + 1) * 32), smem, s, mkv, p);
     if (rc != 0) return rc;
-    return rs_launch_pdl(decode_merge_kernel<HD>, dim3(n_work, p.n_q), dim3(HD >= 128 ? 128 : 64), 0, s, p);
+    return rs_launch_pdl(decode_merge_kernel<HD>, dim3(p.n_work, p.n_q), dim3(HD >= 128 ? 128 : 64), 0, s, p);
 }
 }  // namespace
 
-// Head sizes this kernel is built for; other sizes (and groups above 16 heads) go to the CUDA-core kernel.
-RS_EXPORT int rs_attention_decode_bf16_supported(int n_q, int n_kv, int hd) {
-    if (n_kv <= 0 || n_q % n_kv || n_q / n_kv > 16) return 0;
-    return hd == 32 || hd == 64 || hd == 96 || hd == 128;
+// Shapes this kernel is built for; other head sizes, groups above 16 heads and page sizes that are not a power of
+// two from 8 to 128 go to the CUDA-core kernel.
+RS_EXPORT int rs_attention_decode_bf16_supported(int n_q, int n_kv, int hd, int page_size) {
+    if (n_kv <= 0 || n_q % n_kv || n_q / n_kv > Q_ROWS) return 0;
+    if (hd != 64 && hd != 128) return 0;
+    return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }
 
 RS_EXPORT int rs_attention_decode_bf16_split_keys() { return SPLIT; }
+
+// TMA loads per page of an item in the most recent launch: 1 with the 5-d map, else 2 * head size / 64.
+RS_EXPORT int rs_attention_decode_bf16_loads_per_page() { return g_last_loads_per_page; }
 
 // Same arguments and partial-workspace layout as the decode form of rs_attention_simt; bfloat16 only.
 RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* cache,
@@ -280,23 +457,27 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
                                        int max_splits, const int* split_start, float* partial, int* status,
                                        void* stream) {
     if (n_work <= 0) return 0;
-    if (!rs_attention_decode_bf16_supported(n_q, n_kv, hd) || split_keys != SPLIT || max_splits <= 0 ||
-        partial == nullptr || split_start == nullptr || (q_stride % 2) || ((long)q & 3) || ((long)cache & 15) ||
-        (page_stride % 8))
+    if (!rs_attention_decode_bf16_supported(n_q, n_kv, hd, page_size) || split_keys != SPLIT || max_splits <= 0 ||
+        partial == nullptr || split_start == nullptr || (q_stride % 8) || ((long)q & 15) || ((long)cache & 15) ||
+        page_stride != (long)2 * n_kv * page_size * hd || (long)n_work * n_kv * max_splits > 0x7fff0000L)
         return (int)cudaErrorInvalidValue;
     DecodeParams p;
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
-    p.cache = (const __nv_bfloat16*)cache; p.page_stride = page_stride; p.num_pages = num_pages; p.page_size = page_size;
+    p.num_pages = num_pages; p.page_size = page_size;
     p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
     p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.split_start = split_start; p.partial = partial; p.status = status;
-    cudaStream_t s = (cudaStream_t)stream;
-    switch (hd) {
-        case 32: return launch<32>(p, n_work, max_splits, s);
-        case 64: return launch<64>(p, n_work, max_splits, s);
-        case 96: return launch<96>(p, n_work, max_splits, s);
-        case 128: return launch<128>(p, n_work, max_splits, s);
+    p.split_start = split_start; p.partial = partial; p.status = status; p.n_work = n_work; p.max_splits = max_splits;
+    p.total = n_work * n_kv * max_splits;
+    p.groups = p.depth = 0;
+    CUtensorMap mkv;
+    p.one_load_per_page = cached_page_map(cache, num_pages, n_kv, page_size, hd, &mkv) == 0;
+    if (!p.one_load_per_page) {
+        int rc = rs_tma::get_map(cache, (long)num_pages * 2 * n_kv * page_size, hd, hd, page_size, &mkv);
+        if (rc) return rc;
     }
-    return (int)cudaErrorInvalidValue;
+    g_last_loads_per_page = p.one_load_per_page ? 1 : 2 * (hd / 64);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64) return launch<64>(mkv, p, s);
+    return launch<128>(mkv, p, s);
 }

@@ -90,7 +90,8 @@ def bench_decode_attention(B, S, n_q, n_kv, hd, page, iters, once):
                 total_splits=int(ss[-1]), partial=partial, **common)
     us = timed(lambda i: ops.attention_decode(cache=caches[i], **args), nb, iters, once)
     byts = B * S * n_kv * hd * 2 * 2
-    print(f"decode_attention B={B} S={S} heads {n_q}/{n_kv} hd={hd}: {us:.1f} us, cache {byts / us / 1e6:.2f} TB/s")
+    print(f"decode_attention B={B} S={S} heads {n_q}/{n_kv} hd={hd} page={page}: {us:.1f} us, cache {byts / us / 1e6:.2f} TB/s, "
+          f"{ops.attention_decode_loads_per_page()} TMA load(s) per page")
 
 
 def bench_prefill_attention(S, n_q, n_kv, hd, page, iters, once, force=""):

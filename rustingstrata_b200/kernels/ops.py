@@ -233,7 +233,7 @@ def bf16lib():
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                  c_void_p]
-        lib.rs_attention_decode_bf16_supported.argtypes = [c_int, c_int, c_int]
+        lib.rs_attention_decode_bf16_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                   c_int, c_int, c_float, c_void_p, c_void_p]
@@ -475,9 +475,17 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
         int(window), float(scale), _ptr(status), _stream()), "attention_prefill_bf16")
 
 
-def attention_decode_fast_ok(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
-    """Whether the tensor-core decode kernel takes this shape (bfloat16, head size 32/64/96/128, group <= 16)."""
-    return dtype == torch.bfloat16 and bool(bf16lib().rs_attention_decode_bf16_supported(n_q, n_kv, head_dim))
+def attention_decode_fast_ok(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int = 16) -> bool:
+    """Whether the tensor-core decode kernel takes this shape (bfloat16, head size 64 or 128, group <= 16, pages of
+    8 to 128 tokens, a power of two)."""
+    return dtype == torch.bfloat16 and bool(
+        bf16lib().rs_attention_decode_bf16_supported(n_q, n_kv, head_dim, page_size))
+
+
+def attention_decode_loads_per_page() -> int:
+    """TMA loads the tensor-core decode kernel issued per page of an item in its most recent launch: 1 when the
+    driver took the 5-d map of the cache, else one per K/V and 64-wide half of the head."""
+    return int(bf16lib().rs_attention_decode_bf16_loads_per_page())
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
@@ -487,7 +495,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                      force_simt: bool = False) -> None:
     """Attention of sequences with one query token each: the tensor-core kernel (csrc/attention_decode_mma.cu)
     where it takes the shape, else the CUDA-core kernel's split form.  Same partial-workspace layout."""
-    if force_simt or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim):
+    if force_simt or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size):
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, True, status, split_keys=split_keys, max_splits=max_splits, split_start=split_start,
                        total_splits=total_splits, partial=partial)

@@ -305,14 +305,15 @@ def test_attention_finds_a_far_key_among_hundreds(dtype, far):
     assert (got[0].double().cpu() - want[0]).abs().max() < 0.05
 
 
-@pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (6, 2, 32, 4), (16, 1, 64, 8), (3, 3, 96, 16),
-                                              (9, 1, 64, 16)])
+@pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (16, 1, 64, 8), (9, 1, 64, 16), (3, 3, 128, 32),
+                                              (4, 1, 64, 128), (12, 4, 64, 64), (16, 1, 128, 8)])
 @pytest.mark.parametrize("window", [0, 100])
 def test_decode_tensor_core_kernel_agrees_with_the_cuda_core_kernel(n_q, n_kv, hd, page, window):
     from rustingstrata_b200.kernels import ops as o
-    assert o.attention_decode_fast_ok(torch.bfloat16, n_q, n_kv, hd)
-    assert not o.attention_decode_fast_ok(torch.float32, n_q, n_kv, hd)
-    assert not o.attention_decode_fast_ok(torch.bfloat16, 34, 2, 64) and not o.attention_decode_fast_ok(torch.bfloat16, 4, 2, 48)
+    assert o.attention_decode_fast_ok(torch.bfloat16, n_q, n_kv, hd, page)
+    assert not o.attention_decode_fast_ok(torch.float32, n_q, n_kv, hd, page)
+    assert not o.attention_decode_fast_ok(torch.bfloat16, 34, 2, 64, 16) and not o.attention_decode_fast_ok(torch.bfloat16, 4, 2, 48, 16)
+    assert not o.attention_decode_fast_ok(torch.bfloat16, 4, 2, 64, 4) and not o.attention_decode_fast_ok(torch.bfloat16, 4, 2, 64, 24)
     seqs = [(1, 1), (127, 1), (128, 1), (129, 1), (300, 1), (1000, 1), (16, 1), (2048, 1)]
     torch.manual_seed(3)
     fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window)
