@@ -11,6 +11,8 @@
 //                          K/V and half goes to the same places.)  All lanes copy the query rows.  Table entry
 //                          and query of the next item are fetched before the wait for a free stage, so their
 //                          latency hides behind the loads in flight.
+//   warp 4G + 1          - prefetcher: asks the pages of the next few items into L2 (TMA prefetch), because the
+//                          shared-memory ring alone holds too few bytes in flight to cover the latency of loaded DRAM.
 //   warps 4g .. 4g+3     - consumer group g.  Each warp takes 32 keys of the item in one pass: scores
 //                          S = Q K^T (mma.sync m16n8k16, the group's query heads are the 16-row operand, padded
 //                          with zero rows), float32 softmax with exp2 on pre-scaled scores, then O = P V.  Its
@@ -33,7 +35,8 @@
 namespace {
 constexpr int GROUP_WARPS = 4;
 constexpr int MAX_GROUPS = 3;
-constexpr int MAX_THREADS = (MAX_GROUPS * GROUP_WARPS + 1) * 32;
+constexpr int MAX_THREADS = (MAX_GROUPS * GROUP_WARPS + 2) * 32;
+constexpr int PREFETCH_AHEAD = 4;      // items whose pages are asked into L2 before their stage is free
 constexpr int SPLIT = 128;             // keys per item; must equal the split size the host plans with
 constexpr int KEYS_PER_WARP = SPLIT / GROUP_WARPS;
 constexpr int Q_ROWS = 16;             // rows of the query operand
@@ -60,6 +63,11 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_5d(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global [%0, {%1, %2, %3, %4, %5}];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
 
 struct Item { int w, kvh, split_local, seq, key_lo, key_hi, k_base; bool live; };
@@ -114,6 +122,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + (size_t)stages * (STAGE_BYTES + Q_BYTES + 16));
+    volatile int* produced = abort_flag + 1;         // live items whose loads have been issued
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int piece = p.page_size * 128;             // bytes of one (K|V, half) piece of a page
@@ -123,6 +132,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), GROUP_WARPS); }
         *abort_flag = 0;
+        *produced = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // query rows past the group stay zero for the whole kernel
@@ -191,9 +201,31 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
                     }
                 }
             }
+            if (lane == 0) *produced = n + 1;
             id = id_n; cur = nxt; page = page_n;
 #pragma unroll
             for (int i = 0; i < QV; ++i) qv[i] = qn[i];
+        }
+    } else if (warp == producer_warp + 1) {
+        // ------------------------------------------------------------ prefetcher: the smem ring holds too little to cover
+        // the latency of loaded DRAM, so the pages of the next few items are asked into L2 ahead of the producer
+        if (p.one_load_per_page) {
+            const int pages_per_item = SPLIT / p.page_size;
+            Item it;
+            int n = 0;
+            bool go = true;
+            for (int id = next_live(p, blockIdx.x, it); id < p.total && go; id = next_live(p, id + gridDim.x, it), ++n) {
+                const int kpos = it.k_base + lane * p.page_size;
+                int page = -1;
+                if (lane < pages_per_item && kpos < it.key_hi && kpos + p.page_size > it.key_lo)
+                    page = __ldg(p.block_table + (size_t)it.seq * p.table_stride + kpos / p.page_size);
+                const unsigned long long t0 = global_ns();
+                while (n >= *produced + PREFETCH_AHEAD) {
+                    __nanosleep(200);
+                    if (*abort_flag || global_ns() - t0 > RS_WAIT_LIMIT_NS) { go = false; break; }
+                }
+                if (go && page >= 0 && page < p.num_pages) tma_prefetch_5d(&map_kv, 0, 0, 0, 0, page * 2 * p.n_kv + it.kvh);
+            }
         }
     } else if (warp < producer_warp) {
         // ------------------------------------------------------------ consumers: group g takes live items g, g + G, ...
@@ -430,7 +462,7 @@ int launch(const CUtensorMap& mkv, DecodeParams p, cudaStream_t s) {
     }
     const int sms = rs_tma::sm_count();
     const int grid = p.total < sms ? p.total : sms;
-    int rc = rs_launch_pdl(kern, dim3(grid), dim3((p.groups * GROUP_WARPS + 1) * 32), smem, s, mkv, p);
+    int rc = rs_launch_pdl(kern, dim3(grid), dim3((p.groups * GROUP_WARPS + 2) * 32), smem, s, mkv, p);
     if (rc != 0) return rc;
     return rs_launch_pdl(decode_merge_kernel<HD>, dim3(p.n_work, p.n_q), dim3(HD >= 128 ? 128 : 64), 0, s, p);
 }

@@ -11,8 +11,10 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Two tiny configurations of the architecture that differ in every size and option, and a third with
-# sizes that are no power of two anywhere (head size 48, 5 query heads on 1 kv head, odd widths).
+# Two tiny configurations of the architecture that differ in every size and option, a third with sizes that
+# are no power of two anywhere (head size 48, 5 query heads on 1 kv head, odd widths), and a fourth whose
+# head size, group and page size are ones the tcgen05/TMA attention kernels take, so that those kernels
+# (and not only their CUDA-core stand-ins) run inside the engine under test.
 TINY = {
     "A": dict(
         config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 256, "hidden_size": 64,
@@ -36,6 +38,14 @@ TINY = {
                 "max_position_embeddings": 320, "tie_word_embeddings": False, "use_sliding_window": True,
                 "sliding_window": 40, "max_window_layers": 1, "torch_dtype": "bfloat16"},
         seed=2, std=0.1, norm_std=0.05, page_size=8),
+    "D": dict(
+        config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 777, "hidden_size": 128,
+                "num_hidden_layers": 3, "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64,
+                "intermediate_size": 328, "rms_norm_eps": 2e-6, "rope_theta": 500000.0,
+                "max_position_embeddings": 640, "tie_word_embeddings": False, "use_sliding_window": True,
+                "sliding_window": 150, "layer_types": ["full_attention", "sliding_attention", "full_attention"],
+                "torch_dtype": "bfloat16"},
+        seed=3, std=0.06, norm_std=0.05, page_size=16),
 }
 
 # Tolerances, as max |difference| / max |reference logit| over the compared rows.  The 32-bit engine

@@ -31,7 +31,7 @@ def teacher_forced_ok(cfg, w, prompt, generated, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_greedy_generation_through_the_entry_point(tiny_models, name, dtype):
     cfg, w = P.read_model(tiny_models[name])
     eng = engine(tiny_models, name, dtype)
@@ -64,6 +64,51 @@ def test_long_decoding_and_first_tokens(tiny_models, dtype):
         worst = max(worst, err)
     eng.runner.check_status()
     eng.release("x")
+
+
+def test_tensor_core_attention_inside_the_engine(tiny_models):
+    """The bfloat16 engine on a configuration the tcgen05 prefill and TMA decode attention kernels take: a
+    long prompt in uneven portions, then decoding across several 128-key splits and past the window's edge,
+    two requests side by side, every row against the plain implementation."""
+    from rustingstrata_b200.engine import StepEntry
+    from rustingstrata_b200.kernels import ops
+    c = TINY["D"]["config"]
+    n_q, n_kv, hd, page = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], TINY["D"]["page_size"]
+    import torch
+    assert ops.attention_prefill_kernel(torch.bfloat16, n_q, n_kv, hd, page) == "tc"
+    assert ops.attention_decode_fast_ok(torch.bfloat16, n_q, n_kv, hd, page)
+    cfg, w = P.read_model(tiny_models["D"])
+    eng = engine(tiny_models, "D", "bfloat16", max_tokens=1536, max_batch_tokens=512)
+    toks = {"x": random_tokens(cfg["vocab_size"], 430, 5), "y": random_tokens(cfg["vocab_size"], 300, 6)}
+    ref = {k: P.forward_logits(cfg, w, t) for k, t in toks.items()}
+    scale = {k: np.max(np.abs(r)) for k, r in ref.items()}
+    pos = {"x": 0, "y": 0}
+    worst = 0.0
+
+    def feed(entries):
+        # the engine returns at most 64 rows a step: the last 30 of each portion
+        nonlocal worst
+        first = {k: max(0, n - 30) for k, n in entries}
+        rows = eng.step_raw([StepEntry(k, toks[k][pos[k]:pos[k] + n], list(range(first[k], n))) for k, n in entries]).cpu().numpy()
+        at = 0
+        for k, n in entries:
+            m = n - first[k]
+            lo = pos[k] + first[k]
+            err = float(np.max(np.abs(rows[at:at + m] - ref[k][lo:lo + m])) / scale[k])
+            assert err <= TOL["bfloat16"], f"{k} at {lo}..{lo + m}: {err:.3e}"
+            worst = max(worst, err)
+            at += m
+            pos[k] += n
+
+    feed([("x", 201)])
+    feed([("x", 130), ("y", 137)])
+    feed([("x", 1), ("y", 100)])
+    for _ in range(60):
+        feed([("x", 1), ("y", 1)])
+    eng.runner.check_status()
+    eng.release("x")
+    eng.release("y")
+    eng.runner.cache.check()
 
 
 @pytest.mark.parametrize("dtype", ["float32"])

@@ -129,7 +129,7 @@ def replayed(tiny_models, name, dtype):
 
 @pytest.mark.parametrize("cutting", ["whole", "tail32", "portions", "mixed"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_matches_plain(tiny_models, name, dtype, cutting):
     tr, parts, got, ref, _, _ = replayed(tiny_models, name, dtype)
     worst, n_rows = (0.0, None), 0
