@@ -12,7 +12,8 @@
 //                  MN-major) in shared memory, accumulated in tensor memory over all blocks.  The reference maximum
 //                  of a row only moves when a block exceeds it by more than 2^8; only then are the row's sum and
 //                  its O (loaded, scaled, stored back) corrected, which after the first blocks is rare.
-// Warp 8 issues the MMAs (one elected lane) and owns the tensor-memory allocation, warp 9 issues the TMA loads.
+// Warp 8 issues the MMAs (one elected lane) and owns the tensor-memory allocation, warp 9 issues the TMA loads
+// (lane i looks page i of a block up and loads it, so the lookups of a block run side by side).
 // S is double buffered, so Q K^T of the next block runs under the softmax of this one.  Every mbarrier wait is
 // bounded (tma_helpers.cuh).  Cache pages a block does not own (beyond the sequence, given back by a window)
 // are replaced by page 0: their keys are masked, and their values only have to be finite.
@@ -154,38 +155,47 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 9) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer: lane i loads page i of a block
         if (lane == 0) {
             mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(q_smem + h * HALF_BYTES, &map_q, h * 64, head0, row0 + q_off, bar(Q_FULL));
-            const int* table = p.block_table + (size_t)seq * p.table_stride;
-            const int pages_per_block = BKV / p.page_size;
-            bool ok = true;
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                const int s = j & 1;
-                const uint32_t par = ((j >> 1) & 1) ^ 1u;
-                const int k0 = (blk_lo + j) * BKV;
-                for (int kv = 0; kv < 2 && ok; ++kv) {
-                    if (!mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status)) { ok = false; break; }
-                    const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
-                    mbar_expect_tx(full, TILE_BYTES);
-                    const uint32_t dst = (kv ? v_smem : k_smem) + s * TILE_BYTES;
-                    for (int pg = 0; pg < pages_per_block; ++pg) {
-                        const int kpos = k0 + pg * p.page_size;
-                        int page = 0;
-                        if (kpos < key_hi && kpos + p.page_size > key_lo) {
-                            page = table[kpos / p.page_size];
-                            if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
-                        }
-                        const int row = ((page * 2 + kv) * p.n_kv + kvh) * p.page_size;
+        }
+        const int* table = p.block_table + (size_t)seq * p.table_stride;
+        const int pages_per_block = BKV / p.page_size;
+        auto lookup = [&](int j) {
+            const int kpos = (blk_lo + j) * BKV + lane * p.page_size;
+            int page = 0;
+            if (j < n_blocks && lane < pages_per_block && kpos < key_hi && kpos + p.page_size > key_lo) {
+                page = __ldg(table + kpos / p.page_size);
+                if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
+            }
+            return page;
+        };
+        int page = lookup(0);
+        for (int j = 0; j < n_blocks; ++j) {
+            const int s = j & 1;
+            const uint32_t par = ((j >> 1) & 1) ^ 1u;
+            const int page_next = lookup(j + 1);              // its latency hides behind the waits below
+            int ok = 1;
+            for (int kv = 0; kv < 2; ++kv) {
+                const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
+                if (lane == 0) {
+                    ok = mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status) ? 1 : 0;
+                    if (ok) mbar_expect_tx(full, TILE_BYTES);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);          // also orders the expect_tx before every lane's loads
+                if (!ok) break;
+                if (lane < pages_per_block) {
+                    const uint32_t dst = (kv ? v_smem : k_smem) + s * TILE_BYTES + lane * p.page_size * 128;
+                    const int row = ((page * 2 + kv) * p.n_kv + kvh) * p.page_size;
 #pragma unroll
-                        for (int h = 0; h < HALVES; ++h)
-                            tma_load_2d(dst + h * HALF_BYTES + pg * p.page_size * 128, &map_kv, h * 64, row, full);
-                    }
+                    for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * HALF_BYTES, &map_kv, h * 64, row, full);
                 }
             }
+            if (!ok) break;
+            page = page_next;
         }
     } else if (warp == 8) {
         // ------------------------------------------------------------ MMA issuer
