@@ -4,7 +4,11 @@
 // so a key/value tile in shared memory serves P heads.  Keys are walked in blocks of 128 at absolute
 // positions.  Per block
 //   S = Q K^T      tcgen05.mma, Q (128 x hd) and the K block (128 keys x hd) both K-major in shared memory
-//                  (TMA, 128-byte swizzle, one box per cache page and 64-wide half of the head), S in tensor memory;
+//                  (TMA, 128-byte swizzle), S in tensor memory.  A K or V block lies in shared memory as
+//                  [group of 8 keys][64-wide half of the head][8 keys][64 dims]: every (group, half) piece is one
+//                  1 KiB swizzle atom, the groups are evenly spaced whatever the page size is, and a cache page
+//                  arrives with ONE 5-d TMA load (the TMA unit spends a fixed time per load, so fewer and larger
+//                  loads feed the tensor cores faster);
 //   softmax        eight warps, two threads per row (each half of the block's keys): tcgen05.ld the scores, mask
 //                  (causal, window, length), running max and sum in float32 with exp2, P rounded to bfloat16 and
 //                  written back over S with tcgen05.st (two values per 32-bit column);
@@ -37,6 +41,7 @@ struct TcParams {
     int window;
     float scale_log2;
     int* status;
+    int one_load_per_page;             // the 5-d map of the cache is in use (else 2-d loads of 8 keys x 64 dims)
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
@@ -83,14 +88,14 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr, uint32_t sbo = 1024) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
 // MN-major operand tile (the contiguous direction is N), 128-byte swizzle: 64 elements of N contiguous per row of
-// 128 bytes, 8 rows of K per 1024-byte group (stride byte offset), blocks of 64 N-elements `lbo` bytes apart.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo) {
-    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+// 128 bytes, groups of 8 rows of K `sbo` bytes apart, blocks of 64 N-elements `lbo` bytes apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 __device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn_major) {
@@ -104,6 +109,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int HALVES = HD / 64;                      // 64-wide (128-byte) column blocks of a head
     constexpr int HALF_BYTES = 128 * 128;                // 128 rows x 128 bytes
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // one Q, K or V tile
+    constexpr int GROUP_BYTES = HALVES * 1024;           // 8 keys of a K or V tile: one swizzle atom per half of the head
     constexpr int TMEM_COLS = 512;                       // S0 | S1 | O  (128 + 128 + HD columns)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -188,10 +194,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = __shfl_sync(0xffffffffu, ok, 0);          // also orders the expect_tx before every lane's loads
                 if (!ok) break;
                 if (lane < pages_per_block) {
-                    const uint32_t dst = (kv ? v_smem : k_smem) + s * TILE_BYTES + lane * p.page_size * 128;
-                    const int row = ((page * 2 + kv) * p.n_kv + kvh) * p.page_size;
+                    const uint32_t dst = (kv ? v_smem : k_smem) + s * TILE_BYTES + lane * (p.page_size / 8) * GROUP_BYTES;
+                    const int block = (page * 2 + kv) * p.n_kv + kvh;
+                    if (p.one_load_per_page) {
+                        tma_load_5d(dst, &map_kv, 0, 0, 0, 0, block, full);
+                    } else {
+                        for (int g8 = 0; g8 < p.page_size / 8; ++g8)
 #pragma unroll
-                    for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * HALF_BYTES, &map_kv, h * 64, row, full);
+                            for (int h = 0; h < HALVES; ++h)
+                                tma_load_2d(dst + g8 * GROUP_BYTES + h * 1024, &map_kv, h * 64, block * p.page_size + g8 * 8, full);
+                    }
                 }
             }
             if (!ok) break;
@@ -209,8 +221,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const uint32_t d = tmem_base + s * 128;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-                    umma_ss(d, desc_kmajor(q_smem + off), desc_kmajor(k_smem + s * TILE_BYTES + off), idesc_qk, ks ? 1u : 0u);
+                    umma_ss(d, desc_kmajor(q_smem + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
+                            desc_kmajor(k_smem + s * TILE_BYTES + (ks >> 2) * 1024 + (ks & 3) * 32, GROUP_BYTES), idesc_qk, ks ? 1u : 0u);
                 }
                 umma_commit(bar(K_EMPTY + s));           // the K stage is free once these have read it
                 umma_commit(bar(S_FULL + s));
@@ -227,7 +239,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk)
                     umma_ts(tmem_base + 256, tmem_base + s * 128 + kk * 8,
-                            desc_mnmajor(v_smem + s * TILE_BYTES + kk * 16 * 128, HALF_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
+                            desc_mnmajor(v_smem + s * TILE_BYTES + kk * 2 * GROUP_BYTES, 1024, GROUP_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
                 umma_commit(bar(V_EMPTY + s));
                 umma_commit(bar(O_FULL));                 // completion j of this barrier: O holds blocks 0..j
             }
@@ -409,6 +421,42 @@ int cached_q_map(const void* q, long q_stride, long tokens, int n_q, int hd, int
     return 0;
 }
 
+// 5-d map of the cache: (64 dims, key within a group of 8, half of the head, group of the page, block = (page * 2 + K|V) *
+// n_kv + kv head); one box is a page's keys (or values) of one kv head.  Returns non-zero if the driver does not take it.
+int page_map(const void* cache, int num_pages, int n_kv, int page_size, int hd, CUtensorMap* out) {
+    using namespace rs_tma;
+    EncodeTiledFn enc = get_encoder();
+    if (!enc) return 1;
+    const cuuint64_t row = (cuuint64_t)hd * 2;
+    cuuint64_t dims[5] = {64, 8, (cuuint64_t)(hd / 64), (cuuint64_t)(page_size / 8), (cuuint64_t)num_pages * 2 * n_kv};
+    cuuint64_t strides[4] = {row, 128, 8 * row, (cuuint64_t)page_size * row};
+    cuuint32_t box[5] = {64, 8, (cuuint32_t)(hd / 64), (cuuint32_t)(page_size / 8), 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1;
+}
+
+struct PageMapKey { const void* cache; int num_pages, n_kv, page_size, hd; };
+struct PageMapEntry { PageMapKey key; int refused; CUtensorMap map; };
+std::vector<PageMapEntry> g_page_maps;
+std::mutex g_page_maps_mutex;
+int g_last_loads_per_page = 0;
+
+int cached_page_map(const void* cache, int num_pages, int n_kv, int page_size, int hd, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_page_maps_mutex);
+    for (auto& e : g_page_maps)
+        if (e.key.cache == cache && e.key.num_pages == num_pages && e.key.n_kv == n_kv && e.key.page_size == page_size &&
+            e.key.hd == hd) { *out = e.map; return e.refused; }
+    PageMapEntry e{PageMapKey{cache, num_pages, n_kv, page_size, hd}, 0, {}};
+    e.refused = page_map(cache, num_pages, n_kv, page_size, hd, &e.map);
+    if (g_page_maps.size() > 64) g_page_maps.clear();
+    g_page_maps.push_back(e);
+    *out = e.map;
+    return e.refused;
+}
+
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int n_work, cudaStream_t s) {
     constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 17 + 64 + 6 * ROWS * 4;
@@ -430,6 +478,9 @@ RS_EXPORT int rs_attention_prefill_tc_supported(int n_q, int n_kv, int hd, int p
     return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }
 
+// TMA loads per cache page (keys and values together) in the most recent launch: 2 with the 5-d map.
+RS_EXPORT int rs_attention_prefill_tc_loads_per_page() { return g_last_loads_per_page; }
+
 // Query tokens per CTA: the host cuts each sequence's queries into tiles of this many.
 RS_EXPORT int rs_attention_prefill_tc_q_per_cta(int n_q, int n_kv) { return ROWS / pack_of(n_q / n_kv); }
 
@@ -450,8 +501,12 @@ RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows,
     CUtensorMap mq, mkv;
     int rc = cached_q_map(q, q_stride, q_rows, n_q, hd, p.pack, &mq);
     if (rc) return rc;
-    rc = rs_tma::get_map(cache, (long)num_pages * 2 * n_kv * page_size, hd, hd, page_size, &mkv);
-    if (rc) return rc;
+    p.one_load_per_page = cached_page_map(cache, num_pages, n_kv, page_size, hd, &mkv) == 0;
+    if (!p.one_load_per_page) {
+        rc = rs_tma::get_map(cache, (long)num_pages * 2 * n_kv * page_size, hd, hd, 8, &mkv);
+        if (rc) return rc;
+    }
+    g_last_loads_per_page = p.one_load_per_page ? 2 : 2 * (hd / 64) * (page_size / 8);
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64) return launch<64>(mq, mkv, p, n_work, s);
     return launch<128>(mq, mkv, p, n_work, s);

@@ -101,7 +101,7 @@ def bench_prefill_attention(S, n_q, n_kv, hd, page, iters, once, force=""):
     args = dict(work=d(tiles), n_work=len(tiles) // 2, **common)
     us = timed(lambda i: ops.attention_prefill(cache=caches[0], force=force, **args), 1, iters, once)
     kind = ops.attention_prefill_kernel(torch.bfloat16, n_q, n_kv, hd, page, force)
-    print(f"prefill_attention [{kind}] S={S} heads {n_q}/{n_kv} hd={hd}: {us:.1f} us, {4.0 * n_q * hd * S * S / 2 / us / 1e6:.1f} "
+    print(f"prefill_attention [{kind}] S={S} heads {n_q}/{n_kv} hd={hd} page={page}: {us:.1f} us, {4.0 * n_q * hd * S * S / 2 / us / 1e6:.1f} "
           f"TFLOP/s (causal half counted)")
 
 
