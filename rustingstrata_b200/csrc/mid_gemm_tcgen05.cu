@@ -1,0 +1,469 @@
+// bfloat16 matrix product for 33 to 128 rows of activations (large decode batches, short prompt portions) on the
+// 5th-generation tensor cores, built like the skinny kernel around one job: stream the weight W[N, K] from HBM
+// exactly once, with every SM reading the same number of bytes.
+//
+//   C[m, n] (=|+=) sum_k A[m, k] * W[n, k]
+//
+// The operands are swapped with respect to the large-M kernel: 128 rows of W are the M side of tcgen05.mma and
+// the (padded) rows of A its N side, so a tile of the accumulator in tensor memory is [128 rows of W] x [MP rows
+// of A] and no tensor-core row is wasted on padding.  The product is cut into units of (128 rows of W) x (128 of
+// k); the units, in row-tile-major order, are dealt to the persistent CTAs (one per SM) in equal contiguous
+// shares ("stream-K").  In a CTA
+//   warp 0 (one lane) - TMA producer: per unit two 128 x 64 boxes of W and two MP x 64 boxes of A, 128-byte
+//                       swizzle, into a ring of stages; started before its predecessor has finished (programmatic
+//                       dependent launch), it fills the ring with W, which no kernel writes, and asks for A only
+//                       once the predecessor is done;
+//   warp 1 (one lane) - issues tcgen05.mma (M = 128, N = MP, K = 16; eight per unit), accumulator double
+//                       buffered in tensor memory, tcgen05.commit frees the stage;
+//   warps 2-5         - epilogue: tcgen05.ld of their 32 accumulator lanes (one row of W per thread).  A row tile
+//                       whose k range this CTA covers alone is finished at once; otherwise the float32 partial
+//                       goes to a workspace and bumps the tile's counter.  The contributor that arrives last
+//                       finishes the tile after its own last segment: bulk copies bring all partials into the
+//                       then idle ring at once, they are added in CTA order (fixed by the shape alone), the
+//                       epilogue is applied and the counter reset.  Nobody waits for anybody.
+// Epilogues: store bf16 | store f32 | f32 += (residual add) | SiLU(gate)*up over interleaved rows of W.
+// Every wait on an mbarrier is bounded (tma_helpers.cuh).
+//
+// Reference counterpart: gemvn_bf16 / gemm_bf16 (src/cuda/kernels.cu:826-853,1062-1231); the reference has no
+// kernel of its own for this range of rows.
+#include "tma_helpers.cuh"
+
+namespace {
+constexpr int TILE_N = 128;                // rows of W per unit = M of the MMA
+constexpr int BOX_K = 64;                  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int BOXES = 2;
+constexpr int TILE_K = BOX_K * BOXES;      // k per unit
+constexpr int UMMA_K = 16;
+constexpr int W_BOX_BYTES = TILE_N * BOX_K * 2;
+constexpr int W_BYTES = W_BOX_BYTES * BOXES;
+constexpr int THREADS = 192;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+
+struct MidParams {
+    void* C; long ldc;
+    int M, N, K;
+    int stages;
+    int vec_ok;                // rows of C allow 16-byte (f32) / 8-byte (bf16) access at every fourth column
+    float* workspace;          // [grid][2][MP][128] float32 partials
+    int* counters;             // [row tiles], zero between launches
+    int* status;
+};
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major tile, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart; descriptor version 1, layout 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// f32 accumulator, bf16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// first unit of CTA c when U units are dealt to G CTAs as evenly as possible
+__device__ __forceinline__ int first_unit(int c, int U, int G) { return c * (U / G) + (c < U % G ? c : U % G); }
+__device__ __forceinline__ int cta_of_unit(int u, int U, int G) {
+    const int base = U / G, rem = U % G;
+    return u < rem * (base + 1) ? u / (base + 1) : rem + (u - rem * (base + 1)) / base;
+}
+
+// one finished value of C: row m of A, row n of W (all 32 lanes of a warp call this together, n consecutive)
+template <int EPI>
+__device__ __forceinline__ void store_value(const MidParams& p, float v, int m, int n) {
+    if (EPI == EPI_SWIGLU_BF16) {
+        // rows of W alternate gate, up: the even lane of a pair writes
+        const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+        if ((n & 1) == 0 && n + 1 < p.N)
+            ((__nv_bfloat16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(v / (1.0f + __expf(-v)) * up);
+    } else if (n < p.N) {
+        const size_t o = (size_t)m * p.ldc + n;
+        if (EPI == EPI_STORE_BF16) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(v);
+        else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v;
+        else ((float*)p.C)[o] += v;
+    }
+}
+
+// four finished values of C: row m of A, rows n0 .. n0 + 3 of W (n0 a multiple of 4); `old` holds what C had there
+// (read by the caller ahead of time) when the epilogue accumulates
+template <int EPI>
+__device__ __forceinline__ void store_four(const MidParams& p, float4 v, float4 old, int m, int n0) {
+    if (EPI == EPI_SWIGLU_BF16) {
+        __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)m * p.ldc + (n0 >> 1);
+        const float a = v.x / (1.0f + __expf(-v.x)) * v.y, b = v.z / (1.0f + __expf(-v.z)) * v.w;
+        if (p.vec_ok && n0 + 3 < p.N) {
+            *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(a, b);
+        } else {
+            if (n0 + 1 < p.N) out[0] = __float2bfloat16_rn(a);
+            if (n0 + 3 < p.N) out[1] = __float2bfloat16_rn(b);
+        }
+    } else if (p.vec_ok && n0 + 3 < p.N) {
+        const size_t o = (size_t)m * p.ldc + n0;
+        if (EPI == EPI_STORE_BF16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)p.C + o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        } else if (EPI == EPI_STORE_F32) {
+            *reinterpret_cast<float4*>((float*)p.C + o) = v;
+        } else {
+            *reinterpret_cast<float4*>((float*)p.C + o) = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
+        }
+    } else {
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (n0 + i < p.N) {
+                const size_t o = (size_t)m * p.ldc + n0 + i;
+                if (EPI == EPI_STORE_BF16) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(e[i]);
+                else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = e[i];
+                else ((float*)p.C)[o] += e[i];
+            }
+        }
+    }
+}
+
+template <int MP, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+mid_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const MidParams p) {
+    constexpr int X_BOX_BYTES = MP * BOX_K * 2;
+    constexpr int X_BYTES = X_BOX_BYTES * BOXES;
+    constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr int TMEM_COLS = 2 * MP;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - raw);
+    const int stages = p.stages;
+    // barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2], fix; then tensor-memory base, abort flag, fix_tile[2]
+    const uint32_t bar0 = base + stages * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
+    auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * stages + b); };
+    auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * stages + 2 + b); };
+    const uint32_t fix_bar = bar0 + 8u * (2 * stages + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (size_t)stages * STAGE_BYTES + 8 * (2 * stages + 5));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* fix_tile = abort_flag + 1;                          // [2]: the tile to finish for each of my two partial segments, or -1
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = (p.K + TILE_K - 1) / TILE_K;
+    const int tiles = (p.N + TILE_N - 1) / TILE_N;
+    const int U = tiles * KB, G = gridDim.x;
+    const int u0 = first_unit(blockIdx.x, U, G), u1 = first_unit(blockIdx.x + 1, U, G);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+        *abort_flag = 0;
+        fix_tile[0] = fix_tile[1] = -1;
+        mbar_init(fix_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            pdl_launch_dependents();
+            auto load_w = [&](int s, int tile, int kb) {
+                const uint32_t dst = base + s * STAGE_BYTES;
+#pragma unroll
+                for (int b = 0; b < BOXES; ++b)
+                    tma_load_2d(dst + b * W_BOX_BYTES, &map_w, kb * TILE_K + b * BOX_K, tile * TILE_N, full_bar(s));
+            };
+            auto load_x = [&](int s, int kb) {
+                const uint32_t dst = base + s * STAGE_BYTES + W_BYTES;
+#pragma unroll
+                for (int b = 0; b < BOXES; ++b)
+                    tma_load_2d(dst + b * X_BOX_BYTES, &map_a, kb * TILE_K + b * BOX_K, 0, full_bar(s));
+            };
+            // fill the ring with weights before waiting for the kernel that writes A
+            const int ahead = min(stages, u1 - u0);
+            int tile = u0 / KB, kb = u0 % KB;
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(full_bar(i), STAGE_BYTES);
+                load_w(i, tile, kb);
+                if (++kb == KB) { kb = 0; ++tile; }
+            }
+            pdl_wait();
+            kb = u0 % KB;
+            for (int i = 0; i < ahead; ++i) {
+                load_x(i, kb);
+                if (++kb == KB) kb = 0;
+            }
+            int s = ahead == stages ? 0 : ahead; uint32_t phase = ahead == stages ? 1u : 0u;
+            for (int u = u0 + ahead; u < u1; ++u) {
+                if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status)) break;
+                mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                load_w(s, tile, kb);
+                load_x(s, kb);
+                if (++s == stages) { s = 0; phase ^= 1u; }
+                if (++kb == KB) { kb = 0; ++tile; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer: one accumulator per tile segment
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(TILE_N, MP);
+            int s = 0; uint32_t phase = 0;
+            int seg = 0;
+            bool ok = true;
+            int u = u0;
+            while (u < u1 && ok) {
+                const int kb0 = u % KB;
+                const int seg_end = min(u1, u - kb0 + KB);                 // first unit after this segment
+                const int buf = seg & 1;
+                if (!mbar_wait(tempty_bar(buf), ((seg >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * MP;
+                for (int i = 0; u < seg_end; ++u, ++i) {
+                    if (!mbar_wait(full_bar(s), phase, abort_flag, p.status)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t wst = base + s * STAGE_BYTES, xst = wst + W_BYTES;
+#pragma unroll
+                    for (int b = 0; b < BOXES; ++b) {
+                        const uint64_t dw = make_smem_desc(wst + b * W_BOX_BYTES), dx = make_smem_desc(xst + b * X_BOX_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BOX_K / UMMA_K; ++k)    // 32 bytes (>> 4 = 2) per K = 16 inside the swizzle row
+                            umma_bf16(d_tmem, dw + 2u * k, dx + 2u * k, idesc, (i | b | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));                       // stage free once these MMAs have read it
+                    if (++s == stages) { s = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(tfull_bar(buf));                 // the segment's accumulator is complete
+                ++seg;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps 2..5: thread = one row of W
+        const int quarter = warp & 3;                                // tensor-memory lanes [32 * quarter, +32)
+        const int nl = quarter * 32 + lane;                          // row of W within the tile
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        pdl_wait();                                                  // C and the workspace belong to earlier kernels until now
+        // A warp whose wait ran out keeps walking its segments without touching them, so that the named barrier of
+        // the four epilogue warps below always finds all of them.
+        bool ok = true;
+        int seg = 0;
+        int u = u0;
+        while (u < u1) {
+            const int tile = u / KB, kb0 = u % KB;
+            const int seg_end = min(u1, u - kb0 + KB);
+            const bool whole = kb0 == 0 && seg_end == u - kb0 + KB;
+            const int buf = seg & 1;
+            const int n = tile * TILE_N + nl;
+            const int tile_first = tile * KB;
+            const int slot = (u0 >= tile_first) ? 0 : 1;             // 0: the tile my range starts in
+            if (ok) ok = mbar_wait(tfull_bar(buf), (seg >> 1) & 1, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);                        // the loads below are warp-wide
+            if (ok) {
+                tc_fence_after();
+                float* mine = p.workspace + ((size_t)blockIdx.x * 2 + slot) * MP * TILE_N;
+#pragma unroll 1
+                for (int c = 0; c < MP; c += 32) {
+                    if (c >= p.M) break;
+                    uint32_t r[32];
+                    tmem_ld32(lane_base + buf * MP + c, r);
+                    tmem_ld_wait();
+                    if (whole) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c + j < p.M) store_value<EPI>(p, __uint_as_float(r[j]), c + j, n);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c + j < p.M) __stcg(mine + (size_t)(c + j) * TILE_N + nl, __uint_as_float(r[j]));
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(buf));         // the accumulator may be overwritten
+            }
+            if (!whole) {
+                // my share of this tile is in the workspace: count it.  Whoever counts last will finish the tile,
+                // but only after its own last segment, so that nobody's partial is held up by somebody's additions.
+                __threadfence();
+                epilogue_sync();
+                if (threadIdx.x == 64) {
+                    const int contributors = cta_of_unit(tile_first + KB - 1, U, G) - cta_of_unit(tile_first, U, G) + 1;
+                    fix_tile[slot] = (ok && atomicAdd(p.counters + tile, 1) == contributors - 1) ? tile : -1;
+                }
+            }
+            u = seg_end;
+            ++seg;
+        }
+        epilogue_sync();                                             // fix_tile is written; every stage of the ring is idle
+        uint32_t fix_phase = 0;
+#pragma unroll 1
+        for (int slot = 0; slot < 2; ++slot) {
+            const int tile = fix_tile[slot];
+            if (tile < 0) continue;                                  // the same for all four warps
+            // The partials of all contributors come into the idle ring with bulk copies, all in flight at once,
+            // and are added in CTA order from there.
+            const int tile_first = tile * KB;
+            const int c_first = cta_of_unit(tile_first, U, G), c_last = cta_of_unit(tile_first + KB - 1, U, G);
+            const int nc = c_last - c_first + 1;
+            int rows = (stages * STAGE_BYTES) / (nc * TILE_N * 4);   // rows of A per pass
+            if (rows > p.M) rows = p.M;
+            __threadfence();
+            for (int m0 = 0; m0 < p.M; m0 += rows) {                  // every warp makes every pass, whatever its waits said
+                const int r_now = min(rows, p.M - m0);
+                const uint32_t bytes = (uint32_t)r_now * TILE_N * 4;
+                if (threadIdx.x == 64 && ok) {
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                    mbar_expect_tx(fix_bar, bytes * nc);
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const int cslot = (first_unit(c, U, G) >= tile_first) ? 0 : 1;
+                        const float* src = p.workspace + (((size_t)c * 2 + cslot) * MP + m0) * TILE_N;
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(base + (uint32_t)(c - c_first) * bytes), "l"(src), "r"(bytes), "r"(fix_bar) : "memory");
+                    }
+                }
+                if (ok) ok = mbar_wait(fix_bar, fix_phase, abort_flag, p.status);
+                fix_phase ^= 1u;
+                if (ok) {
+                    const float4* st = reinterpret_cast<const float4*>(aligned);
+                    const int per = r_now * (TILE_N / 4);            // float4 values of one contributor
+                    // four positions per thread at a time, so that the reads of C (when the epilogue adds) are in flight together
+#pragma unroll 1
+                    for (int i0 = threadIdx.x - 64; i0 < per; i0 += 4 * 128) {
+                        float4 acc[4], old[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int i = i0 + q * 128;
+                            old[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (i < per) {
+                                acc[q] = st[i];
+                                const int m = m0 + i / (TILE_N / 4), n0 = tile * TILE_N + (i % (TILE_N / 4)) * 4;
+                                if (EPI == EPI_ADD_F32 && p.vec_ok && n0 + 3 < p.N)
+                                    old[q] = *reinterpret_cast<const float4*>((const float*)p.C + (size_t)m * p.ldc + n0);
+                            }
+                        }
+                        for (int c = 1; c < nc; ++c) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int i = i0 + q * 128;
+                                if (i < per) {
+                                    const float4 v = st[c * per + i];
+                                    acc[q].x += v.x; acc[q].y += v.y; acc[q].z += v.z; acc[q].w += v.w;
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int i = i0 + q * 128;
+                            if (i < per) store_four<EPI>(p, acc[q], old[q], m0 + i / (TILE_N / 4), tile * TILE_N + (i % (TILE_N / 4)) * 4);
+                        }
+                    }
+                }
+                epilogue_sync();                                     // the ring is read before the next pass overwrites it
+            }
+            if (threadIdx.x == 64) p.counters[tile] = 0;
+        }
+    }
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);      // let loads already issued land
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int MP, int EPI>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, MidParams p, int max_ctas, cudaStream_t s) {
+    constexpr int SB = W_BYTES + MP * TILE_K * 2;
+    constexpr int stages = SMEM_BUDGET / SB;
+    constexpr int smem = stages * SB + 1024 + 8 * (2 * stages + 5) + 64;
+    auto kern = mid_gemm_kernel<MP, EPI>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    p.stages = stages;
+    const long U = (long)((p.N + TILE_N - 1) / TILE_N) * ((p.K + TILE_K - 1) / TILE_K);
+    long grid = rs_tma::sm_count();
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    if (grid > U) grid = U;
+    return rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
+}
+
+template <int MP>
+int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const MidParams& p, int max_ctas, cudaStream_t s) {
+    switch (epi) {
+        case EPI_STORE_BF16: return launch<MP, EPI_STORE_BF16>(mw, ma, p, max_ctas, s);
+        case EPI_STORE_F32: return launch<MP, EPI_STORE_F32>(mw, ma, p, max_ctas, s);
+        case EPI_ADD_F32: return launch<MP, EPI_ADD_F32>(mw, ma, p, max_ctas, s);
+        case EPI_SWIGLU_BF16: return launch<MP, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, s);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+RS_EXPORT int rs_mid_gemm_max_rows() { return 128; }
+
+// float32 values of workspace and ints of counters a launch needs (for any M <= 128 and this N).
+RS_EXPORT long rs_mid_gemm_workspace_floats() { return (long)rs_tma::sm_count() * 2 * 128 * TILE_N; }
+RS_EXPORT long rs_mid_gemm_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
+
+// C[M, N] (=|+=) A[M, K] . W[N, K]^T for M <= 128, bf16 inputs; same epilogue codes as rs_gemm_bf16_tc.  a_rows is the
+// row capacity of A's buffer.  workspace/counters as sized above; counters must be zero before the first launch and
+// are left zero.  Launches that share a workspace must not overlap on the GPU.
+RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M, int N,
+                               int K, int epi, float* workspace, int* counters, int max_ctas, int* status, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 128 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
+        workspace == nullptr || counters == nullptr)
+        return (int)cudaErrorInvalidValue;
+    if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
+    const int mp = M <= 64 ? 64 : 128;
+    CUtensorMap mw, ma;
+    int rc = rs_tma::get_map(W, N, K, ldw, TILE_N, &mw);
+    if (rc) return rc;
+    rc = rs_tma::get_map(A, a_rows, K, lda, mp, &ma);
+    if (rc) return rc;
+    MidParams p;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.counters = counters;
+    p.status = status;
+    const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
+    p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (mp == 64) return launch_epi<64>(epi, mw, ma, p, max_ctas, s);
+    return launch_epi<128>(epi, mw, ma, p, max_ctas, s);
+}

@@ -2,7 +2,7 @@
 
     python -m rustingstrata_b200.kernels.microbench KERNEL [--m M] [--n N] [--k K] [--batch B] [--ctx S] ...
 
-KERNEL: skinny | gemm | decode_attention | prefill_attention | rmsnorm | qk_norm_rope | sample.
+KERNEL: skinny | mid | gemm | decode_attention | prefill_attention | rmsnorm | qk_norm_rope | sample.
 The launches are captured in a CUDA graph and the replay is timed with CUDA events, so the figure is
 device time per launch without host overhead; weights (or caches) rotate over buffers larger than the
 L2 cache so every launch reads from HBM.  With ``--once`` it launches the kernel a few times without a
@@ -59,6 +59,8 @@ def bench_linear(kind: str, M: int, N: int, K: int, epilogue: str, bn: int, iter
         out, kw = torch.zeros(rows, N // 2, device=DEV, dtype=torch.bfloat16), dict(swiglu=True)
     if kind == "skinny":
         us = timed(lambda i: ops.skinny_gemm_bf16(a, ws[i], out, M, **kw), nb, iters, once)
+    elif kind == "mid":
+        us = timed(lambda i: ops.mid_gemm_bf16(a, ws[i], out, M, **kw), nb, iters, once)
     else:
         us = timed(lambda i: ops.gemm_bf16_tc(a, ws[i], out, M, bn=bn, **kw), nb, iters, once)
     print(f"{kind} M={M} N={N} K={K} {epilogue}: {us:.1f} us, weights {N * K * 2 / us / 1e6:.2f} TB/s, "
@@ -107,7 +109,7 @@ def bench_prefill_attention(S, n_q, n_kv, hd, page, iters, once, force=""):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("kernel", choices=["skinny", "gemm", "decode_attention", "prefill_attention", "rmsnorm", "qk_norm_rope",
+    ap.add_argument("kernel", choices=["skinny", "mid", "gemm", "decode_attention", "prefill_attention", "rmsnorm", "qk_norm_rope",
                                        "sample"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
@@ -125,7 +127,7 @@ def main(argv=None) -> int:
     ap.add_argument("--force", default="", help="prefill_attention: tc | mma | simt instead of the default choice")
     ap.add_argument("--once", action="store_true", help="a few plain launches, no graph and no timing (for profilers)")
     a = ap.parse_args(argv)
-    if a.kernel in ("skinny", "gemm"):
+    if a.kernel in ("skinny", "mid", "gemm"):
         bench_linear(a.kernel, a.m, a.n, a.k, a.epilogue, a.bn, a.iters, a.once)
     elif a.kernel == "decode_attention":
         bench_decode_attention(a.batch, a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size, a.iters, a.once)

@@ -229,6 +229,9 @@ def bf16lib():
         lib.rs_skinny_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                             c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_skinny_gemm_workspace_floats.restype = c_long
+        lib.rs_mid_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                         c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        lib.rs_mid_gemm_workspace_floats.restype = c_long
         lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -335,6 +338,37 @@ def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n
                                          _ptr(counters), max_ctas, _ptr(status), _stream()), "skinny_gemm_bf16")
 
 
+MID_MAX_ROWS = 128       # what the stream-K tcgen05 kernel takes; the engine uses it from SKINNY_ROWS + 1 rows up to here
+_MID_SCRATCH = {}
+
+
+def _mid_scratch(device):
+    """Workspace and tile counters of the stream-K tcgen05 product, one pair per device, made at the first call."""
+    sc = _MID_SCRATCH.get(device)
+    if sc is None:
+        ws = torch.empty(int(bf16lib().rs_mid_gemm_workspace_floats()), dtype=torch.float32, device=device)
+        counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        sc = _MID_SCRATCH[device] = (ws, counters)
+    return sc
+
+
+def mid_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
+                  swiglu: bool = False, status: Optional[torch.Tensor] = None, max_ctas: int = 0) -> None:
+    """out[:n_rows] (=|+=) a[:n_rows] @ weight.T for n_rows <= 128 on the tensor cores with the operands swapped
+    (rows of the weight fill the 128-row side of the MMA) and the work dealt to the SMs in equal shares of k
+    (csrc/mid_gemm_tcgen05.cu)."""
+    N, K = _check_product(a, weight, out, n_rows, swiglu)
+    if n_rows > MID_MAX_ROWS or not tensor_core_shape_ok(a, weight) or N > 128 * (1 << 16):
+        raise KernelError(f"mid_gemm_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
+                          f"{tuple(weight.shape)} {weight.dtype}: at most {MID_MAX_ROWS} rows, bfloat16, 16-byte aligned")
+    if status is None:
+        status = _default_status(a.device)
+    ws, counters = _mid_scratch(a.device)
+    _check(bf16lib().rs_mid_gemm_bf16(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
+                                      out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), _ptr(ws),
+                                      _ptr(counters), max_ctas, _ptr(status), _stream()), "mid_gemm_bf16")
+
+
 _STATUS = {}
 
 
@@ -349,11 +383,14 @@ def _default_status(device) -> torch.Tensor:
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
            status: Optional[torch.Tensor] = None) -> None:
     """The engine's matrix product: the tensor-core kernels for bfloat16 operands whose rows are 16-byte
-    aligned (skinny kernel up to 32 rows, tcgen05 kernel above), the CUDA-core kernel for everything else
+    aligned (skinny kernel up to 32 rows, stream-K tcgen05 kernel up to 128, tiled tcgen05 kernel above), the
+    CUDA-core kernel for everything else
     (the 32-bit engine, float32-stored weights, odd widths)."""
     if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
         if n_rows <= SKINNY_ROWS:
             skinny_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)
+        elif n_rows <= MID_MAX_ROWS:
+            mid_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)
         else:
             gemm_bf16_tc(a, weight, out, n_rows, accumulate, status=status)
     else:
@@ -365,6 +402,8 @@ def linear_swiglu(a: torch.Tensor, weight_interleaved: torch.Tensor, out: torch.
     """out[:, j] = silu(a @ w[2j]) * (a @ w[2j+1]) in one kernel; only for shapes ``tensor_core_shape_ok`` takes."""
     if n_rows <= SKINNY_ROWS:
         skinny_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
+    elif n_rows <= MID_MAX_ROWS:
+        mid_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
     else:
         gemm_bf16_tc(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
 

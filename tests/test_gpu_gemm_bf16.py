@@ -138,6 +138,63 @@ def test_streaming_skinny_kernel_any_split_of_the_work(max_ctas):
         assert err(f1, want) < 1e-5 and torch.equal(f1, f2)
 
 
+@pytest.mark.parametrize("M", [1, 33, 40, 64, 65, 100, 128])
+@pytest.mark.parametrize("N,K", [(128, 128), (100, 72), (4096, 4096), (6144, 4096), (1000, 1000), (24576, 4096),
+                                 (4096, 12288), (151936, 256), (70, 8), (130, 136)])
+def test_stream_k_tcgen05_kernel(M, N, K):
+    """The kernel for 33 to 128 rows: every epilogue, rows beyond M untouched, widths and depths that end inside a
+    tile, tiles finished by one CTA and tiles pieced together from several."""
+    o = ops()
+    a, w = make(M, N, K, cap=M + 2, seed=M)
+    want = a[:M].double() @ w.double().T
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M + 2, N), 3.0, device=DEV, dtype=torch.bfloat16)
+    o.mid_gemm_bf16(a, w, out, M, status=st)
+    assert err(out[:M], want) < 6e-3 and torch.all(out[M:] == 3.0)
+    f = torch.full((M + 2, N), 3.0, device=DEV)
+    o.mid_gemm_bf16(a, w, f, M, status=st)
+    assert err(f[:M], want) < 1e-5 and torch.all(f[M:] == 3.0)
+    base = torch.randn(M + 2, N, device=DEV)
+    acc = base.clone()
+    o.mid_gemm_bf16(a, w, acc, M, accumulate=True, status=st)
+    assert err(acc[:M], base[:M].double() + want) < 1e-5 and torch.equal(acc[M:], base[M:])
+    if N % 2 == 0:
+        sw = torch.zeros(M + 2, N // 2, device=DEV, dtype=torch.bfloat16)
+        o.mid_gemm_bf16(a, w, sw, M, swiglu=True, status=st)
+        assert err(sw[:M], silu_mul(want)) < 8e-3 and torch.all(sw[M:] == 0)
+    assert st.item() == 0
+
+
+@pytest.mark.parametrize("max_ctas", [1, 2, 3, 7, 50, 147])
+def test_stream_k_tcgen05_kernel_any_split_of_the_work(max_ctas):
+    o = ops()
+    for (M, N, K) in ((40, 320, 1024), (64, 200, 4096), (128, 4096, 640), (100, 515, 2056)):
+        a, w = make(M, N, K, seed=7)
+        want = a.double() @ w.double().T
+        f1 = torch.zeros(M, N, device=DEV)
+        f2 = torch.zeros(M, N, device=DEV)
+        o.mid_gemm_bf16(a, w, f1, M, max_ctas=max_ctas)
+        o.mid_gemm_bf16(a, w, f2, M, max_ctas=max_ctas)
+        assert err(f1, want) < 1e-5 and torch.equal(f1, f2)
+        sw = torch.zeros(M, N // 2, device=DEV, dtype=torch.bfloat16)
+        if N % 2 == 0:
+            o.mid_gemm_bf16(a, w, sw, M, swiglu=True, max_ctas=max_ctas)
+            assert err(sw, silu_mul(want)) < 8e-3
+
+
+def test_stream_k_tcgen05_rows_do_not_depend_on_the_batch():
+    o = ops()
+    a, w = make(64, 2048, 4096, seed=5)
+    g = torch.zeros(64, 2048, device=DEV)
+    o.mid_gemm_bf16(a, w, g, 64)
+    part = torch.zeros(40, 2048, device=DEV)
+    o.mid_gemm_bf16(a[10:50].contiguous(), w, part, 40)
+    assert torch.equal(part, g[10:50])                   # same k order whatever the batch
+    t = torch.zeros(64, 2048, device=DEV)
+    o.gemm_bf16_tc(a, w, t, 64)
+    assert err(g, t.double()) < 2e-5
+
+
 def test_skinny_and_tcgen05_agree_and_rows_do_not_depend_on_the_batch():
     o = ops()
     a, w = make(32, 2048, 4096, seed=5)
