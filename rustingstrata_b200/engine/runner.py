@@ -230,7 +230,7 @@ class ModelRunner:
         if device_tokens is not None and (device_tokens.dtype != torch.int32 or device_tokens.numel() < T
                                           or not device_tokens.is_cuda):
             raise StepError("device_tokens must be int32 on the device with one id per token")
-        graphable = self.use_graphs and bool((q_lens == 1).all())
+        graphable = self.use_graphs and self.model.capturable and bool((q_lens == 1).all())
         try:
             ctx, layout = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R, graphable)
 

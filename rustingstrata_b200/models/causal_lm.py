@@ -85,6 +85,11 @@ class CausalLM:
         yield self.final_norm
         yield self.head
 
+    @property
+    def capturable(self) -> bool:
+        """Whether a step of this model may be replayed from a CUDA graph (every part allows it)."""
+        return all(p.capturable for p in self.parts())
+
     def tensor_needs(self) -> Dict[str, TensorNeed]:
         needs: Dict[str, TensorNeed] = {}
         for p in self.parts():

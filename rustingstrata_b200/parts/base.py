@@ -123,6 +123,10 @@ class Part:
     """Base of all parts."""
     category = ""
     kind = ""
+    # Whether forward() only enqueues work whose shape and addresses depend on the step's layout alone (no read of
+    # device results on the host, no host loop over the batch's contents).  A step is captured into a CUDA graph
+    # only if every part of the model says so; a part that needs the host says False and its model runs eagerly.
+    capturable = True
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         self.spec = spec

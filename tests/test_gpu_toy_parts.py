@@ -22,7 +22,9 @@ def define_toy():
     @register_part("mixer", "toy_decay_sum", replace=True)
     class DecaySum(Mixer):
         """out_t = W s_t with s_t = decay * s_{t-1} + h_t: a recurrent mixer whose only memory is a
-        fixed-size state per request (no cache pages)."""
+        fixed-size state per request (no cache pages).  Its forward loops over the batch on the host, so it
+        tells the engine not to capture steps into CUDA graphs."""
+        capturable = False
 
         def __init__(self, spec, runtime, position=None):
             super().__init__(spec, runtime)
@@ -174,3 +176,167 @@ def test_toy_architecture_with_stateful_mixer(tmp_path, dtype):
         unregister_architecture("ToyDecayLM")
         unregister_part("mixer", "toy_decay_sum")
         unregister_part("feed_forward", "toy_scale")
+
+
+# ----------------------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, again defined here only.
+
+def define_routed():
+    from rustingstrata_b200.config import register_architecture
+    from rustingstrata_b200.parts import (FeedForward, LayerCall, LayerSpec, ModelSpec, PartSpec, PositionEncoding,
+                                          TensorNeed, register_part)
+    from rustingstrata_b200.kernels import ops
+
+    @register_part("feed_forward", "toy_top1_of_n", replace=True)
+    class TopOne(FeedForward):
+        """Every token goes to the one expert its router logit (float32) is largest for; an expert is a matrix
+        followed by SiLU.  The tokens of an expert are gathered, multiplied with the package's product and
+        scattered back into the residual.  Which tokens go where is read back on the host, so steps of a model
+        with this part are not captured into CUDA graphs."""
+        capturable = False
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.hidden, self.n = int(spec.params["hidden"]), int(spec.params["experts"])
+
+        def tensor_needs(self):
+            needs = {self.spec.tensors["router"]: TensorNeed((self.n, self.hidden))}
+            for e in range(self.n):
+                needs[f"{self.spec.tensors['experts']}.{e}"] = TensorNeed((self.hidden, self.hidden))
+            return needs
+
+        def load(self, tensors):
+            self.router = tensors[self.spec.tensors["router"]]
+            self.experts = [tensors[f"{self.spec.tensors['experts']}.{e}"] for e in range(self.n)]
+
+        def forward(self, h, residual, ctx):
+            T = ctx.n_tokens
+            logits = torch.zeros(T, self.n, device=h.device, dtype=torch.float32)
+            ops.linear(h, self.router, logits, T)
+            choice = logits.argmax(dim=1)
+            for e in range(self.n):
+                idx = torch.nonzero(choice == e).flatten()
+                if idx.numel() == 0:
+                    continue
+                x = h[idx].contiguous()
+                y = torch.zeros(idx.numel(), self.hidden, device=h.device, dtype=torch.float32)
+                ops.linear(x, self.experts[e], y, idx.numel())
+                residual[idx] += torch.nn.functional.silu(y)
+
+    @register_part("position", "toy_squeezed_rope", replace=True)
+    class SqueezedRope(PositionEncoding):
+        """Rotation angles of position / squeeze: the same table layout as the package's rotary encoding, which is
+        all the attention kernels ask of a position encoding."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.n_rot, self.base, self.squeeze = int(spec.params["n_rot"]), float(spec.params["base"]), float(spec.params["squeeze"])
+
+        @property
+        def cos_sin(self):
+            return self.runtime.shared(("toy_squeezed_rope", self.n_rot, self.base, self.squeeze), self._table)
+
+        def _table(self):
+            half = self.n_rot // 2
+            inv = np.power(self.base, -2.0 * np.arange(half, dtype=np.float64) / self.n_rot)
+            theta = (np.arange(self.runtime.max_positions, dtype=np.float64) / self.squeeze)[:, None] * inv[None, :]
+            return torch.from_numpy(np.concatenate([np.cos(theta), np.sin(theta)], axis=1).astype(np.float32)).to(self.runtime.device)
+
+    class RoutedConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d, where=""):
+            return cls(dict(d))
+
+    def build(cfg):
+        d = cfg.d
+        H, V = d["hidden_size"], d["vocab_size"]
+        norm = lambda n: PartSpec("rmsnorm", {"width": H, "eps": d["eps"]}, {"weight": n})  # noqa: E731
+        layers = []
+        for i in range(d["layers"]):
+            mixer = PartSpec("paged_attention", {"hidden": H, "n_heads": 3, "n_kv_heads": 3, "head_dim": 16, "qk_norm": False,
+                                                 "window": 9 if i == 1 else None},
+                             {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+            pos = PartSpec("toy_squeezed_rope", {"n_rot": 16, "base": 30.0, "squeeze": 1.0 + i})
+            ff = PartSpec("toy_top1_of_n", {"hidden": H, "experts": d["experts"]}, {"router": f"l{i}.router", "experts": f"l{i}.expert"})
+            layers.append(LayerSpec(PartSpec("pre_norm", {"hidden": H}), mixer, norm(f"l{i}.n1"), ff, norm(f"l{i}.n2"), pos))
+        return ModelSpec("routed", V, H, d["max_positions"], PartSpec("token_table", {"vocab": V, "width": H}, {"weight": "emb"}),
+                         tuple(layers), tuple(LayerCall(i) for i in range(d["layers"])), norm("fn"),
+                         PartSpec("linear", {"vocab": V, "width": H}, {"weight": "head"}))
+
+    register_architecture("ToyRoutedLM", RoutedConfig, build, replace=True)
+
+
+ROUTED = {"architectures": ["ToyRoutedLM"], "vocab_size": 61, "hidden_size": 48, "layers": 2, "experts": 3, "eps": 1e-5,
+          "max_positions": 96}
+
+
+def plain_routed(w, toks):
+    import plain_qwen3 as P
+    d = ROUTED
+    x = w["emb"][np.asarray(toks)]
+    T = len(toks)
+    for i in range(d["layers"]):
+        h = P.rms_norm(x, w[f"l{i}.n1"], d["eps"])
+        q = (h @ w[f"l{i}.q_proj"].T).reshape(T, 3, 16)
+        k = (h @ w[f"l{i}.k_proj"].T).reshape(T, 3, 16)
+        v = (h @ w[f"l{i}.v_proj"].T).reshape(T, 3, 16)
+        pos = np.arange(T) / (1.0 + i)
+        q, k = P.rope_neox(q, pos, 16, 30.0), P.rope_neox(k, pos, 16, 30.0)
+        x = x + P.attention_scores(q, k, v, 3, window=9 if i == 1 else None).reshape(T, 48) @ w[f"l{i}.o_proj"].T
+        h = P.rms_norm(x, w[f"l{i}.n2"], d["eps"])
+        choice = np.argmax(h @ w[f"l{i}.router"].T, axis=1)
+        y = np.stack([P.silu(h[t] @ w[f"l{i}.expert.{choice[t]}"].T) for t in range(T)])
+        x = x + y
+    return P.rms_norm(x, w["fn"], d["eps"]) @ w["head"].T
+
+
+def test_toy_architecture_with_routed_feed_forward_and_its_own_position_encoding(tmp_path):
+    import plain_qwen3 as P
+    from rustingstrata_b200.config import EngineConfig, unregister_architecture
+    from rustingstrata_b200.engine import ModelRunner, StepEntry
+    from rustingstrata_b200.models import manifest_for
+    from rustingstrata_b200.parts import unregister_part
+    from rustingstrata_b200.weights import write_random_model
+    define_routed()
+    try:
+        d = str(tmp_path / "routed")
+        m = manifest_for(ROUTED)
+        assert "l0.router" in m and "l1.expert.2" in m and "l0.gate_proj" not in m
+        write_random_model(d, ROUTED, m, seed=9, std=0.2, norm_std=0.1)
+        w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+        runner = ModelRunner.from_dir(d, EngineConfig(dtype="float32", page_size=4, num_pages=40, max_seqs=4,
+                                                      max_batch_tokens=128, max_logit_rows=128))
+        assert len(runner.model.cache_groups) == 2                     # all keys | a window of 9
+        toks = {r: random_tokens(61, n, 40 + i) for i, (r, n) in enumerate((("a", 50), ("b", 37)))}
+        ref = {r: plain_routed(w, t) for r, t in toks.items()}
+        got = {r: {} for r in toks}
+
+        def step(entries):
+            logits = runner.step([StepEntry(r, toks[r][s:s + n], list(range(n))) for r, s, n in entries]).cpu().numpy()
+            runner.check_status()
+            k = 0
+            for r, s, n in entries:
+                for i in range(n):
+                    got[r][s + i] = logits[k]
+                    k += 1
+        step([("a", 0, 21), ("b", 0, 2)])
+        step([("a", 21, 1), ("b", 2, 30)])
+        step([("a", 22, 28), ("b", 32, 1)])
+        assert not runner.model.capturable
+        for i in range(33, 37):
+            step([("b", i, 1)])                                        # the same layout again and again: still run eagerly
+        assert runner.graph_replays == 0
+        for r in got:
+            rows = np.stack([got[r][i] for i in range(len(toks[r]))])
+            # a router logit that is a near-tie may fall the other way in float32; the seed is chosen so that none is
+            assert rel_err(rows, ref[r]) < 5e-6, r
+        for r in toks:
+            runner.release(r)
+        runner.cache.check()
+    finally:
+        unregister_architecture("ToyRoutedLM")
+        unregister_part("feed_forward", "toy_top1_of_n")
+        unregister_part("position", "toy_squeezed_rope")
