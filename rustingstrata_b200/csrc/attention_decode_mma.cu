@@ -371,31 +371,89 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
     __syncthreads();
 }
 
-// out[token of seq, head, :] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in ascending order
-template <int HD>
-__global__ void decode_merge_kernel(const DecodeParams p) {
-    const int w = blockIdx.x, h = blockIdx.y;
+// out[token of seq, head, :] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+// The splits are added in four interleaved chains (split s goes to chain s mod 4, each chain in ascending order)
+// that meet as (c0 + c1) + (c2 + c3): the order depends on the number of splits alone, that is on the sequence's
+// length, never on the batch.  One CTA per (sequence, head).  TG = 4: four threads per head dim, one per chain (small
+// batches: many loads in flight); TG = 1: one thread per head dim runs all four chains (large batches: small CTAs).
+// Both give the same bits.
+constexpr int MERGE_CHAINS = 4;
+constexpr int MERGE_MAX_SPLITS = 512;      // weights kept in shared memory; longer sequences go in rounds of this many
+template <int HD, int TG>
+__global__ void __launch_bounds__(TG * HD) decode_merge_kernel(const DecodeParams p) {
+    constexpr int NT = TG * HD;
+    __shared__ float wgt[MERGE_MAX_SPLITS], wl[MERGE_MAX_SPLITS];
+    __shared__ float red[NT / 32];
+    __shared__ float part[2][MERGE_CHAINS][HD];
+    const int w = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int d = tid % HD, g = tid / HD;
     pdl_launch_dependents();
     pdl_wait();
-    const int seq = p.work[w];
-    const int kv_len = p.kv_len[seq];
+    const int seq = __ldg(p.work + w);
+    const int kv_len = __ldg(p.kv_len + seq);
     const int key_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
     const int n_splits = (kv_len + SPLIT - 1) / SPLIT - key_lo / SPLIT;
-    const float* base = p.partial + ((size_t)p.split_start[w] * p.n_q + h) * (HD + 2);
+    const float* base = p.partial + ((size_t)__ldg(p.split_start + w) * p.n_q + h) * (HD + 2);
     const size_t stride = (size_t)p.n_q * (HD + 2);
+    // the row's maximum over all splits
     float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ld_dep(base + s * stride + HD));
-    __nv_bfloat16* dst = p.out + (size_t)p.q_start[seq] * p.out_stride + (size_t)h * HD;
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float* ps = base + s * stride;
-            const float e = fast_exp2(ld_dep(ps + HD) - M);
-            num = fmaf(ld_dep(ps + d), e, num);
-            den = fmaf(ld_dep(ps + HD + 1), e, den);
+    for (int s = tid; s < n_splits; s += NT) M = fmaxf(M, ld_dep(base + s * stride + HD));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if ((tid & 31) == 0) red[tid >> 5] = M;
+    __syncthreads();
+    M = red[0];
+#pragma unroll
+    for (int i = 1; i < NT / 32; ++i) M = fmaxf(M, red[i]);
+    float num[MERGE_CHAINS / TG], den[MERGE_CHAINS / TG];
+#pragma unroll
+    for (int c = 0; c < MERGE_CHAINS / TG; ++c) num[c] = den[c] = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += MERGE_MAX_SPLITS) {
+        const int n = min(MERGE_MAX_SPLITS, n_splits - s0);
+        const float* ps = base + (size_t)s0 * stride;
+        __syncthreads();
+        for (int s = tid; s < n; s += NT) {
+            const float e = fast_exp2(ld_dep(ps + s * stride + HD) - M);
+            wgt[s] = e;
+            wl[s] = e * ld_dep(ps + s * stride + HD + 1);
         }
-        dst[d] = __float2bfloat16_rn(num / den);
+        __syncthreads();
+        if (TG == MERGE_CHAINS) {
+            for (int i = g; i < n; i += MERGE_CHAINS * 8) {               // my chain: splits g, g + 4, ...; eight loads in flight
+                float a[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int s = i + MERGE_CHAINS * j;
+                    a[j] = s < n ? ld_dep(ps + s * stride + d) : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int s = i + MERGE_CHAINS * j;
+                    if (s < n) { num[0] = fmaf(a[j], wgt[s], num[0]); den[0] += wl[s]; }
+                }
+            }
+        } else {
+            for (int i = 0; i < n; i += 16) {                              // all chains: sixteen loads in flight
+                float a[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) a[j] = i + j < n ? ld_dep(ps + (i + j) * stride + d) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (i + j < n) { num[j % MERGE_CHAINS] = fmaf(a[j], wgt[i + j], num[j % MERGE_CHAINS]); den[j % MERGE_CHAINS] += wl[i + j]; }
+            }
+        }
     }
+    float nn, dd;
+    if (TG == MERGE_CHAINS) {
+        part[0][g][d] = num[0]; part[1][g][d] = den[0];
+        __syncthreads();
+        nn = (part[0][0][d] + part[0][1][d]) + (part[0][2][d] + part[0][3][d]);
+        dd = (part[1][0][d] + part[1][1][d]) + (part[1][2][d] + part[1][3][d]);
+    } else {
+        nn = (num[0] + num[MERGE_CHAINS / TG > 1 ? 1 : 0]) + (num[MERGE_CHAINS / TG > 2 ? 2 : 0] + num[MERGE_CHAINS / TG > 3 ? 3 : 0]);
+        dd = (den[0] + den[MERGE_CHAINS / TG > 1 ? 1 : 0]) + (den[MERGE_CHAINS / TG > 2 ? 2 : 0] + den[MERGE_CHAINS / TG > 3 ? 3 : 0]);
+    }
+    if (g == 0) p.out[(size_t)__ldg(p.q_start + seq) * p.out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(nn / dd);
 }
 
 // 5-d map of the cache: (64 dims, token of the page, half of the head, K|V, block = page * 2 * n_kv + kv head); one
@@ -453,7 +511,10 @@ int launch(const CUtensorMap& mkv, DecodeParams p, cudaStream_t s) {
     const int grid = p.total < sms ? p.total : sms;
     int rc = rs_launch_pdl(kern, dim3(grid), dim3((p.groups * GROUP_WARPS + 2) * 32), smem, s, mkv, p);
     if (rc != 0) return rc;
-    return rs_launch_pdl(decode_merge_kernel<HD>, dim3(p.n_work, p.n_q), dim3(HD >= 128 ? 128 : 64), 0, s, p);
+    // a small batch: four threads per head dim; else small CTAs (the same bits either way)
+    if ((long)p.n_work * p.n_q <= 1024)
+        return rs_launch_pdl(decode_merge_kernel<HD, MERGE_CHAINS>, dim3(p.n_work, p.n_q), dim3(MERGE_CHAINS * HD), 0, s, p);
+    return rs_launch_pdl(decode_merge_kernel<HD, 1>, dim3(p.n_work, p.n_q), dim3(HD), 0, s, p);
 }
 }  // namespace
 

@@ -323,6 +323,44 @@ def test_decode_tensor_core_kernel_agrees_with_the_cuda_core_kernel(n_q, n_kv, h
     close(fast, slow.double().cpu(), 1.5e-2)
 
 
+def test_decode_result_of_a_long_sequence_does_not_depend_on_the_batch_around_it():
+    """A 5,000-key sequence alone (the merge kernel runs four threads per head dim) and beside 150 short ones (one
+    thread per head dim, and its items land on other CTAs): the same bits."""
+    from rustingstrata_b200.parts.attention import SPLIT_KEYS, decode_splits
+    o = ops()
+    n_q, n_kv, hd, page, long_kv = 8, 2, 64, 16, 5000
+    g = torch.Generator().manual_seed(11)
+    width = (long_kv + page - 1) // page
+    n_pages = width + 150 * 2
+    cache = (torch.randn(n_pages, 2, n_kv, page, hd, generator=g)).to(torch.bfloat16).to(DEV)
+    q_all = torch.randn(151, n_q * hd, generator=g).to(torch.bfloat16).to(DEV)
+    table = torch.zeros(151, width, dtype=torch.int32)
+    table[0] = torch.arange(width, dtype=torch.int32)
+    for s in range(1, 151):
+        table[s, :2] = torch.tensor([width + 2 * (s - 1), width + 2 * (s - 1) + 1], dtype=torch.int32)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)  # noqa: E731
+    outs = []
+    for n in (1, 151):
+        kv_lens = np.array([long_kv] + [20] * (n - 1), np.int32)
+        splits = decode_splits(kv_lens, 0)
+        ss = np.zeros(n + 1, np.int32)
+        ss[1:] = np.cumsum(splits)
+        out = torch.zeros(n, n_q * hd, device=DEV, dtype=torch.bfloat16)
+        st = status()
+        o.attention_decode(q=q_all[:n].contiguous(), out=out, cache=cache, block_table=table[:n].contiguous().to(DEV),
+                           q_start=dev(np.arange(n + 1)), kv_len=dev(kv_lens), work=dev(np.arange(n)), n_work=n, n_q=n_q,
+                           n_kv=n_kv, head_dim=hd, page_size=page, window=0, scale=1 / math.sqrt(hd), status=st,
+                           split_keys=SPLIT_KEYS, max_splits=int(splits.max()), split_start=dev(ss), total_splits=int(ss[-1]),
+                           partial=torch.empty(o.attention_partial_floats(int(ss[-1]), n_q, hd), device=DEV))
+        assert st.item() == 0
+        outs.append(out[0].clone())
+    assert torch.equal(outs[0], outs[1])
+    k = cache[:width, 0].permute(0, 2, 1, 3).reshape(width * page, n_kv, hd)[:long_kv].double().cpu()
+    v = cache[:width, 1].permute(0, 2, 1, 3).reshape(width * page, n_kv, hd)[:long_kv].double().cpu()
+    want = ref_attention(q_all[0].double().cpu().view(n_q, hd), k, v, long_kv - 1, n_kv, 0, 1 / math.sqrt(hd))
+    close(outs[0].view(1, n_q, hd), want.view(1, n_q, hd), 1.5e-2)
+
+
 @pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (6, 2, 32, 4), (16, 1, 64, 8), (3, 3, 96, 16),
                                               (10, 2, 64, 16), (40, 1, 64, 16)])
 @pytest.mark.parametrize("window", [0, 70])
