@@ -59,7 +59,7 @@ struct DecodeParams {
     int one_load_per_page;             // the 5-d map is in use
 };
 
-struct Item { int w, kvh, split_local, seq, key_lo, key_hi, k_base; bool live; };
+struct Item { int w, kvh, split_local, seq, key_lo, key_hi, k_base, kv_len; bool live; };
 
 // The metadata arrays are uploaded before the step's first kernel, so the read-only path is safe for them.
 __device__ __forceinline__ Item decode_item(const DecodeParams& p, int id) {
@@ -70,6 +70,7 @@ __device__ __forceinline__ Item decode_item(const DecodeParams& p, int id) {
     it.w = r / p.n_kv;
     it.seq = __ldg(p.work + it.w);
     const int kv_len = __ldg(p.kv_len + it.seq);
+    it.kv_len = kv_len;
     const int lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
     const int split = lo / SPLIT + it.split_local;
     it.key_lo = max(lo, split * SPLIT);
@@ -129,7 +130,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
         *reinterpret_cast<uint4*>(aligned + (size_t)stages * STAGE_BYTES + (size_t)i * 16) = make_uint4(0, 0, 0, 0);
     __syncthreads();
     pdl_launch_dependents();
-    pdl_wait();                                      // the query and the new key and value come from the previous kernel
+    // The query and the new token's key and value come from the previous kernel: every role waits for it before it
+    // touches them; the producer first starts the loads that cannot hold the new token.
 
     if (warp == producer_warp) {
         // ------------------------------------------------------------ producer
@@ -147,6 +149,45 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
             for (int i = 0; i < QV; ++i)
                 if (lane + 32 * i < nvec) qv[i] = ld_dep(src + lane + 32 * i);
         };
+        auto load_pages = [&](const Item& it, int page, int s) {
+            if (lane < pages_per_item) {
+                const uint32_t dst = base + s * STAGE_BYTES + lane * page_block;
+                if (p.one_load_per_page) {
+                    tma_load_5d(dst, &map_kv, 0, 0, 0, 0, page * 2 * p.n_kv + it.kvh, full_bar(s));
+                } else {
+#pragma unroll
+                    for (int kv = 0; kv < 2; ++kv) {
+                        const int row = ((page * 2 + kv) * p.n_kv + it.kvh) * p.page_size;
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h)
+                            tma_load_2d(dst + (kv * HALVES + h) * piece, &map_kv, h * 64, row, full_bar(s));
+                    }
+                }
+            }
+        };
+        auto stage_of = [&](int n) { return (n % p.groups) * p.depth + (n / p.groups) % p.depth; };
+        // Before waiting for the previous kernel: keys and values of this CTA's first items, as far as their splits
+        // end before the position that kernel is writing (the sequence's last).  Their stages are fresh.
+        int early = 0;
+        {
+            Item it;
+            int id_e = next_live(p, blockIdx.x, it);
+            while (id_e < p.total && early < stages && it.k_base + SPLIT < it.kv_len) {
+                const int kpos = it.k_base + lane * p.page_size;
+                int pg = 0;
+                if (lane < pages_per_item && kpos < it.key_hi && kpos + p.page_size > it.key_lo)
+                    pg = __ldg(p.block_table + (size_t)it.seq * p.table_stride + kpos / p.page_size);
+                if (pg < 0 || pg >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); pg = 0; }
+                const int s = stage_of(early);
+                if (lane == 0)
+                    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(STAGE_BYTES) : "memory");
+                __syncwarp();                        // the byte count is expected before any lane's load can land
+                load_pages(it, pg, s);
+                ++early;
+                id_e = next_live(p, id_e + gridDim.x, it);
+            }
+        }
+        pdl_wait();
         Item cur, nxt;
         int page, page_n = 0;
         uint4 qv[QV], qn[QV];
@@ -156,11 +197,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
             const int id_n = next_live(p, id + gridDim.x, nxt);
             if (id_n < p.total) fetch(nxt, page_n, qn);
             const int k = n / p.groups;
-            const int s = (n % p.groups) * p.depth + k % p.depth;
+            const int s = stage_of(n);
             const uint32_t parity = (uint32_t)(k / p.depth) & 1u;
             if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
+            const bool loaded = n < early;           // its keys and values are already on their way
             int ok = 1;
-            if (lane == 0) ok = mbar_wait(empty_bar(s), parity ^ 1u, abort_flag, p.status) ? 1 : 0;
+            if (lane == 0 && !loaded) ok = mbar_wait(empty_bar(s), parity ^ 1u, abort_flag, p.status) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             const uint32_t qdst = q0 + s * Q_BYTES;
@@ -174,22 +216,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
                 }
             }
             __syncwarp();                            // every lane's query rows are written before lane 0 arrives
-            if (lane == 0) mbar_expect_tx(full_bar(s), STAGE_BYTES);
-            __syncwarp();                            // ... and the byte count is expected before any lane's load can land
-            if (lane < pages_per_item) {
-                const uint32_t dst = base + s * STAGE_BYTES + lane * page_block;
-                if (p.one_load_per_page) {
-                    tma_load_5d(dst, &map_kv, 0, 0, 0, 0, page * 2 * p.n_kv + cur.kvh, full_bar(s));
-                } else {
-#pragma unroll
-                    for (int kv = 0; kv < 2; ++kv) {
-                        const int row = ((page * 2 + kv) * p.n_kv + cur.kvh) * p.page_size;
-#pragma unroll
-                        for (int h = 0; h < HALVES; ++h)
-                            tma_load_2d(dst + (kv * HALVES + h) * piece, &map_kv, h * 64, row, full_bar(s));
-                    }
-                }
+            if (lane == 0) {
+                if (loaded) mbar_arrive(full_bar(s));
+                else mbar_expect_tx(full_bar(s), STAGE_BYTES);
             }
+            __syncwarp();                            // ... and the byte count is expected before any lane's load can land
+            if (!loaded) load_pages(cur, page, s);
             if (lane == 0) *produced = n + 1;
             id = id_n; cur = nxt; page = page_n;
 #pragma unroll
@@ -198,6 +230,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
     } else if (warp == producer_warp + 1) {
         // ------------------------------------------------------------ prefetcher: the smem ring holds too little to cover
         // the latency of loaded DRAM, so the pages of the next few items are asked into L2 ahead of the producer
+        pdl_wait();
         if (p.one_load_per_page) {
             const int pages_per_item = SPLIT / p.page_size;
             Item it;
@@ -223,6 +256,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
         auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_WARPS * 32) : "memory"); };
         // A warp whose wait ran out keeps walking its items without touching them, so that the group's named
         // barrier below always finds all four warps.
+        pdl_wait();                                  // the workspace of partials belongs to earlier kernels until now
         bool ok = true;
         Item it;
         int n = 0;
