@@ -187,9 +187,12 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         bool ok = true;
         int seg_start = u0;                                    // first unit of the current tile segment
         int tile = u0 / KB, kb = u0 % KB;
-        for (int u = u0; u < u1 && ok; ++u) {
-            if (!mbar_wait(full_bar(s), phase, abort_flag, p.status)) { ok = false; break; }
+        // A warp whose wait ran out keeps walking its units without touching them, so that the consumers' named
+        // barrier below always finds all four warps.
+        for (int u = u0; u < u1; ++u) {
+            if (ok) ok = mbar_wait(full_bar(s), phase, abort_flag, p.status);
             const uint32_t wst = base + s * STAGE_BYTES, xst = wst + W_BYTES;
+            if (ok) {
 #pragma unroll
             for (int b = 0; b < BOXES; ++b) {
                 const uint32_t row_a = wst + b * W_BOX_BYTES + (16 * warp + g) * 128, row_b = row_a + 8 * 128;
@@ -212,6 +215,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(s));
+            }
             if (++s == stages) { s = 0; phase ^= 1u; }
 
             if (kb == KB - 1 || u == u1 - 1) {
@@ -223,7 +227,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const int tile_first = tile * KB;
                 const bool whole = seg_start == tile_first && kb == KB - 1;
                 if (whole) {
-                    store_tile<NT, EPI>(p, acc, tile, warp, g, t);
+                    if (ok) store_tile<NT, EPI>(p, acc, tile, warp, g, t);
                 } else {
                     const int c_first = cta_of_unit(tile_first, U, G), c_last = cta_of_unit(tile_first + KB - 1, U, G);
                     const int slot = (u0 >= tile_first) ? 0 : 1;            // 0: the tile my range starts in
@@ -234,12 +238,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         for (int i = 0; i < 4; ++i) __stcg(mine + (j * 4 + i) * 32 + lane, acc[j][i]);
                     __threadfence();
                     consumer_sync();
-                    if (threadIdx.x == 0) {
-                        const int seen = atomicAdd(p.counters + tile, 1);
-                        *last_flag = (seen == c_last - c_first) ? 1 : 0;
-                    }
+                    if (threadIdx.x == 0) *last_flag = (ok && atomicAdd(p.counters + tile, 1) == c_last - c_first) ? 1 : 0;
                     consumer_sync();
-                    if (*last_flag) {
+                    if (*last_flag && ok) {
                         __threadfence();
 #pragma unroll
                         for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
