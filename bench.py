@@ -159,6 +159,7 @@ def main() -> int:
         return rids
 
     def finish_all():
+        eng.drain()
         for r in list(eng.scheduler.running):
             eng.scheduler.running.remove(r)
             runner.release(r.rid)
@@ -173,13 +174,18 @@ def main() -> int:
         launches0 = ops.launch_count()
         ms = eng.decode_steps_device_timed(steps)
         launches = (ops.launch_count() - launches0) / steps
-        # end to end: host token ids in, host token ids out, every step
+        # end to end through Engine.step: every step's inputs go up from pinned host memory and its chosen ids come
+        # back to the host.  The engine launches a step while the one before it still runs, so the region starts and
+        # ends with nothing under way: `steps` calls, then the step the last call launched ahead is taken in too.
+        eng.drain()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(steps):
             eng.step()
+        done_steps = steps + (1 if eng._flight is not None else 0)
+        eng.drain()
         torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1000 / steps
+        e2e_ms = (time.perf_counter() - t0) * 1000 / done_steps
         finish_all()
         return ms, e2e_ms, launches, kv_tokens
 
@@ -192,9 +198,11 @@ def main() -> int:
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     rid_prompt = rng.integers(0, V, size=PROMPT).tolist()
     eng.add_request(rid_prompt, CONTEXT - PROMPT, SamplingParams())
+    eng.lookahead = False                      # the timed step is the prompt alone, not the first decode step behind it
     ev0.record()
     eng.step()
     ev1.record()
+    eng.lookahead = True
     torch.cuda.synchronize()
     prefill_ms = ev0.elapsed_time(ev1)
     finish_all()

@@ -75,11 +75,13 @@ def cmd_generate(args):
     rid = eng.add_request(ids, n, sp, eos_ids=args.eos or ())
     t0 = time.perf_counter()
     done = []
+    eng.lookahead = False                  # the prompt's time must not hold the first decode step launched behind it
     while not eng.scheduler.running or eng.scheduler.running[0].prefilling:
         done += eng.step()
         if done:
             break
     torch.cuda.synchronize()
+    eng.lookahead = True
     t1 = time.perf_counter()
     while eng.has_work():
         done += eng.step()
@@ -100,9 +102,11 @@ def bench_once(eng, prompts, tg):
         eng.add_request(p, tg + 1, SamplingParams())
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    eng.lookahead = False                  # as above
     while eng.scheduler.waiting or any(r.prefilling for r in eng.scheduler.running):
         eng.step()
     torch.cuda.synchronize()
+    eng.lookahead = True
     t1 = time.perf_counter()
     steps = 0
     while eng.has_work():

@@ -339,4 +339,17 @@ RS_EXPORT int rs_residual_add(float* x, const void* delta, int dt, long n, void*
 }
 
 // Turns programmatic dependent launch on or off for every kernel of this library (default on).
+// dst[i] = src[idx[i]]: the ids a step chose, brought into the order of the next step's rows on the device
+__global__ void gather_i32_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ idx, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = ld_dep(src + __ldg(idx + i));
+}
+
+RS_EXPORT int rs_gather_i32(int* dst, const int* src, const int* idx, int n, void* stream) {
+    if (n <= 0) return 0;
+    return rs_launch_pdl(gather_i32_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, dst, src, idx, n);
+}
+
 RS_EXPORT void rs_core_set_pdl(int on) { rs_pdl_switch() = on ? 1 : 0; }

@@ -22,6 +22,15 @@ from .runner import ModelRunner, StepEntry
 from .scheduler import Request, Scheduled, Scheduler
 
 
+class _Flight:
+    """A step that has been enqueued on the device and whose tokens have not been read yet."""
+
+    def __init__(self, batch, sampled, host_rows, logits, event, picked_h, h2d_bytes):
+        self.batch, self.sampled, self.host_rows, self.logits = batch, sampled, host_rows, logits
+        self.event, self.picked_h, self.h2d_bytes = event, picked_h, h2d_bytes
+        self.n_rows = len(sampled)       # rows the device sampled; stays what it was if rows are dropped later
+
+
 class Engine:
     def __init__(self, model: Union[str, Mapping], dtype: str = "bfloat16", random_seed: Optional[int] = None,
                  page_size: int = 16, num_pages: int = 0, max_tokens: int = 4096, max_batch_tokens: int = 2048,
@@ -46,14 +55,26 @@ class Engine:
         self._samplers: Dict[Hashable, Sampler] = {}
         self._ids = itertools.count()
         n = cfg.max_logit_rows
-        self._temps_h = torch.zeros(n, dtype=torch.float32).pin_memory()
-        self._unif_h = torch.zeros(n, dtype=torch.float32).pin_memory()
+        # pinned host buffers come in pairs: two steps can be under way (one running, the next one launched ahead)
+        self._temps_hh = [torch.zeros(n, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self._unif_hh = [torch.zeros(n, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self._src_hh = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._picked_hh = [torch.zeros(n + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._temps_h, self._unif_h, self._picked_h = self._temps_hh[0], self._unif_hh[0], self._picked_hh[0]
         self._temps_d = torch.zeros(n, dtype=torch.float32, device=r.device)
         self._unif_d = torch.zeros(n, dtype=torch.float32, device=r.device)
         self._picked_d = torch.zeros(n, dtype=torch.int32, device=r.device)
-        self._picked_h = torch.zeros(n + 1, dtype=torch.int32).pin_memory()
+        self._src_d = torch.zeros(n, dtype=torch.int32, device=r.device)
+        self._next_ids_d = torch.zeros(n, dtype=torch.int32, device=r.device)
         self.h2d_bytes_last_step = 0
         self.d2h_bytes_last_step = 0
+        # While a step runs, the next one is launched if the scheduler can tell its batch without this step's tokens
+        # (all requests decoding, nobody waiting, device-side sampling): the ids stay on the device, the host reads
+        # them one step late.  ``lookahead = False`` makes every step wait for its tokens before the next is built.
+        self.lookahead = True
+        self._flight: Optional[_Flight] = None
+        self._launches = 0
+        self.steps_launched_ahead = 0
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int = 32, sampling: Optional[SamplingParams] = None,
@@ -74,21 +95,88 @@ class Engine:
 
     # ------------------------------------------------------------------ one scheduler step
     def step(self) -> List[Request]:
-        """Schedules and runs one step, chooses the next tokens, returns the requests that finished."""
-        batch = self.scheduler.schedule()
-        if not batch:
-            if self.scheduler.has_work():
-                self.scheduler.step_index += 1     # nothing could run (arrivals in the future): time passes
-            return []
-        entries = [StepEntry(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
-        sampled = [s for s in batch if s.samples]
-        host_rows = self._prepare_sampling(sampled)
-        logits = self.runner.step(entries, post=self._sample_post if sampled else None)
-        chosen = self._collect(sampled, host_rows, logits)
-        done = self.scheduler.advance(batch, chosen)
+        """Runs one step to its end: schedules and launches it (unless the previous call already launched it ahead),
+        launches the step after it when that is possible, then reads this step's tokens and returns the requests
+        that finished with it."""
+        fl, self._flight = self._flight, None
+        if fl is None:
+            batch = self.scheduler.schedule()
+            if not batch:
+                if self.scheduler.has_work():
+                    self.scheduler.step_index += 1     # nothing could run (arrivals in the future): time passes
+                return []
+            fl = self._launch(batch, None)
+        nxt = None
+        try:
+            if self.lookahead and fl.sampled and not fl.host_rows:
+                ahead = self.scheduler.lookahead(fl.batch)
+                if ahead:
+                    nxt = self._launch(ahead, fl)
+                    self.steps_launched_ahead += 1
+            chosen = self._collect(fl)
+        except Exception:
+            self._drop_flight(nxt)
+            raise
+        done = self.scheduler.advance(fl.batch, chosen)
         for r in done:
             self._samplers.pop(r.rid, None)
+        if nxt is not None:
+            gone = {id(r) for r in done}
+            if gone:                                   # ended by an end-of-sequence token: its row ran for nothing
+                nxt.batch = [s for s in nxt.batch if id(s.request) not in gone]
+                nxt.sampled = [(i, s) for i, s in nxt.sampled if id(s.request) not in gone]
+            if nxt.batch:
+                self._flight = nxt
         return done
+
+    def _drop_flight(self, fl: Optional["_Flight"]) -> None:
+        """Forgets a step launched ahead whose results will not be used (its kernels still run to their end)."""
+        if fl is not None:
+            fl.event.synchronize()
+
+    def drain(self) -> List[Request]:
+        """Waits for a step launched ahead and takes its tokens in, so that nothing is under way; returns the
+        requests that finished with it."""
+        done: List[Request] = []
+        while self._flight is not None:
+            look, self.lookahead = self.lookahead, False
+            try:
+                done += self.step()
+            finally:
+                self.lookahead = look
+        return done
+
+    def _launch(self, batch: List[Scheduled], prev: Optional["_Flight"]) -> "_Flight":
+        """Enqueues one step: sampling parameters up, the forward pass and the device's token choice, the chosen
+        ids down, an event behind them.  With ``prev`` the tokens are the ids ``prev`` chose, taken on the device."""
+        k = self._launches & 1
+        self._launches += 1
+        self._temps_h, self._unif_h, self._picked_h = self._temps_hh[k], self._unif_hh[k], self._picked_hh[k]
+        sampled = [(i, s) for i, s in enumerate(x for x in batch if x.samples)]
+        only = [s for _, s in sampled]
+        host_rows = self._prepare_sampling(only)
+        device_tokens = None
+        if prev is None:
+            entries = [StepEntry(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
+        else:
+            row_of = {id(s.request): i for i, s in prev.sampled}
+            src = self._src_hh[k].numpy()
+            for j, s in enumerate(batch):
+                src[j] = row_of[id(s.request)]
+            n = len(batch)
+            self._src_d[:n].copy_(self._src_hh[k][:n], non_blocking=True)
+            ops.gather_i32(self._next_ids_d, self._picked_d, self._src_d, n)
+            device_tokens = self._next_ids_d
+            entries = [StepEntry(s.request.rid, [0], [0]) for s in batch]
+        logits = self.runner.step(entries, device_tokens=device_tokens, post=self._sample_post if sampled else None)
+        R = len(sampled)
+        if R:
+            self._picked_h[:R].copy_(self._picked_d[:R], non_blocking=True)
+        self._picked_h[R:R + 1].copy_(self.runner.status, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        h2d = self.runner.h2d_bytes_last_step + 8 * R + (4 * len(batch) if prev is not None else 0)
+        return _Flight(batch, sampled, host_rows, logits, event, self._picked_h, h2d)
 
     def _prepare_sampling(self, sampled: Sequence[Scheduled]) -> List[int]:
         """Uploads temperatures and uniforms of the rows the device will sample; returns the rows that
@@ -115,24 +203,18 @@ class Engine:
         """The device's token choice, run right after the forward pass (inside the graph of a captured step)."""
         ops.sample(logits, n_rows, self._picked_d, self.runner.status, self._temps_d, self._unif_d)
 
-    def _collect(self, sampled: Sequence[Scheduled], host_rows: List[int], logits: Optional[torch.Tensor]
-                 ) -> Dict[Hashable, int]:
-        """Brings the chosen ids (and the logits of host-sampled rows) back and records them."""
-        if not sampled:
-            self.runner.check_status()
-            return {}
-        R = len(sampled)
-        self._picked_h[:R].copy_(self._picked_d[:R], non_blocking=True)
-        self._picked_h[R:R + 1].copy_(self.runner.status, non_blocking=True)
-        host_logits = {i: logits[i].to("cpu").numpy() for i in host_rows}      # also waits for the stream
-        self.h2d_bytes_last_step = self.runner.h2d_bytes_last_step + 8 * R
-        self.d2h_bytes_last_step = 4 * (R + 1) + 4 * logits.shape[1] * len(host_rows)
-        torch.cuda.current_stream().synchronize()
-        picked = self._picked_h.numpy()
+    def _collect(self, fl: "_Flight") -> Dict[Hashable, int]:
+        """Waits for the step's chosen ids (and brings the logits of host-sampled rows back) and records them."""
+        R = fl.n_rows
+        host_logits = {i: fl.logits[i].to("cpu").numpy() for i in fl.host_rows}      # also waits for the stream
+        self.h2d_bytes_last_step = fl.h2d_bytes
+        self.d2h_bytes_last_step = 4 * (R + 1) + (4 * fl.logits.shape[1] * len(fl.host_rows) if fl.host_rows else 0)
+        fl.event.synchronize()
+        picked = fl.picked_h.numpy()
         if int(picked[R]) != 0:
             self.runner.check_status()
         out = {}
-        for i, s in enumerate(sampled):
+        for i, s in fl.sampled:
             smp = self._samplers[s.request.rid]
             if i in host_logits:
                 out[s.request.rid] = smp.pick(host_logits[i])
@@ -169,6 +251,7 @@ class Engine:
         """Runs ``n_steps`` greedy decode steps of all running requests with the chosen ids staying on
         the device between steps (the host only counts lengths), and returns the milliseconds per step
         measured with CUDA events.  The generated ids are appended to the requests afterwards."""
+        self.drain()
         reqs = list(self.scheduler.running)
         if not reqs or any(r.prefilling for r in reqs) or self.scheduler.waiting:
             raise RuntimeError("device decode needs every request past its prompt and none waiting")

@@ -200,6 +200,38 @@ class Scheduler:
         promise(req, n)
         return n
 
+    # ---------------------------------------------------------------- the step after the one in flight
+    def lookahead(self, batch: Sequence[Scheduled]) -> Optional[List[Scheduled]]:
+        """The batch ``schedule`` would build after ``advance(batch, ...)``, if that can be said before the
+        tokens of ``batch`` are known: nobody waits, every running request samples in ``batch`` (so all of
+        them decode next), and the pages for one more token each are free.  Requests that end with ``batch`` by
+        length are left out; one that ends by an end-of-sequence token is only found out afterwards, and the
+        engine drops its row.  The tokens are placeholders (-1): the device feeds the ids it chose.  None when
+        the next step has to wait for ``advance``."""
+        if self.waiting or not batch or len(batch) != len(self.running):
+            return None
+        if any(not s.samples for s in batch) or {id(s.request) for s in batch} != {id(r) for r in self.running}:
+            return None
+        by_req = {id(s.request): s for s in batch}
+        promised = [0] * len(self.cache.groups)
+        out: List[Scheduled] = []
+        for req in self.running:
+            s = by_req[id(req)]
+            if req.computed + len(s.tokens) != len(req.prompt) + len(req.generated):
+                return None                                   # not its newest token: it will still be prefilling
+            n_gen = len(req.generated) + 1
+            if n_gen >= req.max_new_tokens or len(req.prompt) + n_gen >= self.max_positions:
+                continue                                      # ends with the step in flight
+            need = self.cache.pages_to_reserve(req.rid, 1)
+            if any(need[g] + promised[g] > self.cache.n_free(g) for g in range(len(need))):
+                return None                                   # pages run out: schedule() decides who yields
+            for g, k in enumerate(need):
+                promised[g] += k
+            out.append(Scheduled(req, [-1], True))
+        if not out or len(out) > self.max_batch_tokens:
+            return None
+        return out
+
     # ---------------------------------------------------------------- after the step
     def advance(self, batch: Sequence[Scheduled], new_tokens: Dict[Hashable, int]) -> List[Request]:
         """Records what the step computed and the tokens it chose; returns requests that finished

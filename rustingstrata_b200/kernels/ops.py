@@ -84,6 +84,7 @@ def core():
     if _core is None:
         lib = load_library("core")
         lib.rs_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_gather_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.rs_rmsnorm.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_long,
                                    c_int, c_int, c_void_p]
         lib.rs_qk_norm_rope_kv.argtypes = [c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -116,6 +117,14 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: tor
         raise KernelError(f"embed: table {tuple(table.shape)} / ids {ids.numel()} do not fit out {tuple(out.shape)}")
     _check(core().rs_embed(_ptr(table), dtype_code(table), _ptr(ids), _ptr(out), T, H, table.shape[0], _ptr(status),
                            _stream()), "embed")
+
+
+def gather_i32(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor, n: int) -> None:
+    """dst[i] = src[idx[i]] for i < n, all int32 on the device (idx must point inside src)."""
+    _cuda(dst, src, idx)
+    if dst.dtype != torch.int32 or src.dtype != torch.int32 or idx.dtype != torch.int32 or dst.numel() < n or idx.numel() < n:
+        raise KernelError("gather_i32: int32 tensors with at least n entries")
+    _check(core().rs_gather_i32(_ptr(dst), _ptr(src), _ptr(idx), n, _stream()), "gather_i32")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

@@ -190,3 +190,44 @@ def test_step_errors_leave_the_cache_untouched(tiny_models):
     r.cache.check()
     out = r.step([StepEntry("a", [5], [0])])
     assert out.shape == (1, 256)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(tiny_models, dtype):
+    """While a step runs, the engine launches the next one with the chosen ids staying on the device.  The tokens
+    are those of an engine that waits for every step, with greedy and with temperature sampling, when requests end
+    by length at different times, when one ends by an end-of-sequence token the engine could not foresee, and
+    when a request arrives in the middle."""
+    from rustingstrata_b200.sampling import SamplingParams
+    cfg, w = P.read_model(tiny_models["B"])
+    prompts = [random_tokens(cfg["vocab_size"], n, 300 + n) for n in (5, 17, 9, 30)]
+    plans = [(12, 0.0), (25, 0.8), (7, 0.0), (18, 1.3)]
+
+    def run(lookahead, eos=()):
+        eng = engine(tiny_models, "B", dtype)
+        eng.lookahead = lookahead
+        rids = [eng.add_request(p, n, SamplingParams(temp=t, seed=11 + i), eos_ids=eos)
+                for i, (p, (n, t)) in enumerate(zip(prompts[:3], plans[:3]))]
+        out, steps = {}, 0
+        while eng.has_work():
+            for r in eng.step():
+                out[r.rid] = (list(r.generated), r.finish_reason)
+            steps += 1
+            if steps == 6:                                       # a late arrival
+                rids.append(eng.add_request(prompts[3], plans[3][0], SamplingParams(temp=plans[3][1], seed=99), eos_ids=eos))
+        eng.runner.check_status()
+        eng.runner.cache.check()
+        assert all(eng.runner.cache.n_free(g) == eng.runner.num_pages for g in range(len(eng.runner.cache.groups)))
+        return [out[r] for r in rids], eng.steps_launched_ahead
+
+    slow, n0 = run(False)
+    fast, n1 = run(True)
+    assert n0 == 0 and n1 > 20
+    assert fast == slow
+    assert [len(g) for g, _ in slow] == [12, 25, 7, 18]
+    # an end-of-sequence token in the middle of the longest request
+    eos = (slow[1][0][10],)
+    slow_e, _ = run(False, eos)
+    fast_e, n2 = run(True, eos)
+    assert fast_e == slow_e and n2 > 5
+    assert slow_e[1][1] == "eos" and len(slow_e[1][0]) <= 10

@@ -169,3 +169,95 @@ def test_a_lone_request_is_never_preempted_and_never_deadlocks():
         steps += 1
         assert steps < 40
     assert sched.preemptions == 0 and cache.n_free(0) == 4
+
+
+# ------------------------------------------------------------------ the step after the one in flight
+def _decoding(n_req=3, pages=64, max_new=8, eos=()):
+    from rustingstrata_b200.cache import CacheManager, GroupNeed
+    from rustingstrata_b200.engine.scheduler import Request, Scheduler
+    cache = CacheManager([GroupNeed(None)], page_size=4, num_pages=pages, max_seqs=8)
+    sch = Scheduler(cache, max_batch_tokens=64, max_seqs=8, max_positions=256)
+    for i in range(n_req):
+        sch.add(Request(rid=i, prompt=[1, 2, 3, 4, 5][: 3 + i % 3], max_new_tokens=max_new, eos_ids=tuple(eos)))
+    return cache, sch
+
+
+def _run(cache, sch, batch, token=7):
+    for s in batch:
+        cache.reserve(s.request.rid, len(s.tokens))
+        cache.commit(s.request.rid, len(s.tokens))
+    return sch.advance(batch, {s.request.rid: token for s in batch if s.samples})
+
+
+def test_lookahead_is_the_batch_schedule_would_build():
+    cache, sch = _decoding()
+    batch = sch.schedule()                                     # the three prompts, whole
+    for s in batch:                                            # what the runner's step does on the host
+        cache.reserve(s.request.rid, len(s.tokens))
+        cache.commit(s.request.rid, len(s.tokens))
+    ahead = sch.lookahead(batch)
+    assert ahead is not None and [s.request.rid for s in ahead] == [0, 1, 2]
+    assert all(s.tokens == [-1] and s.samples for s in ahead)
+    sch.advance(batch, {0: 7, 1: 7, 2: 7})
+    real = sch.schedule()
+    assert [s.request.rid for s in real] == [s.request.rid for s in ahead] and all(len(s.tokens) == 1 for s in real)
+
+
+def test_lookahead_waits_when_it_cannot_know():
+    from rustingstrata_b200.engine.scheduler import Request
+    cache, sch = _decoding()
+    batch = sch.schedule()
+    for s in batch:
+        cache.reserve(s.request.rid, len(s.tokens))
+        cache.commit(s.request.rid, len(s.tokens))
+    sch.add(Request(rid=9, prompt=[1, 2], max_new_tokens=4))   # somebody waits: admission comes first
+    assert sch.lookahead(batch) is None
+    sch.waiting.clear()
+    assert sch.lookahead(batch[:2]) is None                    # a running request that is not in the batch
+    assert sch.lookahead([]) is None
+
+
+def test_lookahead_with_a_portion_that_does_not_end_the_prompt():
+    from rustingstrata_b200.cache import CacheManager, GroupNeed
+    from rustingstrata_b200.engine.scheduler import Request, Scheduler
+    cache = CacheManager([GroupNeed(None)], page_size=4, num_pages=64, max_seqs=4)
+    sch = Scheduler(cache, max_batch_tokens=64, max_seqs=4, max_positions=256, prefill_chunk=4)
+    sch.add(Request(rid=0, prompt=list(range(1, 11)), max_new_tokens=4))
+    batch = sch.schedule()
+    assert not batch[0].samples
+    for s in batch:
+        cache.reserve(s.request.rid, len(s.tokens))
+        cache.commit(s.request.rid, len(s.tokens))
+    assert sch.lookahead(batch) is None                        # still prefilling after this step
+
+
+def test_lookahead_leaves_out_requests_that_end_by_length_and_stops_when_pages_run_out():
+    cache, sch = _decoding(n_req=2, pages=64, max_new=2)
+    batch = sch.schedule()
+    _run(cache, sch, batch)                                    # one token generated each
+    batch = sch.schedule()
+    for s in batch:
+        cache.reserve(s.request.rid, 1)
+        cache.commit(s.request.rid, 1)
+    assert sch.lookahead(batch) is None                        # both end with this step: nothing to launch
+    # pages: two requests hold one full page each and one page is free: the fifth tokens of both do not fit
+    from rustingstrata_b200.cache import CacheManager, GroupNeed
+    from rustingstrata_b200.engine.scheduler import Request, Scheduler
+    cache = CacheManager([GroupNeed(None)], page_size=4, num_pages=3, max_seqs=4)
+    sch = Scheduler(cache, max_batch_tokens=64, max_seqs=4, max_positions=256)
+    for i in range(2):
+        sch.add(Request(rid=i, prompt=[1, 2, 3], max_new_tokens=6))
+    batch = sch.schedule()
+    assert len(batch) == 2                                     # both prompts: one page each, one page stays free
+    for s in batch:
+        cache.reserve(s.request.rid, len(s.tokens))
+        cache.commit(s.request.rid, len(s.tokens))
+    ahead = sch.lookahead(batch)                               # their fourth tokens go into the pages they hold
+    assert ahead is not None and len(ahead) == 2
+    sch.advance(batch, {0: 7, 1: 7})
+    batch = sch.schedule()
+    for s in batch:
+        cache.reserve(s.request.rid, len(s.tokens))
+        cache.commit(s.request.rid, len(s.tokens))
+    assert cache.n_free(0) == 1
+    assert sch.lookahead(batch) is None                        # both need a new page and one is free: schedule() decides
