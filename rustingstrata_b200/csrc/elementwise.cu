@@ -189,9 +189,11 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int
     }
 }
 
-// bfloat16 fast path: whole head rotated (n_rot == hd), bfloat16 norm weights (or none), 8-byte aligned rows.
-// A lane owns 4 consecutive elements of the lower half of a head and the 4 it pairs with in the upper half, so a
-// head takes L = hd / 8 lanes; when L is a power of two a warp serves 32 / L heads side by side.
+// bfloat16 fast path: whole head rotated (n_rot == hd), bfloat16 norm weights (or none), aligned rows.
+// A lane owns E consecutive elements of the lower half of a head and the E it pairs with in the upper half (E = 8:
+// 16-byte accesses, when half a head is a multiple of 8; else E = 4), so a head takes L = hd / (2 E) lanes; when L is
+// a power of two a warp serves 32 / L heads side by side.
+template <int E>
 __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride, int n_q, int n_kv, int hd,
                                             const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w,
                                             float eps, const float* __restrict__ cos_sin,
@@ -199,6 +201,7 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
                                             const int* __restrict__ block_table, int table_stride, int page_size,
                                             __nv_bfloat16* __restrict__ cache, long page_stride, int num_pages, int write_kv,
                                             int n_tokens, int lanes_per_head, int* status) {
+    struct alignas(2 * E) Vec { uint32_t w[E / 2]; };           // E bfloat16 values
     pdl_launch_dependents();
     pdl_wait();
     const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
@@ -225,47 +228,63 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     }
     const __nv_bfloat16* w = h < n_q ? q_w : k_w;
     const int half = hd >> 1;
-    auto unpack = [](uint2 u, float* f) {
-        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
-        f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(b); f[3] = __high2float(b);
+    auto unpack = [](const Vec& u, float* f) {
+#pragma unroll
+        for (int k = 0; k < E / 2; ++k) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.w[k]);
+            f[2 * k] = __low2float(a); f[2 * k + 1] = __high2float(a);
+        }
     };
     auto pack = [](const float* f) {
-        const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
-        uint2 u;
-        u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&b);
+        Vec u;
+#pragma unroll
+        for (int k = 0; k < E / 2; ++k) {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+            u.w[k] = *reinterpret_cast<const uint32_t*>(&a);
+        }
         return u;
     };
-    const int i = sub * 4;
+    const int i = sub * E;
     const bool mine = ok && i < half;
-    uint2 ua = make_uint2(0, 0), ub = make_uint2(0, 0);
-    if (mine) { ua = *reinterpret_cast<const uint2*>(src + i); ub = *reinterpret_cast<const uint2*>(src + half + i); }
+    Vec ua, ub;
+#pragma unroll
+    for (int k = 0; k < E / 2; ++k) ua.w[k] = ub.w[k] = 0u;
+    if (mine) { ua = *reinterpret_cast<const Vec*>(src + i); ub = *reinterpret_cast<const Vec*>(src + half + i); }
     if (is_v) {                                    // values are copied as they are
-        if (mine) { *reinterpret_cast<uint2*>(dst + i) = ua; *reinterpret_cast<uint2*>(dst + half + i) = ub; }
-        ua = make_uint2(0, 0); ub = make_uint2(0, 0);
+        if (mine) { *reinterpret_cast<Vec*>(dst + i) = ua; *reinterpret_cast<Vec*>(dst + half + i) = ub; }
+#pragma unroll
+        for (int k = 0; k < E / 2; ++k) ua.w[k] = ub.w[k] = 0u;
     }
-    float a[4], b[4];
+    float a[E], b[E];
     unpack(ua, a); unpack(ub, b);
     float ss = 0.f;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) { ss = fmaf(a[u], a[u], ss); ss = fmaf(b[u], b[u], ss); }
+    for (int u = 0; u < E; ++u) { ss = fmaf(a[u], a[u], ss); ss = fmaf(b[u], b[u], ss); }
     for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // within the head's lanes
     if (!mine || is_v) return;
     const float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;
-    float wa[4] = {1.f, 1.f, 1.f, 1.f}, wb[4] = {1.f, 1.f, 1.f, 1.f};
-    if (w != nullptr) { unpack(*reinterpret_cast<const uint2*>(w + i), wa); unpack(*reinterpret_cast<const uint2*>(w + half + i), wb); }
-    const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i);
-    const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i);
-    const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-    float ra[4], rb[4];
+    float wa[E], wb[E];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < E; ++u) wa[u] = wb[u] = 1.f;
+    if (w != nullptr) { unpack(*reinterpret_cast<const Vec*>(w + i), wa); unpack(*reinterpret_cast<const Vec*>(w + half + i), wb); }
+    float cc[E], sv[E];
+#pragma unroll
+    for (int u = 0; u < E; u += 4) {
+        const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i + u);
+        const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i + u);
+        cc[u] = c.x; cc[u + 1] = c.y; cc[u + 2] = c.z; cc[u + 3] = c.w;
+        sv[u] = sn.x; sv[u + 1] = sn.y; sv[u + 2] = sn.z; sv[u + 3] = sn.w;
+    }
+    float ra[E], rb[E];
+#pragma unroll
+    for (int u = 0; u < E; ++u) {
         float x = a[u] * scale, y = b[u] * scale;
         if (w != nullptr) { x *= wa[u]; y *= wb[u]; }
         ra[u] = x * cc[u] - y * sv[u];
         rb[u] = x * sv[u] + y * cc[u];
     }
-    *reinterpret_cast<uint2*>(dst + i) = pack(ra);
-    *reinterpret_cast<uint2*>(dst + half + i) = pack(rb);
+    *reinterpret_cast<Vec*>(dst + i) = pack(ra);
+    *reinterpret_cast<Vec*>(dst + half + i) = pack(rb);
 }
 
 RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, int n_kv, int hd, const void* q_w,
@@ -282,12 +301,16 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
                                                                   ((long)q_w & 7) == 0 && ((long)k_w & 7) == 0);
     if (dt == RS_BF16 && cos_sin != nullptr && n_rot == hd && hd % 8 == 0 && hd <= 256 && row_stride % 4 == 0 && page_stride % 4 == 0 &&
         ((long)qkv & 7) == 0 && ((long)cache & 7) == 0 && ((long)cos_sin & 15) == 0 && weights_ok && (q_w != nullptr || k_w == nullptr)) {
-        int lanes = hd / 8;                                   // lanes a head needs; a power of two packs several heads per warp
+        // 16-byte accesses when half a head is a multiple of 8 elements and everything is 16-byte aligned
+        const bool wide = hd % 16 == 0 && row_stride % 8 == 0 && page_stride % 8 == 0 && ((long)qkv & 15) == 0 && ((long)cache & 15) == 0 &&
+                          ((long)q_w & 15) == 0 && ((long)k_w & 15) == 0;
+        int lanes = hd / (wide ? 16 : 8);                     // lanes a head needs; a power of two packs several heads per warp
         if (lanes & (lanes - 1)) lanes = 32;
         const long heads_per_warp = 32 / lanes;
         const long nwarps = (warps + heads_per_warp - 1) / heads_per_warp;
         const long nblocks = (nwarps * 32 + threads - 1) / threads;
-        return rs_launch_pdl(qk_norm_rope_kv_bf16_kernel, dim3((unsigned)nblocks), dim3(threads), 0, (cudaStream_t)stream,
+        auto kern = wide ? qk_norm_rope_kv_bf16_kernel<8> : qk_norm_rope_kv_bf16_kernel<4>;
+        return rs_launch_pdl(kern, dim3((unsigned)nblocks), dim3(threads), 0, (cudaStream_t)stream,
                              (__nv_bfloat16*)qkv, row_stride, n_q, n_kv, hd, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, eps,
                              cos_sin, positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16*)cache,
                              page_stride, num_pages, write_kv, n_tokens, lanes, status);
@@ -338,7 +361,6 @@ RS_EXPORT int rs_residual_add(float* x, const void* delta, int dt, long n, void*
     return rs_launch_result();
 }
 
-// Turns programmatic dependent launch on or off for every kernel of this library (default on).
 // dst[i] = src[idx[i]]: the ids a step chose, brought into the order of the next step's rows on the device
 __global__ void gather_i32_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ idx, int n) {
     pdl_launch_dependents();
@@ -352,4 +374,5 @@ RS_EXPORT int rs_gather_i32(int* dst, const int* src, const int* idx, int n, voi
     return rs_launch_pdl(gather_i32_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, dst, src, idx, n);
 }
 
+// Turns programmatic dependent launch on or off for every kernel of this library (default on).
 RS_EXPORT void rs_core_set_pdl(int on) { rs_pdl_switch() = on ? 1 : 0; }
