@@ -171,9 +171,10 @@ def main() -> int:
         for _ in range(warmup):
             eng.step()
         kv_tokens = sum(runner.length(r.rid) for r in eng.scheduler.running)
-        launches0 = ops.launch_count()
-        ms = eng.decode_steps_device_timed(steps)
-        launches = (ops.launch_count() - launches0) / steps
+        # kernels of this package that run inside the timed region: its steps are graph replays, whose kernel nodes the
+        # runner counted at capture (the warm-up steps of the device-timed loop, launched from Python, are not timed)
+        ms = eng.decode_steps_device_timed(steps, warmup=3)
+        launches = eng.kernels_in_timed_steps / steps
         # end to end through Engine.step: every step's inputs go up from pinned host memory and its chosen ids come
         # back to the host.  The engine launches a step while the one before it still runs, so the region starts and
         # ends with nothing under way: `steps` calls, then the step the last call launched ahead is taken in too.

@@ -17,10 +17,10 @@
 //                               activation rows the 8-column operand).  W and A are read with the same
 //                               lane-to-k assignment, so no shuffle is needed: the sum over k does not care
 //                               in which order k is visited.
-// A row tile whose k range is shared by several CTAs is completed without anyone waiting: each contributor
-// writes its float32 partial (same thread-to-element mapping everywhere) to a workspace and bumps the tile's
-// counter; the contributor that arrives last adds the partials in CTA order and applies the epilogue, then
-// resets the counter.  The order of the additions is fixed by the shape alone.
+// A row tile whose k range is shared by several CTAs is completed by a second, small kernel launched behind this one
+// (skinny_reduce_kernel): each contributor writes its float32 partial (same thread-to-element mapping everywhere) to
+// a workspace and is done, so every CTA of the product does the same amount of work and none lags behind adding up
+// a tile; the small kernel adds the partials in CTA order, which the shape alone fixes, and applies the epilogue.
 // Epilogues: store bf16 | store f32 | f32 += (residual add) | SiLU(gate)*up over interleaved rows of W.
 // Waits on mbarriers are bounded (tma_helpers.cuh).
 //
@@ -47,7 +47,6 @@ struct SkinnyParams {
     int M, N, K;
     int stages;
     float* workspace;          // [grid][2][CONSUMER_WARPS][NT * 4][32] float32 partials
-    int* counters;             // [row tiles], zero between launches
     int* status;
 };
 
@@ -56,7 +55,6 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
 // first unit of CTA c when U units are dealt to G CTAs as evenly as possible
 __device__ __forceinline__ int first_unit(int c, int U, int G) { return c * (U / G) + (c < U % G ? c : U % G); }
@@ -117,7 +115,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (base - raw) + stages * STAGE_BYTES + 16 * stages);
-    int* last_flag = const_cast<int*>(abort_flag) + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = (p.K + TILE_K - 1) / TILE_K;
@@ -128,7 +125,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), CONSUMER_WARPS); }
         *abort_flag = 0;
-        *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -229,33 +225,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (whole) {
                     if (ok) store_tile<NT, EPI>(p, acc, tile, warp, g, t);
                 } else {
-                    const int c_first = cta_of_unit(tile_first, U, G), c_last = cta_of_unit(tile_first + KB - 1, U, G);
+                    // shared with other CTAs: my float32 partial goes to the workspace; skinny_reduce_kernel adds them up
                     const int slot = (u0 >= tile_first) ? 0 : 1;            // 0: the tile my range starts in
                     float* mine = p.workspace + ((((size_t)blockIdx.x * 2 + slot) * CONSUMER_WARPS + warp) * (NT * 4)) * 32;
 #pragma unroll
                     for (int j = 0; j < NT; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) __stcg(mine + (j * 4 + i) * 32 + lane, acc[j][i]);
-                    __threadfence();
-                    consumer_sync();
-                    if (threadIdx.x == 0) *last_flag = (ok && atomicAdd(p.counters + tile, 1) == c_last - c_first) ? 1 : 0;
-                    consumer_sync();
-                    if (*last_flag && ok) {
-                        __threadfence();
-#pragma unroll
-                        for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-                        for (int c = c_first; c <= c_last; ++c) {
-                            const int cslot = (first_unit(c, U, G) >= tile_first) ? 0 : 1;
-                            const float* src = p.workspace + ((((size_t)c * 2 + cslot) * CONSUMER_WARPS + warp) * (NT * 4)) * 32;
-#pragma unroll
-                            for (int j = 0; j < NT; ++j)
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) acc[j][i] += __ldcg(src + (j * 4 + i) * 32 + lane);
-                        }
-                        store_tile<NT, EPI>(p, acc, tile, warp, g, t);
-                        if (threadIdx.x == 0) p.counters[tile] = 0;
-                    }
-                    consumer_sync();                                         // last_flag may be rewritten next time
                 }
 #pragma unroll
                 for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
@@ -270,6 +246,51 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         while (global_ns() - t0 < 200000ull) __nanosleep(1000);          // let loads already issued land
     }
     __syncthreads();
+}
+
+// Adds up the partials of the row tiles that several CTAs of skinny_gemm_kernel shared and applies the epilogue: one CTA
+// per CTA boundary of the product; it acts if its boundary is the first one inside a tile.  The partials are added in
+// CTA order, which the shape alone fixes.  G is the grid of the product.
+template <int NT, int EPI>
+__global__ void __launch_bounds__(CONSUMER_WARPS * 32) skinny_reduce_kernel(const SkinnyParams p, int G) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int KB = (p.K + TILE_K - 1) / TILE_K;
+    const int U = ((p.N + TILE_N - 1) / TILE_N) * KB;
+    const int b = blockIdx.x + 1;                              // boundary between CTA b - 1 and CTA b
+    const int ub = first_unit(b, U, G);
+    if (ub % KB == 0) return;                                  // on a tile's edge: nobody shares because of it
+    const int tile = ub / KB, tile_first = tile * KB;
+    if (first_unit(b - 1, U, G) > tile_first) return;          // an earlier boundary lies in this tile: its CTA acts
+    const int c_first = b - 1, c_last = cta_of_unit(tile_first + KB - 1, U, G);
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    constexpr int CH = NT == 1 ? 4 : (NT == 2 ? 2 : 1);       // contributors whose loads are in flight together
+    for (int c0 = c_first; c0 <= c_last; c0 += CH) {
+        float v[CH][NT][4];
+#pragma unroll
+        for (int cc = 0; cc < CH; ++cc) {
+            const int c = min(c0 + cc, c_last);
+            const int cslot = (first_unit(c, U, G) >= tile_first) ? 0 : 1;
+            const float* src = p.workspace + ((((size_t)c * 2 + cslot) * CONSUMER_WARPS + warp) * (NT * 4)) * 32;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[cc][j][i] = ld_dep(src + (j * 4 + i) * 32 + lane);
+        }
+#pragma unroll
+        for (int cc = 0; cc < CH; ++cc)
+            if (c0 + cc <= c_last) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[j][i] += v[cc][j][i];
+            }
+    }
+    store_tile<NT, EPI>(p, acc, tile, warp, g, t);
 }
 
 template <int NT> constexpr int stage_bytes() { return W_BYTES + 8 * NT * TILE_K * 2; }
@@ -292,7 +313,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, SkinnyParams p, int max
     long grid = rs_tma::sm_count();
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
     if (grid > U) grid = U;
-    return rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
+    int rc = rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
+    if (rc != 0 || grid < 2) return rc;
+    return rs_launch_pdl(skinny_reduce_kernel<NT, EPI>, dim3((unsigned)(grid - 1)), dim3(CONSUMER_WARPS * 32), 0, s, p, (int)grid);
 }
 
 template <int NT>
@@ -309,19 +332,17 @@ int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const Skin
 
 RS_EXPORT int rs_skinny_gemm_max_rows() { return 64; }
 
-// float32 values of workspace and ints of counters a launch needs (for any M <= 64 and this N).
+// float32 values of workspace a launch needs (for any M <= 64).
 RS_EXPORT long rs_skinny_gemm_workspace_floats() { return (long)rs_tma::sm_count() * 2 * CONSUMER_WARPS * 8 * 4 * 32; }
-RS_EXPORT long rs_skinny_gemm_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
 
 // C[M, N] (=|+=) A[M, K] . W[N, K]^T for M <= 64, bf16 inputs; same epilogue codes as rs_gemm_bf16_tc.  a_rows is the
-// row capacity of A's buffer.  workspace/counters as sized above; counters must be zero before the first launch and
-// are left zero.  Launches that share a workspace must not overlap on the GPU.
+// row capacity of A's buffer.  workspace as sized above.  Launches that share a workspace must not overlap on the GPU.
 RS_EXPORT int rs_skinny_gemm_bf16(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M,
-                                  int N, int K, int epi, float* workspace, int* counters, int max_ctas, int* status,
+                                  int N, int K, int epi, float* workspace, int max_ctas, int* status,
                                   void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
-        workspace == nullptr || counters == nullptr)
+        workspace == nullptr)
         return (int)cudaErrorInvalidValue;
     if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
@@ -331,7 +352,7 @@ RS_EXPORT int rs_skinny_gemm_bf16(const void* A, long lda, long a_rows, const vo
     rc = rs_tma::get_map(A, a_rows, K, lda, 8 * nt, &ma);
     if (rc) return rc;
     SkinnyParams p;
-    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.counters = counters;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace;
     p.status = status;
     cudaStream_t s = (cudaStream_t)stream;
     switch (nt) {

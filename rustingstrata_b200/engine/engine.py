@@ -247,10 +247,12 @@ class Engine:
         return outs[0] if single else outs
 
     # ------------------------------------------------------------------ device-resident greedy decode
-    def decode_steps_device_timed(self, n_steps: int) -> float:
-        """Runs ``n_steps`` greedy decode steps of all running requests with the chosen ids staying on
-        the device between steps (the host only counts lengths), and returns the milliseconds per step
-        measured with CUDA events.  The generated ids are appended to the requests afterwards."""
+    def decode_steps_device_timed(self, n_steps: int, warmup: int = 3) -> float:
+        """Runs ``warmup + n_steps`` greedy decode steps of all running requests with the chosen ids staying on
+        the device between steps (the host only counts lengths), and returns the milliseconds per step of the last
+        ``n_steps``, measured with CUDA events.  The warm-up steps let this loop's own CUDA graph be captured (the
+        first step of a new layout runs eagerly, the second captures) before the clock starts.  The generated ids
+        are appended to the requests afterwards."""
         self.drain()
         reqs = list(self.scheduler.running)
         if not reqs or any(r.prefilling for r in reqs) or self.scheduler.waiting:
@@ -259,24 +261,28 @@ class Engine:
         r = self.runner
         first = torch.tensor([q.all_tokens[-1] for q in reqs], dtype=torch.int32).pin_memory()
         self._picked_d[:B].copy_(first, non_blocking=True)
-        history = torch.zeros((n_steps, B), dtype=torch.int32, device=r.device)
+        total = warmup + n_steps
+        history = torch.zeros((total, B), dtype=torch.int32, device=r.device)
         entries = [StepEntry(q.rid, [0], [0]) for q in reqs]
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        ev0.record()
         self._temps_h[:B].zero_()
         self._temps_d[:B].copy_(self._temps_h[:B], non_blocking=True)
-        for i in range(n_steps):
+        for i in range(total):
+            if i == warmup:
+                torch.cuda.synchronize()
+                ev0.record()
+                launched0 = ops.launch_count() + r.kernels_replayed
             r.step(entries, device_tokens=self._picked_d, post=self._sample_post)
             history[i].copy_(self._picked_d[:B], non_blocking=True)
         ev1.record()
         torch.cuda.synchronize()
         r.check_status()
         ms = ev0.elapsed_time(ev1) / n_steps
+        self.kernels_in_timed_steps = ops.launch_count() + r.kernels_replayed - launched0
         hist = history.cpu().numpy()
         for j, q in enumerate(reqs):
             q.generated.extend(int(t) for t in hist[:, j])
-            q.computed += n_steps
+            q.computed += total
         return ms
 
     # ------------------------------------------------------------------ replay hook

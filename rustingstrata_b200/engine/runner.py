@@ -88,6 +88,7 @@ class ModelRunner:
         self.use_graphs = True
         self._graphs: Dict = {}
         self.graph_replays = 0
+        self.kernels_replayed = 0           # kernels this runner launched through graph replays
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -255,18 +256,21 @@ class ModelRunner:
                     # engine's pinned buffers or graphs there is "not permitted" and invalidates the capture
                     gc_was_on = gc.isenabled()
                     gc.disable()
+                    n0 = ops.launch_count()
                     try:
                         with torch.cuda.graph(graph):
                             logits = run()
                     finally:
                         if gc_was_on:
                             gc.enable()
-                    self._graphs[key] = (graph, logits)
+                    kernels = ops.launch_count() - n0          # kernel nodes of this graph
+                    self._graphs[key] = (graph, logits, kernels)
                     graph.replay()
                 else:
-                    graph, logits = entry
+                    graph, logits, kernels = entry
                     graph.replay()
                     self.graph_replays += 1
+                    self.kernels_replayed += kernels
         except Exception:
             for rid in reserved:
                 self.cache.rollback(rid)

@@ -236,7 +236,7 @@ def bf16lib():
         lib.rs_gemm_bf16_tc.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_void_p, c_void_p]
         lib.rs_skinny_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
-                                            c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+                                            c_int, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_skinny_gemm_workspace_floats.restype = c_long
         lib.rs_mid_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                          c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
@@ -321,14 +321,13 @@ _SKINNY_SCRATCH = {}
 
 
 def _skinny_scratch(device):
-    """Workspace and tile counters of the skinny product, one pair per device, made at the first call
+    """Workspace of the skinny product (partials of shared row tiles), one per device, made at the first call
     (before any graph capture: the engine runs every shape once eagerly first)."""
-    sc = _SKINNY_SCRATCH.get(device)
-    if sc is None:
-        ws = torch.empty(int(bf16lib().rs_skinny_gemm_workspace_floats()), dtype=torch.float32, device=device)
-        counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
-        sc = _SKINNY_SCRATCH[device] = (ws, counters)
-    return sc
+    ws = _SKINNY_SCRATCH.get(device)
+    if ws is None:
+        ws = _SKINNY_SCRATCH[device] = torch.empty(int(bf16lib().rs_skinny_gemm_workspace_floats()), dtype=torch.float32,
+                                                   device=device)
+    return ws
 
 
 def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
@@ -336,15 +335,15 @@ def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n
     """out[:n_rows] (=|+=) a[:n_rows] @ weight.T for n_rows <= 64: persistent CTAs stream the weight through a
     TMA-fed ring of shared-memory stages (csrc/skinny_gemm_tma.cu)."""
     N, K = _check_product(a, weight, out, n_rows, swiglu)
-    if n_rows > SKINNY_MAX_ROWS or not tensor_core_shape_ok(a, weight) or N > 64 * (1 << 16):
+    if n_rows > SKINNY_MAX_ROWS or not tensor_core_shape_ok(a, weight) or N <= 0:
         raise KernelError(f"skinny_gemm_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
                           f"{tuple(weight.shape)} {weight.dtype}: at most {SKINNY_MAX_ROWS} rows, bfloat16, 16-byte aligned")
     if status is None:
         status = _default_status(a.device)
-    ws, counters = _skinny_scratch(a.device)
+    ws = _skinny_scratch(a.device)
     _check(bf16lib().rs_skinny_gemm_bf16(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
                                          out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), _ptr(ws),
-                                         _ptr(counters), max_ctas, _ptr(status), _stream()), "skinny_gemm_bf16")
+                                         max_ctas, _ptr(status), _stream()), "skinny_gemm_bf16", 2)
 
 
 MID_MAX_ROWS = 128       # what the stream-K tcgen05 kernel takes; the engine uses it from SKINNY_ROWS + 1 rows up to here
