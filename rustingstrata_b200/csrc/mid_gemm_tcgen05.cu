@@ -1,4 +1,5 @@
-// bfloat16 matrix product for 33 to 128 rows of activations (large decode batches, short prompt portions) on the
+// bfloat16 matrix product for up to 128 rows of activations (the engine uses it from 17 rows: larger decode batches,
+// short prompt portions) on the
 // 5th-generation tensor cores, built like the skinny kernel around one job: stream the weight W[N, K] from HBM
 // exactly once, with every SM reading the same number of bytes.
 //

@@ -316,7 +316,8 @@ def gemm_bf16_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
 
 
 SKINNY_MAX_ROWS = 64     # what the kernel takes
-SKINNY_ROWS = 32         # up to here the engine prefers it to the tcgen05 kernel
+SKINNY_MAX_WEIGHT = 1 << 28   # weights of this many elements or more (an output head) stream faster through the tcgen05 kernel
+SKINNY_ROWS = 16         # up to here the engine prefers it; from 17 rows the stream-K tcgen05 kernel is faster
 _SKINNY_SCRATCH = {}
 
 
@@ -391,11 +392,11 @@ def _default_status(device) -> torch.Tensor:
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
            status: Optional[torch.Tensor] = None) -> None:
     """The engine's matrix product: the tensor-core kernels for bfloat16 operands whose rows are 16-byte
-    aligned (skinny kernel up to 32 rows, stream-K tcgen05 kernel up to 128, tiled tcgen05 kernel above), the
+    aligned (skinny kernel up to 16 rows, stream-K tcgen05 kernel up to 128, tiled tcgen05 kernel above), the
     CUDA-core kernel for everything else
     (the 32-bit engine, float32-stored weights, odd widths)."""
     if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
-        if n_rows <= SKINNY_ROWS:
+        if n_rows <= SKINNY_ROWS and weight.numel() < SKINNY_MAX_WEIGHT:
             skinny_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)
         elif n_rows <= MID_MAX_ROWS:
             mid_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)

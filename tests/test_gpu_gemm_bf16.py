@@ -138,11 +138,11 @@ def test_streaming_skinny_kernel_any_split_of_the_work(max_ctas):
         assert err(f1, want) < 1e-5 and torch.equal(f1, f2)
 
 
-@pytest.mark.parametrize("M", [1, 33, 40, 64, 65, 100, 128])
+@pytest.mark.parametrize("M", [1, 17, 33, 40, 64, 65, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 128), (100, 72), (4096, 4096), (6144, 4096), (1000, 1000), (24576, 4096),
                                  (4096, 12288), (151936, 256), (70, 8), (130, 136)])
 def test_stream_k_tcgen05_kernel(M, N, K):
-    """The kernel for 33 to 128 rows: every epilogue, rows beyond M untouched, widths and depths that end inside a
+    """The stream-K tcgen05 kernel (the engine's choice for 17 to 128 rows): every epilogue, rows beyond M untouched, widths and depths that end inside a
     tile, tiles finished by one CTA and tiles pieced together from several."""
     o = ops()
     a, w = make(M, N, K, cap=M + 2, seed=M)
