@@ -1,4 +1,4 @@
-// bfloat16 matrix product for up to 128 rows of activations (the engine uses it from 17 rows: larger decode batches,
+// bfloat16 matrix product for up to 128 rows of activations (the engine uses it from 9 rows: larger decode batches,
 // short prompt portions) on the
 // 5th-generation tensor cores, built like the skinny kernel around one job: stream the weight W[N, K] from HBM
 // exactly once, with every SM reading the same number of bytes.
@@ -6,7 +6,7 @@
 //   C[m, n] (=|+=) sum_k A[m, k] * W[n, k]
 //
 // The operands are swapped with respect to the large-M kernel: 128 rows of W are the M side of tcgen05.mma and
-// the (padded) rows of A its N side, so a tile of the accumulator in tensor memory is [128 rows of W] x [MP rows
+// the (padded: 16, 32, 64 or 128) rows of A its N side, so a tile of the accumulator in tensor memory is [128 rows of W] x [MP rows
 // of A] and no tensor-core row is wasted on padding.  The product is cut into units of (128 rows of W) x (128 of
 // k); the units, in row-tile-major order, are dealt to the persistent CTAs (one per SM) in equal contiguous
 // shares ("stream-K").  In a CTA
@@ -154,7 +154,7 @@ mid_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     constexpr int X_BOX_BYTES = MP * BOX_K * 2;
     constexpr int X_BYTES = X_BOX_BYTES * BOXES;
     constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-    constexpr int TMEM_COLS = 2 * MP;
+    constexpr int TMEM_COLS = 2 * MP < 64 ? 64 : 2 * MP;     // the epilogue reads 32 columns at a time
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -453,7 +453,7 @@ RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void*
         workspace == nullptr || counters == nullptr)
         return (int)cudaErrorInvalidValue;
     if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
-    const int mp = M <= 64 ? 64 : 128;
+    const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     CUtensorMap mw, ma;
     int rc = rs_tma::get_map(W, N, K, ldw, TILE_N, &mw);
     if (rc) return rc;
@@ -465,6 +465,8 @@ RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void*
     const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (mp == 16) return launch_epi<16>(epi, mw, ma, p, max_ctas, s);
+    if (mp == 32) return launch_epi<32>(epi, mw, ma, p, max_ctas, s);
     if (mp == 64) return launch_epi<64>(epi, mw, ma, p, max_ctas, s);
     return launch_epi<128>(epi, mw, ma, p, max_ctas, s);
 }

@@ -317,7 +317,7 @@ def gemm_bf16_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
 
 SKINNY_MAX_ROWS = 64     # what the kernel takes
 SKINNY_MAX_WEIGHT = 1 << 28   # weights of this many elements or more (an output head) stream faster through the tcgen05 kernel
-SKINNY_ROWS = 16         # up to here the engine prefers it; from 17 rows the stream-K tcgen05 kernel is faster
+SKINNY_ROWS = 8          # up to here the engine prefers it; from 9 rows the stream-K tcgen05 kernel is as fast or faster
 _SKINNY_SCRATCH = {}
 
 
@@ -392,7 +392,7 @@ def _default_status(device) -> torch.Tensor:
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
            status: Optional[torch.Tensor] = None) -> None:
     """The engine's matrix product: the tensor-core kernels for bfloat16 operands whose rows are 16-byte
-    aligned (skinny kernel up to 16 rows, stream-K tcgen05 kernel up to 128, tiled tcgen05 kernel above), the
+    aligned (skinny kernel up to 8 rows, stream-K tcgen05 kernel up to 128, tiled tcgen05 kernel above), the
     CUDA-core kernel for everything else
     (the 32-bit engine, float32-stored weights, odd widths)."""
     if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
