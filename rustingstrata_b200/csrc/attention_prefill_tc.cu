@@ -29,7 +29,11 @@
 namespace {
 constexpr int ROWS = 128;              // rows per CTA = TMEM lanes
 constexpr int BKV = 128;               // keys per block
-constexpr int THREADS = 320;             // warps 0-7 softmax, warp 8 MMA issuer, warp 9 TMA producer
+constexpr int PARTS = 2;                // softmax threads per row: each takes 128 / PARTS keys of a block and hd / PARTS dims of O
+                                        // (four threads per row, 16 softmax warps, were 4 % slower: the softmax is not short of warps)
+constexpr int SOFTMAX_WARPS = 4 * PARTS;
+constexpr int MMA_WARP = SOFTMAX_WARPS, TMA_WARP = SOFTMAX_WARPS + 1;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr int KV_STAGES = 2;
 
 struct TcParams {
@@ -77,6 +81,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -122,7 +134,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint8_t* aligned = smem_raw + (base - raw);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* xchg = reinterpret_cast<float*>(tmem_slot + 4);     // [2 blocks parity][2 halves][ROWS] maxima, then [2][ROWS] sums
+    float* xchg = reinterpret_cast<float*>(tmem_slot + 4);     // [2 blocks parity][PARTS][ROWS] maxima, then [PARTS][ROWS] sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = p.work[2 * blockIdx.x], q_off = p.work[2 * blockIdx.x + 1];
@@ -145,13 +157,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1);
-            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), 8);
+            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), SOFTMAX_WARPS);
         }
         mbar_init(bar(O_FULL), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -160,7 +172,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 9) {
+    if (warp == TMA_WARP) {
         // ------------------------------------------------------------ TMA producer: lane i loads page i of a block
         if (lane == 0) {
             mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
@@ -209,7 +221,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!ok) break;
             page = page_next;
         }
-    } else if (warp == 8) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && n_blocks > 0) {
             const uint32_t idesc_qk = idesc_bf16(ROWS, BKV, 0), idesc_pv = idesc_bf16(ROWS, HD, 1);
@@ -245,80 +257,95 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     } else {
-        // ------------------------------------------------------------ softmax warps 0..7: two threads per row
-        // warps w and w + 4 own the same 32 rows (tensor-memory lanes 32 (w & 3) ..): the first takes the keys
-        // [0, 64) of a block and the head dims [0, hd/2) of O, the second the other halves.  The two exchange
-        // their row maxima through shared memory once per block; their partial sums meet at the end.
-        constexpr int HK = BKV / 2, HO = HD / 2;
+        // ------------------------------------------------------------ softmax warps: PARTS threads per row
+        // The warps w, w + 4, w + 8, ... own the same 32 rows (tensor-memory lanes 32 (w & 3) ..): warp number `part`
+        // of them takes the keys [part * HK, +HK) of a block and the head dims [part * HO, +HO) of O.  They exchange
+        // their row maxima through shared memory once per block; their partial sums meet at the end.  A warp whose
+        // wait ran out keeps walking the blocks without touching them, so that the named barriers stay in step.
+        constexpr int HK = BKV / PARTS, HO = HD / PARTS;
+        static_assert(HK % 32 == 0 && (HO % 32 == 0 || HO == 16), "scores in loads of 32 columns; O in loads of 32 or 16 columns");
+        constexpr int OC = HO >= 32 ? 32 : 16;       // columns of O per load
         constexpr float RESCALE_ABOVE = 8.f;         // log2 units: keep the old maximum while the new one is within 2^8 of it
-        const int quarter = warp & 3, half = warp >> 2;
+        const int quarter = warp & 3, part = warp >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t o_addr = lane_base + 256 + half * HO;
+        const uint32_t o_addr = lane_base + 256 + part * HO;
         const int qpos = qpos0 + r / p.pack;
         float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
-        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
-        for (int j = 0; j < n_blocks && ok; ++j) {
+        auto row_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + quarter), "n"(PARTS * 32) : "memory"); };
+        auto load_o = [&](int c, uint32_t* v) {
+            if (OC == 32) tmem_ld32(o_addr + c, v); else tmem_ld16(o_addr + c, v);
+            tmem_ld_wait();
+        };
+        for (int j = 0; j < n_blocks; ++j) {
             const int s = j & 1;
-            const int k0 = (blk_lo + j) * BKV + half * HK;           // first key of this thread's half block
-            if (!mbar_wait(bar(S_FULL + s), (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t s_addr = lane_base + s * 128 + half * HK;
             const int kb0 = (blk_lo + j) * BKV;
-            const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
-                                   (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
-            // the row's scores of this half block, once, into registers (scaled to log2 units, masked)
+            const int k0 = kb0 + part * HK;                            // first key of this thread's part of the block
+            if (ok) ok = mbar_wait(bar(S_FULL + s), (j >> 1) & 1, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);                          // tensor-memory loads and stores are warp-wide
             float x[HK];
+            float mx = -INFINITY;
+            if (ok) {
+                tc_fence_after();
+                const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
+                                       (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
+                // the row's scores of this part of the block, once, into registers (scaled to log2 units, masked)
 #pragma unroll
-            for (int c = 0; c < HK; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(s_addr + c, v);
-                tmem_ld_wait();
+                for (int c = 0; c < HK; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_base + s * 128 + part * HK + c, v);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) x[c + i] = __uint_as_float(v[i]) * p.scale_log2;
-            }
-            if (need_mask) {
-#pragma unroll
-                for (int i = 0; i < HK; ++i) {
-                    const int kpos = k0 + i;
-                    const bool vis = kpos <= qpos && kpos < key_hi && kpos >= key_lo && (p.window <= 0 || kpos > qpos - p.window);
-                    x[i] = vis ? x[i] : -INFINITY;
+                    for (int i = 0; i < 32; ++i) x[c + i] = __uint_as_float(v[i]) * p.scale_log2;
                 }
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < HK; i += 4) {
-                mx0 = fmaxf(mx0, x[i]); mx1 = fmaxf(mx1, x[i + 1]); mx2 = fmaxf(mx2, x[i + 2]); mx3 = fmaxf(mx3, x[i + 3]);
+                    for (int i = 0; i < HK; ++i) {
+                        const int kpos = k0 + i;
+                        const bool vis = kpos <= qpos && kpos < key_hi && kpos >= key_lo && (p.window <= 0 || kpos > qpos - p.window);
+                        x[i] = vis ? x[i] : -INFINITY;
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < HK; i += 4) {
+                    mx0 = fmaxf(mx0, x[i]); mx1 = fmaxf(mx1, x[i + 1]); mx2 = fmaxf(mx2, x[i + 2]); mx3 = fmaxf(mx3, x[i + 3]);
+                }
+                mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            xchg[((j & 1) * 2 + half) * ROWS + r] = mx;
-            pair_sync();
-            const float m_blk = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * ROWS + r]);
+            xchg[((j & 1) * PARTS + part) * ROWS + r] = mx;
+            row_sync();
+            float m_blk = mx;
+#pragma unroll
+            for (int q = 0; q < PARTS; ++q) m_blk = fmaxf(m_blk, xchg[((j & 1) * PARTS + q) * ROWS + r]);
+            if (!ok) continue;
             // The reference maximum only moves when the block's maximum exceeds it by more than 2^8 (or it was
-            // still -inf): then everything accumulated so far, O in tensor memory included, is rescaled.  Both
+            // still -inf): then everything accumulated so far, O in tensor memory included, is rescaled.  All
             // threads of a row see the same numbers and take the same decision.
             const bool move = m_blk > m_used + RESCALE_ABOVE || (m_used == -INFINITY && m_blk > -INFINITY);
             if (__any_sync(0xffffffffu, move)) {
                 const float corr = move ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_blk)) : 1.f;
                 if (j > 0) {                                          // O holds the products of blocks 0..j-1
-                    if (!mbar_wait(bar(O_FULL), (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
-                    tc_fence_after();
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(O_FULL), (j - 1) & 1, abort_flag, p.status));
+                    if (ok) {
+                        tc_fence_after();
 #pragma unroll
-                    for (int c = 0; c < HO; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(o_addr + c, v);
-                        tmem_ld_wait();
+                        for (int c = 0; c < HO; c += OC) {
+                            uint32_t v[32];
+                            load_o(c, v);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                        tmem_st16(o_addr + c, v);
-                        tmem_st16(o_addr + c + 16, v + 16);
+                            for (int i = 0; i < OC; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                            tmem_st16(o_addr + c, v);
+                            if (OC == 32) tmem_st16(o_addr + c + 16, v + 16);
+                        }
+                        tmem_st_wait();
                     }
-                    tmem_st_wait();
                 }
                 l_run *= corr;
                 if (move) m_used = m_blk;
             }
+            if (!ok) continue;
             // P = 2^(x - m), its sum, and P as bfloat16 pairs written over S
             const float sub = (m_used == -INFINITY) ? 0.f : m_used;     // nothing visible yet: every x is -inf, P = 0
             float rs0 = 0.f, rs1 = 0.f;
@@ -332,7 +359,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
                     pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
                 }
-                tmem_st16(lane_base + s * 128 + ((half * HK + c) >> 1), pk);
+                tmem_st16(lane_base + s * 128 + ((part * HK + c) >> 1), pk);
             }
             tmem_st_wait();
             l_run += rs0 + rs1;
@@ -340,24 +367,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_READY + s));
         }
-        // the row's sum: both halves used the same reference maxima, so their partial sums simply add
-        xchg[(4 + half) * ROWS + r] = l_run;
-        pair_sync();
-        l_run += xchg[(4 + (half ^ 1)) * ROWS + r];
-        if (ok) ok = mbar_wait(bar(O_FULL), (n_blocks - 1) & 1, abort_flag, p.status);
-        tc_fence_after();
-        if (ok) {
+        // the row's sum: all parts used the same reference maxima, so their partial sums simply add (in a fixed order)
+        xchg[(2 * PARTS + part) * ROWS + r] = l_run;
+        row_sync();
+        l_run = 0.f;
+#pragma unroll
+        for (int q = 0; q < PARTS; ++q) l_run += xchg[(2 * PARTS + q) * ROWS + r];
+        if (ok && n_blocks > 0) ok = mbar_wait(bar(O_FULL), (n_blocks - 1) & 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && n_blocks > 0) {
+            tc_fence_after();
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
             __nv_bfloat16* dst = p.out + (size_t)(row0 + q_off + r / p.pack) * p.out_stride + (size_t)(head0 + r % p.pack) * HD +
-                                 half * HO;
+                                 part * HO;
 #pragma unroll
-            for (int c = 0; c < HO; c += 32) {
+            for (int c = 0; c < HO; c += OC) {
                 uint32_t v[32];
-                tmem_ld32(o_addr + c, v);                              // warp-collective: rows beyond the tile load too
-                tmem_ld_wait();
+                load_o(c, v);                                          // warp-collective: rows beyond the tile load too
                 if (r < n_rows) {
 #pragma unroll
-                    for (int d = 0; d < 32; d += 8) {
+                    for (int d = 0; d < OC; d += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
@@ -376,7 +405,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         while (global_ns() - t0 < 200000ull) __nanosleep(1000);
     }
     __syncthreads();
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
@@ -459,7 +488,7 @@ int cached_page_map(const void* cache, int num_pages, int n_kv, int page_size, i
 
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int n_work, cudaStream_t s) {
-    constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 17 + 64 + 6 * ROWS * 4;
+    constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 17 + 64 + 3 * PARTS * ROWS * 4;
     auto kern = prefill_attention_tc_kernel<HD>;
     static bool attr_set = false;
     if (!attr_set) {
