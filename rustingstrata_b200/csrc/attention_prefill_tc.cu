@@ -290,14 +290,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_fence_after();
                 const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
                                        (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
-                // the row's scores of this part of the block, once, into registers (scaled to log2 units, masked)
+                // the row's scores of this part of the block, once, into registers (masked)
 #pragma unroll
                 for (int c = 0; c < HK; c += 32) {
                     uint32_t v[32];
                     tmem_ld32(lane_base + s * 128 + part * HK + c, v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) x[c + i] = __uint_as_float(v[i]) * p.scale_log2;
+                    for (int i = 0; i < 32; ++i) x[c + i] = __uint_as_float(v[i]);      // raw scores: the scale goes into the exponent's FMA
                 }
                 if (need_mask) {
 #pragma unroll
@@ -312,7 +312,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int i = 0; i < HK; i += 4) {
                     mx0 = fmaxf(mx0, x[i]); mx1 = fmaxf(mx1, x[i + 1]); mx2 = fmaxf(mx2, x[i + 2]); mx3 = fmaxf(mx3, x[i + 3]);
                 }
-                mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;         // the scale is positive: it commutes with the maximum
             }
             xchg[((j & 1) * PARTS + part) * ROWS + r] = mx;
             row_sync();
@@ -354,7 +354,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float e0 = fast_exp2(x[c + i] - sub), e1 = fast_exp2(x[c + i + 1] - sub);
+                    const float e0 = fast_exp2(fmaf(x[c + i], p.scale_log2, -sub)), e1 = fast_exp2(fmaf(x[c + i + 1], p.scale_log2, -sub));
                     rs0 += e0; rs1 += e1;
                     __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
                     pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
