@@ -441,3 +441,17 @@ def test_temperature_draw_distribution_and_edges():
     out3 = torch.zeros(2, dtype=torch.int32, device=DEV)
     o.sample(logits[:2].contiguous(), 2, out3, status(), temps3, u3)
     assert out3.tolist() == [3, 400]          # p^4 normalised: 0.5^4 / sum = 0.877 < 0.9 → second token
+
+
+# ------------------------------------------------------------------------------- ids of the next step, on the device
+@pytest.mark.parametrize("n", [1, 7, 128, 129, 1000])
+def test_gather_of_chosen_ids(n):
+    o = ops()
+    g = torch.Generator().manual_seed(n)
+    src = torch.randint(0, 1 << 20, (1500,), generator=g, dtype=torch.int32)
+    idx = torch.randint(0, 1500, (n,), generator=g, dtype=torch.int32)
+    dst = torch.full((n + 3,), -5, dtype=torch.int32, device=DEV)
+    o.gather_i32(dst, src.to(DEV), idx.to(DEV), n)
+    assert torch.equal(dst[:n].cpu(), src[idx.long()]) and torch.all(dst[n:] == -5)
+    with pytest.raises(o.KernelError):
+        o.gather_i32(dst, src.to(DEV).float(), idx.to(DEV), n)
