@@ -96,16 +96,17 @@ struct GemmParams {
     void* C; long ldc;
     int M, N, K;
     int vec_ok;            // C rows allow 16-byte vector access
+    int bn;                // columns per tile: the template's BN, or less (a multiple of 16) in buffers sized for BN
     int* status;
 };
 
 template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0) {
-    // r: 32 consecutive accumulator columns [col0, col0 + 32) of output row `row`
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int nmax) {
+    // r: 32 consecutive accumulator columns [col0, col0 + 32) of output row `row`; columns from nmax on are not this tile's
     if (row >= p.M) return;
     if (EPI == EPI_SWIGLU_BF16) {
         // columns alternate gate, up: out[row, (col0 + 2j) / 2] = silu(gate_j) * up_j
-        const int half_n = p.N >> 1, oc0 = col0 >> 1;
+        const int half_n = nmax >> 1, oc0 = col0 >> 1;
         __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + oc0;
         if (p.vec_ok && oc0 + 16 <= half_n) {
             uint32_t packed[8];
@@ -129,7 +130,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
         }
     } else if (EPI == EPI_STORE_BF16) {
         __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col0;
-        if (p.vec_ok && col0 + 32 <= p.N) {
+        if (p.vec_ok && col0 + 32 <= nmax) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t w[4];
@@ -143,11 +144,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                if (col0 + j < nmax) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
         }
     } else {   // float32 store or accumulate
         float* out = (float*)p.C + (size_t)row * p.ldc + col0;
-        if (p.vec_ok && col0 + 32 <= p.N) {
+        if (p.vec_ok && col0 + 32 <= nmax) {
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
@@ -161,7 +162,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) out[j] = (EPI == EPI_ADD_F32 ? out[j] : 0.f) + __uint_as_float(r[j]);
+                if (col0 + j < nmax) out[j] = (EPI == EPI_ADD_F32 ? out[j] : 0.f) + __uint_as_float(r[j]);
         }
     }
 }
@@ -185,7 +186,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    const int bn = p.bn;                                                // <= BN: buffers and tensor-memory columns are laid out for BN
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + bn - 1) / bn;
     const int num_tiles = tiles_m * tiles_n, num_kb = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -209,10 +211,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int s = 0; uint32_t phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;       // m fastest: neighbours share W
+                const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * bn;       // m fastest: neighbours share W
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                    mbar_expect_tx(full_bar(s), A_BYTES + bn * BK * 2);
                     const uint32_t sa = base + s * C::STAGE_BYTES;
                     tma_load_2d(sa, &map_a, kb * BK, m0, full_bar(s));
                     tma_load_2d(sa + A_BYTES, &map_w, kb * BK, n0, full_bar(s));
@@ -223,7 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(BM, BN);
+            const uint32_t idesc = make_idesc(BM, bn);
             int s = 0; uint32_t phase = 0;
             bool ok = true;
             int local = 0;
@@ -253,16 +255,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
             const int buf = local & 1;
-            const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+            const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * bn;
+            const int nmax = min(p.N, n0 + bn);
             if (!mbar_wait(tfull_bar(buf), (local >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int c = 0; c < bn; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c, r);
                 tmem_ld_wait();
-                if (n0 + c < p.N) epilogue_chunk<EPI>(p, r, row, n0 + c);
+                if (n0 + c < nmax) epilogue_chunk<EPI>(p, r, row, n0 + c, nmax);
             }
             tc_fence_before();
             __syncwarp();
@@ -295,7 +298,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, in
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + p.bn - 1) / p.bn);
     int grid = tiles < sm_count() ? tiles : sm_count();
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
     kern<<<grid, THREADS, Cfg<BN>::SMEM_BYTES, s>>>(ma, mw, p);
@@ -325,19 +328,25 @@ RS_EXPORT int rs_gemm_tc_supported(long a_ptr, long lda, long w_ptr, long ldw, i
 
 // C[M, N] (=|+=) A[M, K] . W[N, K]^T with bf16 inputs.  a_rows is the row capacity of A's buffer (>= M): the
 // tensor map covers the whole buffer, rows beyond M are computed and dropped.  epi: 0 bf16 store, 1 f32 store,
-// 2 f32 accumulate, 3 SiLU(gate)*up over interleaved columns into a bf16 [M, N/2] output.  bn: 64, 128, 256 or
-// 0 to choose.  max_ctas > 0 caps the grid (tests use it to force several tiles per CTA).
+// 2 f32 accumulate, 3 SiLU(gate)*up over interleaved columns into a bf16 [M, N/2] output.  bn: columns per tile, 64, 128,
+// a multiple of 16 from 144 to 256, or 0 to choose.  max_ctas > 0 caps the grid (tests use it to force several tiles per CTA).
 RS_EXPORT int rs_gemm_bf16_tc(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M,
                               int N, int K, int epi, int bn, int max_ctas, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!rs_gemm_tc_supported((long)A, lda, (long)W, ldw, N, K, epi) || a_rows < M) return (int)cudaErrorInvalidValue;
+    int tpl = bn;                                        // template instantiation (buffer sizes): 64, 128 or 256
     if (bn == 0) {
         // widest tile that still gives every SM work: 256 columns need the fewest loads of A per flop
         const long tm = (M + BM - 1) / BM;
         const int sms = sm_count();
-        if (tm * ((N + 255) / 256) * 4 >= 3L * sms) bn = 256;
-        else if (tm * ((N + 127) / 128) * 4 >= 3L * sms) bn = 128;
-        else bn = 64;
+        // (Narrower tiles that would fill the last wave better, 240 or 176 columns for 4096 or 6144, were measured: each
+        // was slower than 256 by 2 to 17 %, the narrower tile costs more than the fuller wave gives.)
+        if (tm * ((N + 255) / 256) * 4 >= 3L * sms) {
+            bn = tpl = 256;
+        } else if (tm * ((N + 127) / 128) * 4 >= 3L * sms) bn = tpl = 128;
+        else bn = tpl = 64;
+    } else if (bn > 128 && bn <= 256 && bn % 16 == 0) {
+        tpl = 256;
     }
     CUtensorMap ma, mw;
     int rc = get_map(A, a_rows, K, lda, BM, &ma);
@@ -345,12 +354,12 @@ RS_EXPORT int rs_gemm_bf16_tc(const void* A, long lda, long a_rows, const void* 
     rc = get_map(W, N, K, ldw, bn, &mw);
     if (rc) return rc;
     GemmParams p;
-    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status; p.bn = bn;
     const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (bn == 256) return launch_epi<256>(epi, ma, mw, p, max_ctas, s);
-    if (bn == 128) return launch_epi<128>(epi, ma, mw, p, max_ctas, s);
-    if (bn == 64) return launch_epi<64>(epi, ma, mw, p, max_ctas, s);
+    if (tpl == 256) return launch_epi<256>(epi, ma, mw, p, max_ctas, s);
+    if (tpl == 128 && bn == 128) return launch_epi<128>(epi, ma, mw, p, max_ctas, s);
+    if (tpl == 64 && bn == 64) return launch_epi<64>(epi, ma, mw, p, max_ctas, s);
     return (int)cudaErrorInvalidValue;
 }

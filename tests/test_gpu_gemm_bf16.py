@@ -36,7 +36,7 @@ SHAPES = [(128, 256, 64), (128, 128, 128), (129, 136, 72), (300, 520, 200), (204
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("bn", [0, 64, 128, 144, 176, 240, 256])
 def test_tcgen05_gemm_store_and_accumulate(M, N, K, bn):
     o = ops()
     a, w = make(M, N, K, cap=M + 5)
@@ -70,6 +70,24 @@ def test_tcgen05_gemm_swiglu_and_several_tiles_per_cta(M, N, K, max_ctas):
     f = torch.zeros(M, N, device=DEV)
     o.gemm_bf16_tc(a, w, f, M, status=st, max_ctas=max_ctas, bn=128)
     assert err(f, a.double() @ w.double().T) < 1e-5 and st.item() == 0
+
+
+@pytest.mark.parametrize("bn", [144, 208, 224, 240])
+def test_tcgen05_gemm_tile_widths_between_128_and_256_with_the_fused_epilogue(bn):
+    """Tiles whose width is not a multiple of the 32-column epilogue step: the last step of a tile must not write
+    into the next tile's columns (gate/up pairs included), with several tiles per CTA."""
+    o = ops()
+    for (M, N, K) in ((300, 1000, 200), (2048, 4096, 512)):
+        a, w = make(M, N, K, seed=2)
+        full = a.double() @ w.double().T
+        st = torch.zeros(1, dtype=torch.int32, device=DEV)
+        sw = torch.zeros(M, N // 2, device=DEV, dtype=torch.bfloat16)
+        o.gemm_bf16_tc(a, w, sw, M, swiglu=True, status=st, bn=bn, max_ctas=5)
+        assert err(sw, silu_mul(full)) < 8e-3
+        base = torch.randn(M, N, device=DEV)
+        acc = base.clone()
+        o.gemm_bf16_tc(a, w, acc, M, accumulate=True, status=st, bn=bn, max_ctas=5)
+        assert err(acc, base.double() + full) < 1e-5 and st.item() == 0
 
 
 def test_tcgen05_gemm_strided_views_and_unaligned_output():
