@@ -94,51 +94,19 @@ def cmd_generate(args):
     return 0
 
 
-def bench_once(eng, prompts, tg):
-    """One repetition: timed prefill of every prompt (one step each batch), then timed greedy decode."""
-    import torch
-    from .sampling import SamplingParams
-    for p in prompts:
-        eng.add_request(p, tg + 1, SamplingParams())
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    eng.lookahead = False                  # as above
-    while eng.scheduler.waiting or any(r.prefilling for r in eng.scheduler.running):
-        eng.step()
-    torch.cuda.synchronize()
-    eng.lookahead = True
-    t1 = time.perf_counter()
-    steps = 0
-    while eng.has_work():
-        eng.step()
-        steps += 1
-    torch.cuda.synchronize()
-    t2 = time.perf_counter()
-    n_prompt = sum(len(p) for p in prompts)
-    return n_prompt / (t1 - t0), len(prompts) * steps / (t2 - t1)
-
-
-def _stat(xs):
-    return f"{sum(xs) / len(xs):.1f} ({min(xs):.1f}-{max(xs):.1f})"
+def _stat(d):
+    return f"{d['mean']:.1f} ({d['min']:.1f}-{d['max']:.1f})"
 
 
 def cmd_bench(args):
-    import numpy as np
     pps = [int(x) for x in args.pp.split(",")]
     ctx = max(args.ctx, (max(pps) + args.tg + 1) * args.batch)
     eng = _make_engine(args, ctx=ctx, max_seqs=max(args.batch, 1))
-    rng = np.random.default_rng(0)
     results = []
     for n in pps:
-        pre, dec = [], []
-        for _ in range(args.reps):
-            prompts = [rng.integers(0, eng.runner.vocab_size, size=n).tolist() for _ in range(args.batch)]
-            p, d = bench_once(eng, prompts, args.tg)
-            pre.append(p)
-            dec.append(d)
-        print(f"pp {n:6d}: prefill {_stat(pre)} tok/s | tg {args.tg}: decode {_stat(dec)} tok/s")
-        results.append({"pp": n, "batch": args.batch, "prefill_tok_s": {"mean": sum(pre) / len(pre), "min": min(pre), "max": max(pre)},
-                        "decode_tok_s": {"mean": sum(dec) / len(dec), "min": min(dec), "max": max(dec)}})
+        rec = eng.bench([n], args.tg, args.reps, args.batch)[0]
+        print(f"pp {n:6d}: prefill {_stat(rec['prefill_tok_s'])} tok/s | tg {args.tg}: decode {_stat(rec['decode_tok_s'])} tok/s")
+        results.append(rec)
     if args.json_out:
         rec = {"schema": "rustingstrata_b200.bench.v1", "model": args.model, "dtype": args.dtype, "ctx": ctx, "tg": args.tg,
                "reps": args.reps, "unix_time": int(time.time()), "results": results}

@@ -246,6 +246,42 @@ class Engine:
         outs = [results[r] for r in rids]
         return outs[0] if single else outs
 
+    # ------------------------------------------------------------------ timed prefill and decode
+    def bench(self, pp: Sequence[int] = (512, 4096), tg: int = 128, reps: int = 3, batch: int = 1, seed: int = 0) -> List[dict]:
+        """The reference's ``bench`` (src/main.rs:1192-1265) as a method: for every prompt length in ``pp``, ``reps``
+        times: ``batch`` prompts of seeded random ids are run to the end of their prompts (timed: prefill tok/s), then
+        ``tg`` tokens each are decoded greedily (timed: decode tok/s over all requests).  Wall-clock times around
+        ``step`` with a device synchronisation on both sides.  Returns one record per prompt length with mean, min
+        and max of both rates."""
+        import time
+        rng = np.random.default_rng(seed)
+        out = []
+        for n in pp:
+            pre, dec = [], []
+            for _ in range(reps):
+                self.drain()
+                for _ in range(batch):
+                    self.add_request(rng.integers(0, self.runner.vocab_size, size=n).tolist(), tg + 1, SamplingParams())
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                look, self.lookahead = self.lookahead, False   # the prompts' time must not hold the first decode step
+                while self.scheduler.waiting or any(r.prefilling for r in self.scheduler.running):
+                    self.step()
+                torch.cuda.synchronize()
+                self.lookahead = look
+                t1 = time.perf_counter()
+                steps = 0
+                while self.has_work():
+                    self.step()
+                    steps += 1
+                torch.cuda.synchronize()
+                t2 = time.perf_counter()
+                pre.append(n * batch / (t1 - t0))
+                dec.append(batch * steps / (t2 - t1))
+            stat = lambda xs: {"mean": sum(xs) / len(xs), "min": min(xs), "max": max(xs)}  # noqa: E731
+            out.append({"pp": int(n), "tg": int(tg), "batch": int(batch), "prefill_tok_s": stat(pre), "decode_tok_s": stat(dec)})
+        return out
+
     # ------------------------------------------------------------------ device-resident greedy decode
     def decode_steps_device_timed(self, n_steps: int, warmup: int = 3) -> float:
         """Runs ``warmup + n_steps`` greedy decode steps of all running requests with the chosen ids staying on

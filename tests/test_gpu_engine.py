@@ -231,3 +231,14 @@ def test_steps_launched_ahead_change_nothing(tiny_models, dtype):
     fast_e, n2 = run(True, eos)
     assert fast_e == slow_e and n2 > 5
     assert slow_e[1][1] == "eos" and len(slow_e[1][0]) <= 10
+
+
+def test_bench_method_of_the_entry_point(tiny_models):
+    eng = engine(tiny_models, "D", "bfloat16")
+    recs = eng.bench(pp=[20, 130], tg=6, reps=2, batch=3)
+    assert [r["pp"] for r in recs] == [20, 130] and all(r["batch"] == 3 and r["tg"] == 6 for r in recs)
+    for r in recs:
+        for k in ("prefill_tok_s", "decode_tok_s"):
+            assert 0 < r[k]["min"] <= r[k]["mean"] <= r[k]["max"]
+    assert not eng.has_work()
+    eng.runner.cache.check()
