@@ -19,8 +19,12 @@ import time
 
 
 def _engine_flags(ap):
-    ap.add_argument("--model", required=True, help="model folder (config.json + model.safetensors)")
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--model", default=None, help="model folder (config.json + model.safetensors)")
+    ap.add_argument("--random-weights", action="store_true",
+                    help="no model folder: draw the weights on the device from --config and --weights-seed")
+    ap.add_argument("--config", default=None, help="config.json of the architecture (with --random-weights)")
+    ap.add_argument("--weights-seed", type=int, default=0)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     ap.add_argument("--ctx", type=int, default=4096, help="cache size in tokens")
     ap.add_argument("--chunk", type=int, default=None, help="prefill portion in tokens [default: the token budget]")
     ap.add_argument("--page-size", type=int, default=16)
@@ -51,8 +55,17 @@ def _sampling(args):
 def _make_engine(args, ctx=None, max_seqs=None):
     from .engine import Engine
     ctx = ctx or args.ctx
-    return Engine(args.model, dtype=args.dtype, page_size=args.page_size, max_tokens=ctx,
-                  max_batch_tokens=min(max(ctx, 64), 8192), max_seqs=max_seqs or args.parallel, prefill_chunk=args.chunk)
+    dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(args.dtype, args.dtype)
+    kw = dict(dtype=dtype, page_size=args.page_size, max_tokens=ctx, max_batch_tokens=min(max(ctx, 64), 8192),
+              max_seqs=max_seqs or args.parallel, prefill_chunk=args.chunk)
+    if args.random_weights:
+        if not args.config:
+            raise SystemExit("--random-weights needs --config config.json")
+        with open(args.config) as f:
+            return Engine(json.load(f), random_seed=args.weights_seed, **kw)
+    if not args.model:
+        raise SystemExit("give --model DIR, or --random-weights --config config.json")
+    return Engine(args.model, **kw)
 
 
 def _prompt_ids(args, vocab):
@@ -108,7 +121,7 @@ def cmd_bench(args):
         print(f"pp {n:6d}: prefill {_stat(rec['prefill_tok_s'])} tok/s | tg {args.tg}: decode {_stat(rec['decode_tok_s'])} tok/s")
         results.append(rec)
     if args.json_out:
-        rec = {"schema": "rustingstrata_b200.bench.v1", "model": args.model, "dtype": args.dtype, "ctx": ctx, "tg": args.tg,
+        rec = {"schema": "rustingstrata_b200.bench.v1", "model": args.model or args.config, "dtype": args.dtype, "ctx": ctx, "tg": args.tg,
                "reps": args.reps, "unix_time": int(time.time()), "results": results}
         with open(args.json_out, "w") as f:
             f.write(json.dumps(rec) + "\n")
@@ -158,7 +171,8 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate", help="generation (greedy unless --temp)")
     _engine_flags(g)
-    g.add_argument("--prompt", default="", help='prompt token ids, e.g. "1,2,3" ("-" reads standard input)')
+    g.add_argument("--prompt", "--prompt-ids", dest="prompt", default="",
+                   help='prompt token ids, e.g. "1,2,3" ("-" reads standard input)')
     g.add_argument("--prompt-len", type=int, default=0, help="draw this many random prompt ids instead")
     g.add_argument("--prompt-seed", type=int, default=0)
     g.add_argument("-n", type=int, default=32, help="tokens to generate")
