@@ -21,8 +21,8 @@
 //                          (sequence, split, head).  Then the stage goes back to the producer.
 // With few warps per SM every dependent instruction's latency shows, so the consumers do as little as they
 // can (one pass, no running maximum) and three groups overlap one another's chains.
-// The merge kernel adds the splits of a head in ascending order.  Keys of a split are visited in the same
-// order whatever the batch holds, so a row's result does not depend on its neighbours.  Pages an item does
+// The merge kernel adds the splits of a head in an order that the sequence's length alone fixes (see there).  Keys of
+// a split are visited in the same order whatever the batch holds, so a row's result does not depend on its neighbours.  Pages an item does
 // not own (beyond the sequence, given back by a window) are replaced by page 0: their keys are masked and
 // their values only have to be finite.  Waits on mbarriers are bounded (tma_helpers.cuh).
 //
