@@ -122,42 +122,43 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int U = tiles * KB, G = gridDim.x;
     const int u0 = first_unit(blockIdx.x, U, G), u1 = first_unit(blockIdx.x + 1, U, G);
 
-    if (threadIdx.x == 0) {
+    auto load_w = [&](int s, int tile, int kb) {
+        const uint32_t dst = base + s * STAGE_BYTES;
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b)
+            tma_load_2d(dst + b * W_BOX_BYTES, &map_w, kb * TILE_K + b * BOX_K, tile * TILE_N, full_bar(s));
+    };
+    auto load_x = [&](int s, int kb) {
+        const uint32_t dst = base + s * STAGE_BYTES + W_BYTES;
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b)
+            tma_load_2d(dst + b * X_BOX_BYTES, &map_a, kb * TILE_K + b * BOX_K, 0, full_bar(s));
+    };
+    // The producer's lane sets the barriers up itself and starts the first ring of weights (which no kernel writes)
+    // before the CTA meets, so that the loads are on their way while the other warps are still arriving.
+    const int ahead = min(stages, u1 - u0);
+    if (warp == CONSUMER_WARPS && lane == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), CONSUMER_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pdl_launch_dependents();
+        int tile = u0 / KB, kb = u0 % KB;
+        for (int i = 0; i < ahead; ++i) {
+            mbar_expect_tx(full_bar(i), W_BYTES + X_BYTES);
+            load_w(i, tile, kb);
+            if (++kb == KB) { kb = 0; ++tile; }
+        }
     }
     __syncthreads();
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            pdl_launch_dependents();
-            auto load_w = [&](int s, int tile, int kb) {
-                const uint32_t dst = base + s * STAGE_BYTES;
-#pragma unroll
-                for (int b = 0; b < BOXES; ++b)
-                    tma_load_2d(dst + b * W_BOX_BYTES, &map_w, kb * TILE_K + b * BOX_K, tile * TILE_N, full_bar(s));
-            };
-            auto load_x = [&](int s, int kb) {
-                const uint32_t dst = base + s * STAGE_BYTES + W_BYTES;
-#pragma unroll
-                for (int b = 0; b < BOXES; ++b)
-                    tma_load_2d(dst + b * X_BOX_BYTES, &map_a, kb * TILE_K + b * BOX_K, 0, full_bar(s));
-            };
-            // fill the ring with weights before waiting for the kernel that writes A
-            const int ahead = min(stages, u1 - u0);
-            int tile = u0 / KB, kb = u0 % KB;
-            for (int i = 0; i < ahead; ++i) {
-                mbar_expect_tx(full_bar(i), W_BYTES + X_BYTES);
-                load_w(i, tile, kb);
-                if (++kb == KB) { kb = 0; ++tile; }
-            }
-            pdl_wait();
-            kb = u0 % KB;
-            for (int i = 0; i < ahead; ++i) {
-                load_x(i, kb);
-                if (++kb == KB) kb = 0;
+            int tile = (u0 + ahead) / KB, kb = (u0 + ahead) % KB;          // the next unit whose weights are to be asked for
+            pdl_wait();                                                   // the kernel that writes A is done
+            for (int i = 0, kx = u0 % KB; i < ahead; ++i) {
+                load_x(i, kx);
+                if (++kx == KB) kx = 0;
             }
             int s = ahead == stages ? 0 : ahead; uint32_t phase = ahead == stages ? 1u : 0u;
             for (int u = u0 + ahead; u < u1; ++u) {
