@@ -1,0 +1,563 @@
+// Attention of long prompt portions on the 5th-generation tensor cores with TWO query tiles per CTA (head sizes 64
+// and 128).  Same arithmetic, layouts and masks as attention_prefill_tc.cu, which it follows line by line where it
+// can; what differs is the schedule.  There one tile's softmax is a chain of dependent steps per key block (load
+// scores, maximum, exchange, exponentials, store P, signal) that leaves the tensor pipe idle for most of a block's
+// time.  Here a CTA owns 256 rows = two tiles of 128 (tile B's query tokens follow tile A's), each with its own eight
+// softmax warps, its own scores S and output O in tensor memory (4 x 128 columns), and both tiles use every K and V
+// block that the CTA loads once.  The MMA warp alternates: P V of tile A and Q K^T of A's next block run while tile
+// B's warps are in their softmax, and the other way round.  With one score buffer per tile, Q K^T of the next block
+// follows P V of this one on the tensor pipe (which keeps the order of issue), and P lies inside the columns of the
+// scores its own thread has already read: part 0 of a row writes P over columns [0, 32) of S, part 1 over [64, 96).
+// The softmax reads its scores twice (maximum, then exponentials) instead of keeping them, to fit 112 registers.
+//
+// Reference counterpart: attn_prefill_* (src/cuda/kernels.cu:2813-3156), an mma.sync kernel with f16 inputs.
+#include "tma_helpers.cuh"
+#include <math.h>
+
+namespace {
+constexpr int ROWS = 128;              // rows per tile = TMEM lanes
+constexpr int TILES = 2;               // query tiles per CTA
+constexpr int BKV = 128;               // keys per block
+constexpr int PARTS = 2;                // softmax threads per row: each takes 128 / PARTS keys of a block and hd / PARTS dims of O
+                                        // (four threads per row, 16 softmax warps, were 4 % slower: the softmax is not short of warps)
+constexpr int SOFTMAX_WARPS = 4 * PARTS * TILES;
+constexpr int MMA_WARP = SOFTMAX_WARPS, TMA_WARP = SOFTMAX_WARPS + 1;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+constexpr int KV_STAGES = 2;
+
+struct TcParams {
+    __nv_bfloat16* out; long out_stride;
+    int page_size, num_pages;
+    const int* block_table; int table_stride;
+    const int* q_start; const int* kv_len; const int* work;
+    int n_q, n_kv, group, pack, tokens_per_cta;
+    int window;
+    float scale_log2;
+    int* status;
+    int one_load_per_page;             // the 5-d map of the cache is in use (else 2-d loads of 8 keys x 64 dims)
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr, uint32_t sbo = 1024) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// MN-major operand tile (the contiguous direction is N), 128-byte swizzle: 64 elements of N contiguous per row of
+// 128 bytes, groups of 8 rows of K `sbo` bytes apart, blocks of 64 N-elements `lbo` bytes apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams p) {
+    constexpr int HALVES = HD / 64;                      // 64-wide (128-byte) column blocks of a head
+    constexpr int HALF_BYTES = 128 * 128;                // 128 rows x 128 bytes
+    constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // one Q, K or V tile
+    constexpr int GROUP_BYTES = HALVES * 1024;           // 8 keys of a K or V tile: one swizzle atom per half of the head
+    constexpr int TMEM_COLS = 512;                       // S of tile A | S of tile B | O of tile A | O of tile B
+    constexpr int O_COL = TILES * 128;                   // first column of the outputs
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t q_smem = base, k_smem = base + TILES * TILE_BYTES, v_smem = k_smem + KV_STAGES * TILE_BYTES;
+    const uint32_t bar0 = v_smem + KV_STAGES * TILE_BYTES;
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2] (per stage); s_full[2], p_ready[2], o_full[2] (per tile)
+    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_FULL = 13, NBAR = 15 };
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+    uint8_t* aligned = smem_raw + (base - raw);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xchg = reinterpret_cast<float*>(tmem_slot + 4);     // per tile: [2 blocks parity][PARTS][ROWS] maxima, then [PARTS][ROWS] sums
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = p.work[2 * blockIdx.x], q_off = p.work[2 * blockIdx.x + 1];
+    const int chunks_per_group = p.group / p.pack;
+    const int kvh = blockIdx.y / chunks_per_group;
+    const int head0 = kvh * p.group + (blockIdx.y % chunks_per_group) * p.pack;
+    const int row0 = p.q_start[seq];
+    const int q_len = p.q_start[seq + 1] - row0;
+    const int kv_len = p.kv_len[seq];
+    const int tile_tok = ROWS / p.pack;                  // query tokens of one tile
+    const int n_tok = min(p.tokens_per_cta, q_len - q_off);      // of both tiles together
+    const int qpos0 = kv_len - q_len + q_off;            // position of tile A's first query
+    const int key_lo = p.window > 0 ? max(0, qpos0 - p.window + 1) : 0;
+    const int key_hi = min(kv_len, qpos0 + n_tok);
+    const int blk_lo = key_lo / BKV, blk_hi = (key_hi + BKV - 1) / BKV;
+    const int n_blocks = blk_hi - blk_lo;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1);
+            mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1);
+            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), SOFTMAX_WARPS / TILES); mbar_init(bar(O_FULL + s), 1);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == TMA_WARP) {
+        // ------------------------------------------------------------ TMA producer: lane i loads page i of a block
+        if (lane == 0) {
+            mbar_expect_tx(bar(Q_FULL), TILES * TILE_BYTES);
+#pragma unroll
+            for (int t = 0; t < TILES; ++t)
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h)          // tokens beyond the buffer come as zeros; their rows are never stored
+                    tma_load_3d(q_smem + t * TILE_BYTES + h * HALF_BYTES, &map_q, h * 64, head0, row0 + q_off + t * tile_tok, bar(Q_FULL));
+        }
+        const int* table = p.block_table + (size_t)seq * p.table_stride;
+        const int pages_per_block = BKV / p.page_size;
+        auto lookup = [&](int j) {
+            const int kpos = (blk_lo + j) * BKV + lane * p.page_size;
+            int page = 0;
+            if (j < n_blocks && lane < pages_per_block && kpos < key_hi && kpos + p.page_size > key_lo) {
+                page = __ldg(table + kpos / p.page_size);
+                if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
+            }
+            return page;
+        };
+        int page = lookup(0);
+        for (int j = 0; j < n_blocks; ++j) {
+            const int s = j & 1;
+            const uint32_t par = ((j >> 1) & 1) ^ 1u;
+            const int page_next = lookup(j + 1);              // its latency hides behind the waits below
+            int ok = 1;
+            for (int kv = 0; kv < 2; ++kv) {
+                const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
+                if (lane == 0) {
+                    ok = mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status) ? 1 : 0;
+                    if (ok) mbar_expect_tx(full, TILE_BYTES);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);          // also orders the expect_tx before every lane's loads
+                if (!ok) break;
+                if (lane < pages_per_block) {
+                    const uint32_t dst = (kv ? v_smem : k_smem) + s * TILE_BYTES + lane * (p.page_size / 8) * GROUP_BYTES;
+                    const int block = (page * 2 + kv) * p.n_kv + kvh;
+                    if (p.one_load_per_page) {
+                        tma_load_5d(dst, &map_kv, 0, 0, 0, 0, block, full);
+                    } else {
+                        for (int g8 = 0; g8 < p.page_size / 8; ++g8)
+#pragma unroll
+                            for (int h = 0; h < HALVES; ++h)
+                                tma_load_2d(dst + g8 * GROUP_BYTES + h * 1024, &map_kv, h * 64, block * p.page_size + g8 * 8, full);
+                    }
+                }
+            }
+            if (!ok) break;
+            page = page_next;
+        }
+    } else if (warp == MMA_WARP) {
+        // ------------------------------------------------------------ MMA issuer: the two tiles take turns
+        if (lane == 0 && n_blocks > 0) {
+            const uint32_t idesc_qk = idesc_bf16(ROWS, BKV, 0), idesc_pv = idesc_bf16(ROWS, HD, 1);
+            bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, p.status);
+            // S of tile t = Q_t K^T of block j (the K stage must have landed: the caller waits once per block)
+            auto issue_qk = [&](int t, int j) {
+                const int s = j & 1;
+                const uint32_t d = tmem_base + t * 128;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    umma_ss(d, desc_kmajor(q_smem + t * TILE_BYTES + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
+                            desc_kmajor(k_smem + s * TILE_BYTES + (ks >> 2) * 1024 + (ks & 3) * 32, GROUP_BYTES), idesc_qk, ks ? 1u : 0u);
+                }
+                umma_commit(bar(S_FULL + t));
+            };
+            // O of tile t += P_t V of block j; P lies in two runs of 32 columns inside S (keys 0..63 at column 0, 64..127 at 64)
+            auto issue_pv = [&](int t, int j) {
+                const int s = j & 1;
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk)
+                    umma_ts(tmem_base + O_COL + t * HD, tmem_base + t * 128 + (kk >> 2) * 64 + (kk & 3) * 8,
+                            desc_mnmajor(v_smem + s * TILE_BYTES + kk * 2 * GROUP_BYTES, 1024, GROUP_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
+                umma_commit(bar(O_FULL + t));                 // completion j of this barrier: O of tile t holds blocks 0..j
+            };
+            if (ok) ok = mbar_wait(bar(K_FULL + 0), 0, abort_flag, p.status);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0, 0);
+                issue_qk(1, 0);
+                umma_commit(bar(K_EMPTY + 0));               // the K stage is free once both tiles' products have read it
+            }
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int s = j & 1, sn = (j + 1) & 1;
+                const uint32_t par = (j >> 1) & 1, parn = ((j + 1) >> 1) & 1;
+                const bool more = j + 1 < n_blocks;
+                // tile A: P V of this block, then Q K^T of the next (the tensor pipe keeps the order of issue, so the
+                // next scores overwrite S only after P has been read out of it)
+                if (!mbar_wait(bar(P_READY + 0), j & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(bar(V_FULL + s), par, abort_flag, p.status)) break;
+                tc_fence_after();
+                issue_pv(0, j);
+                if (more) {
+                    if (!mbar_wait(bar(K_FULL + sn), parn, abort_flag, p.status)) break;
+                    tc_fence_after();
+                    issue_qk(0, j + 1);
+                }
+                // tile B: the same, while tile A's warps are in their softmax
+                if (!mbar_wait(bar(P_READY + 1), j & 1, abort_flag, p.status)) break;
+                tc_fence_after();
+                issue_pv(1, j);
+                umma_commit(bar(V_EMPTY + s));               // the V stage is free once both tiles' products have read it
+                if (more) {
+                    issue_qk(1, j + 1);
+                    umma_commit(bar(K_EMPTY + sn));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps: 8 per tile, PARTS threads per row
+        // Of a tile's warps, w, w + 4 own the same 32 rows (tensor-memory lanes 32 (w & 3) ..): warp number `part` of them
+        // takes the keys [part * HK, +HK) of a block and the head dims [part * HO, +HO) of O.  They exchange their row
+        // maxima through shared memory once per block; their partial sums meet at the end.  A warp whose wait ran out
+        // keeps walking the blocks without touching them, so that the named barriers stay in step.
+        constexpr int HK = BKV / PARTS, HO = HD / PARTS;
+        static_assert(PARTS == 2 && HK == 64 && (HO % 32 == 0 || HO == 16), "P of a part lies in the first half of its own score columns");
+        constexpr int OC = HO >= 32 ? 32 : 16;       // columns of O per load
+        constexpr float RESCALE_ABOVE = 8.f;         // log2 units: keep the old maximum while the new one is within 2^8 of it
+        const int t = warp >> 3, quarter = warp & 3, part = (warp >> 2) & 1;
+        const int r = quarter * 32 + lane;                             // row within the tile
+        const int tok = t * tile_tok + r / p.pack;                     // query token within the CTA
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t s_addr = lane_base + t * 128 + part * HK;       // my scores; my P goes over the first half of them
+        const uint32_t o_addr = lane_base + O_COL + t * HD + part * HO;
+        float* xc = xchg + t * (3 * PARTS * ROWS);
+        const int qpos = qpos0 + tok;
+        float m_used = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        auto row_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + t * 4 + quarter), "n"(PARTS * 32) : "memory"); };
+        auto load_o = [&](int c, uint32_t* v) {
+            if (OC == 32) tmem_ld32(o_addr + c, v); else tmem_ld16(o_addr + c, v);
+            tmem_ld_wait();
+        };
+        auto visible = [&](int kpos) {
+            return kpos <= qpos && kpos < key_hi && kpos >= key_lo && (p.window <= 0 || kpos > qpos - p.window);
+        };
+        for (int j = 0; j < n_blocks; ++j) {
+            const int kb0 = (blk_lo + j) * BKV;
+            const int k0 = kb0 + part * HK;                            // first key of this thread's part of the block
+            if (ok) ok = mbar_wait(bar(S_FULL + t), j & 1, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);                          // tensor-memory loads and stores are warp-wide
+            const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
+                                   (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
+            float mx = -INFINITY;
+            if (ok) {
+                tc_fence_after();
+                // first pass over the row's scores of this part of the block: the maximum
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < HK; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(s_addr + c, v);
+                    tmem_ld_wait();
+                    if (need_mask) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (!visible(k0 + c + i)) v[i] = 0xff800000u;      // -inf
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(v[i])); mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(v[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+                    }
+                }
+                mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;     // the scale is positive: it commutes with the maximum
+            }
+            xc[((j & 1) * PARTS + part) * ROWS + r] = mx;
+            row_sync();
+            float m_blk = mx;
+#pragma unroll
+            for (int q = 0; q < PARTS; ++q) m_blk = fmaxf(m_blk, xc[((j & 1) * PARTS + q) * ROWS + r]);
+            if (!ok) continue;
+            // The reference maximum only moves when the block's maximum exceeds it by more than 2^8 (or it was
+            // still -inf): then everything accumulated so far, O in tensor memory included, is rescaled.  All
+            // threads of a row see the same numbers and take the same decision.
+            const bool move = m_blk > m_used + RESCALE_ABOVE || (m_used == -INFINITY && m_blk > -INFINITY);
+            if (__any_sync(0xffffffffu, move)) {
+                const float corr = move ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_blk)) : 1.f;
+                if (j > 0) {                                          // O holds the products of blocks 0..j-1
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(O_FULL + t), (j - 1) & 1, abort_flag, p.status));
+                    if (ok) {
+                        tc_fence_after();
+#pragma unroll
+                        for (int c = 0; c < HO; c += OC) {
+                            uint32_t v[32];
+                            load_o(c, v);
+#pragma unroll
+                            for (int i = 0; i < OC; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                            tmem_st16(o_addr + c, v);
+                            if (OC == 32) tmem_st16(o_addr + c + 16, v + 16);
+                        }
+                        tmem_st_wait();
+                    }
+                }
+                l_run *= corr;
+                if (move) m_used = m_blk;
+            }
+            if (!ok) continue;
+            // second pass: P = 2^(x * scale - m), its sum, and P as bfloat16 pairs over the scores already read
+            const float sub = (m_used == -INFINITY) ? 0.f : m_used;     // nothing visible yet: every x is -inf, P = 0
+            float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < HK; c += 32) {
+                uint32_t v[32], pk[16];
+                tmem_ld32(s_addr + c, v);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!visible(k0 + c + i)) v[i] = 0xff800000u;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -sub));
+                    const float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -sub));
+                    rs0 += e0; rs1 += e1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
+                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                tmem_st16(s_addr + (c >> 1), pk);
+            }
+            tmem_st_wait();
+            l_run += rs0 + rs1;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(P_READY + t));
+        }
+        // the row's sum: all parts used the same reference maxima, so their partial sums simply add (in a fixed order)
+        xc[(2 * PARTS + part) * ROWS + r] = l_run;
+        row_sync();
+        l_run = 0.f;
+#pragma unroll
+        for (int q = 0; q < PARTS; ++q) l_run += xc[(2 * PARTS + q) * ROWS + r];
+        if (ok && n_blocks > 0) ok = mbar_wait(bar(O_FULL + t), (n_blocks - 1) & 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && n_blocks > 0) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + q_off + tok) * p.out_stride + (size_t)(head0 + r % p.pack) * HD + part * HO;
+#pragma unroll
+            for (int c = 0; c < HO; c += OC) {
+                uint32_t v[32];
+                load_o(c, v);                                          // warp-collective: rows beyond the tile load too
+                if (tok < n_tok) {
+#pragma unroll
+                    for (int d = 0; d < OC; d += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[d + 2 * u]) * inv, __uint_as_float(v[d + 2 * u + 1]) * inv);
+                            w[u] = *reinterpret_cast<uint32_t*>(&b);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+__host__ __device__ inline int pack_of(int group) {
+    int p = 1;
+    while (p < 16 && group % (2 * p) == 0) p *= 2;
+    return p;
+}
+
+// 3-D map of the query part of the projection buffer: (head dim, head, token), box 64 x pack x (128 / pack).
+int q_map(const void* q, long q_stride, long tokens, int n_q, int hd, int pack, CUtensorMap* out) {
+    using namespace rs_tma;
+    EncodeTiledFn enc = get_encoder();
+    if (!enc) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)n_q, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)pack, (cuuint32_t)(ROWS / pack)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+struct QMapKey { const void* q; long stride, tokens; int n_q, hd, pack; };
+std::vector<std::pair<QMapKey, CUtensorMap>> g_qmaps;
+std::mutex g_qmaps_mutex;
+
+int cached_q_map(const void* q, long q_stride, long tokens, int n_q, int hd, int pack, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_qmaps_mutex);
+    for (auto& e : g_qmaps)
+        if (e.first.q == q && e.first.stride == q_stride && e.first.tokens == tokens && e.first.n_q == n_q && e.first.hd == hd &&
+            e.first.pack == pack) { *out = e.second; return 0; }
+    CUtensorMap m;
+    int rc = q_map(q, q_stride, tokens, n_q, hd, pack, &m);
+    if (rc) return rc;
+    if (g_qmaps.size() > 64) g_qmaps.clear();
+    g_qmaps.push_back({QMapKey{q, q_stride, tokens, n_q, hd, pack}, m});
+    *out = m;
+    return 0;
+}
+
+// 5-d map of the cache: (64 dims, key within a group of 8, half of the head, group of the page, block = (page * 2 + K|V) *
+// n_kv + kv head); one box is a page's keys (or values) of one kv head.  Returns non-zero if the driver does not take it.
+int page_map(const void* cache, int num_pages, int n_kv, int page_size, int hd, CUtensorMap* out) {
+    using namespace rs_tma;
+    EncodeTiledFn enc = get_encoder();
+    if (!enc) return 1;
+    const cuuint64_t row = (cuuint64_t)hd * 2;
+    cuuint64_t dims[5] = {64, 8, (cuuint64_t)(hd / 64), (cuuint64_t)(page_size / 8), (cuuint64_t)num_pages * 2 * n_kv};
+    cuuint64_t strides[4] = {row, 128, 8 * row, (cuuint64_t)page_size * row};
+    cuuint32_t box[5] = {64, 8, (cuuint32_t)(hd / 64), (cuuint32_t)(page_size / 8), 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1;
+}
+
+struct PageMapKey { const void* cache; int num_pages, n_kv, page_size, hd; };
+struct PageMapEntry { PageMapKey key; int refused; CUtensorMap map; };
+std::vector<PageMapEntry> g_page_maps;
+std::mutex g_page_maps_mutex;
+int g_last_loads_per_page = 0;
+
+int cached_page_map(const void* cache, int num_pages, int n_kv, int page_size, int hd, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_page_maps_mutex);
+    for (auto& e : g_page_maps)
+        if (e.key.cache == cache && e.key.num_pages == num_pages && e.key.n_kv == n_kv && e.key.page_size == page_size &&
+            e.key.hd == hd) { *out = e.map; return e.refused; }
+    PageMapEntry e{PageMapKey{cache, num_pages, n_kv, page_size, hd}, 0, {}};
+    e.refused = page_map(cache, num_pages, n_kv, page_size, hd, &e.map);
+    if (g_page_maps.size() > 64) g_page_maps.clear();
+    g_page_maps.push_back(e);
+    *out = e.map;
+    return e.refused;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int n_work, cudaStream_t s) {
+    constexpr int smem = (TILES + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 17 + 64 + TILES * 3 * PARTS * ROWS * 4;
+    auto kern = prefill_attention_tc2_kernel<HD>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    kern<<<dim3(n_work, p.n_kv * (p.group / p.pack)), THREADS, smem, s>>>(mq, mkv, p);
+    return rs_launch_result();
+}
+}  // namespace
+
+RS_EXPORT int rs_attention_prefill_tc2_supported(int n_q, int n_kv, int hd, int page_size) {
+    if (n_kv <= 0 || n_q % n_kv) return 0;
+    if (hd != 64 && hd != 128) return 0;
+    return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+}
+
+// TMA loads per cache page (keys and values together) in the most recent launch: 2 with the 5-d map.
+RS_EXPORT int rs_attention_prefill_tc2_loads_per_page() { return g_last_loads_per_page; }
+
+// Query tokens per CTA: the host cuts each sequence's queries into tiles of this many.
+RS_EXPORT int rs_attention_prefill_tc2_q_per_cta(int n_q, int n_kv) { return TILES * ROWS / pack_of(n_q / n_kv); }
+
+// q: the projection buffer [q_rows, q_stride] whose first n_q * hd columns of every row are the queries.
+RS_EXPORT int rs_attention_prefill_tc2(const void* q, long q_stride, long q_rows, void* out, long out_stride, const void* cache,
+                                      long page_stride, int num_pages, int page_size, const int* block_table,
+                                      int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
+                                      int n_q, int n_kv, int hd, int window, float scale, int* status, void* stream) {
+    if (n_work <= 0) return 0;
+    if (!rs_attention_prefill_tc2_supported(n_q, n_kv, hd, page_size) || (q_stride % 8) || (out_stride % 8) || ((long)q & 15) ||
+        ((long)out & 15) || ((long)cache & 15) || page_stride != (long)2 * n_kv * page_size * hd)
+        return (int)cudaErrorInvalidValue;
+    TcParams p;
+    p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.page_size = page_size; p.num_pages = num_pages;
+    p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
+    p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.pack = pack_of(p.group); p.tokens_per_cta = TILES * ROWS / p.pack;
+    p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    CUtensorMap mq, mkv;
+    int rc = cached_q_map(q, q_stride, q_rows, n_q, hd, p.pack, &mq);
+    if (rc) return rc;
+    p.one_load_per_page = cached_page_map(cache, num_pages, n_kv, page_size, hd, &mkv) == 0;
+    if (!p.one_load_per_page) {
+        rc = rs_tma::get_map(cache, (long)num_pages * 2 * n_kv * page_size, hd, hd, 8, &mkv);
+        if (rc) return rc;
+    }
+    g_last_loads_per_page = p.one_load_per_page ? 2 : 2 * (hd / 64) * (page_size / 8);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64) return launch<64>(mq, mkv, p, n_work, s);
+    return launch<128>(mq, mkv, p, n_work, s);
+}
