@@ -422,16 +422,36 @@ __global__ void __launch_bounds__(TG * HD) decode_merge_kernel(const DecodeParam
     const int w = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int d = tid % HD, g = tid / HD;
     pdl_launch_dependents();
-    pdl_wait();
+    // the step's metadata is in place before its first kernel: it is read while the attention kernel is still at work
     const int seq = __ldg(p.work + w);
     const int kv_len = __ldg(p.kv_len + seq);
     const int key_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
     const int n_splits = (kv_len + SPLIT - 1) / SPLIT - key_lo / SPLIT;
     const float* base = p.partial + ((size_t)__ldg(p.split_start + w) * p.n_q + h) * (HD + 2);
     const size_t stride = (size_t)p.n_q * (HD + 2);
+    __nv_bfloat16* const out_row = p.out + (size_t)__ldg(p.q_start + seq) * p.out_stride + (size_t)h * HD;
+    pdl_wait();
+    // Everything the first round needs is asked for at once, before anything is waited for: the splits' maxima and
+    // sums (kept in registers when there is at most one split per thread) and the first accumulators of this
+    // thread's chain(s).  The arithmetic and its order are the same as if they were loaded where they are used.
+    constexpr int ROUND = TG == MERGE_CHAINS ? 8 : 16;            // accumulator loads in flight per thread
+    const int n_first = min(MERGE_MAX_SPLITS, n_splits);
+    const bool mine_only = n_splits <= NT;                         // uniform
+    float my_m = -INFINITY, my_l = 0.f;
+    if (mine_only && tid < n_splits) {
+        my_m = ld_dep(base + tid * stride + HD);
+        my_l = ld_dep(base + tid * stride + HD + 1);
+    }
+    float a0[ROUND];
+#pragma unroll
+    for (int j = 0; j < ROUND; ++j) {
+        const int s = TG == MERGE_CHAINS ? g + MERGE_CHAINS * j : j;
+        a0[j] = s < n_first ? ld_dep(base + s * stride + d) : 0.f;
+    }
     // the row's maximum over all splits
-    float M = -INFINITY;
-    for (int s = tid; s < n_splits; s += NT) M = fmaxf(M, ld_dep(base + s * stride + HD));
+    float M = my_m;
+    if (!mine_only)
+        for (int s = tid; s < n_splits; s += NT) M = fmaxf(M, ld_dep(base + s * stride + HD));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     if ((tid & 31) == 0) red[tid >> 5] = M;
@@ -446,33 +466,43 @@ __global__ void __launch_bounds__(TG * HD) decode_merge_kernel(const DecodeParam
         const int n = min(MERGE_MAX_SPLITS, n_splits - s0);
         const float* ps = base + (size_t)s0 * stride;
         __syncthreads();
-        for (int s = tid; s < n; s += NT) {
-            const float e = fast_exp2(ld_dep(ps + s * stride + HD) - M);
-            wgt[s] = e;
-            wl[s] = e * ld_dep(ps + s * stride + HD + 1);
+        if (mine_only) {
+            if (tid < n) {
+                const float e = fast_exp2(my_m - M);
+                wgt[tid] = e;
+                wl[tid] = e * my_l;
+            }
+        } else {
+            for (int s = tid; s < n; s += NT) {
+                const float e = fast_exp2(ld_dep(ps + s * stride + HD) - M);
+                wgt[s] = e;
+                wl[s] = e * ld_dep(ps + s * stride + HD + 1);
+            }
         }
         __syncthreads();
         if (TG == MERGE_CHAINS) {
-            for (int i = g; i < n; i += MERGE_CHAINS * 8) {               // my chain: splits g, g + 4, ...; eight loads in flight
-                float a[8];
+            for (int i = g; i < n; i += MERGE_CHAINS * ROUND) {          // my chain: splits g, g + 4, ...; eight loads in flight
+                float a[ROUND];
+                const bool first = s0 == 0 && i == g;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < ROUND; ++j) {
                     const int s = i + MERGE_CHAINS * j;
-                    a[j] = s < n ? ld_dep(ps + s * stride + d) : 0.f;
+                    a[j] = first ? a0[j] : (s < n ? ld_dep(ps + s * stride + d) : 0.f);
                 }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < ROUND; ++j) {
                     const int s = i + MERGE_CHAINS * j;
                     if (s < n) { num[0] = fmaf(a[j], wgt[s], num[0]); den[0] += wl[s]; }
                 }
             }
         } else {
-            for (int i = 0; i < n; i += 16) {                              // all chains: sixteen loads in flight
-                float a[16];
+            for (int i = 0; i < n; i += ROUND) {                           // all chains: sixteen loads in flight
+                float a[ROUND];
+                const bool first = s0 == 0 && i == 0;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) a[j] = i + j < n ? ld_dep(ps + (i + j) * stride + d) : 0.f;
+                for (int j = 0; j < ROUND; ++j) a[j] = first ? a0[j] : (i + j < n ? ld_dep(ps + (i + j) * stride + d) : 0.f);
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
+                for (int j = 0; j < ROUND; ++j)
                     if (i + j < n) { num[j % MERGE_CHAINS] = fmaf(a[j], wgt[i + j], num[j % MERGE_CHAINS]); den[j % MERGE_CHAINS] += wl[i + j]; }
             }
         }
@@ -487,7 +517,7 @@ __global__ void __launch_bounds__(TG * HD) decode_merge_kernel(const DecodeParam
         nn = (num[0] + num[MERGE_CHAINS / TG > 1 ? 1 : 0]) + (num[MERGE_CHAINS / TG > 2 ? 2 : 0] + num[MERGE_CHAINS / TG > 3 ? 3 : 0]);
         dd = (den[0] + den[MERGE_CHAINS / TG > 1 ? 1 : 0]) + (den[MERGE_CHAINS / TG > 2 ? 2 : 0] + den[MERGE_CHAINS / TG > 3 ? 3 : 0]);
     }
-    if (g == 0) p.out[(size_t)__ldg(p.q_start + seq) * p.out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(nn / dd);
+    if (g == 0) out_row[d] = __float2bfloat16_rn(nn / dd);
 }
 
 // 5-d map of the cache: (64 dims, token of the page, half of the head, K|V, block = page * 2 * n_kv + kv head); one

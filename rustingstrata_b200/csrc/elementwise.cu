@@ -64,10 +64,27 @@ __global__ void __launch_bounds__(512) rmsnorm_bf16_vec_kernel(const float* x, l
                                                                __nv_bfloat16* __restrict__ out, long out_stride, int n) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
+    const int n4 = n >> 2;
+    // the weights are the model's, not the previous kernel's: they are fetched while that kernel is still at work
+    float wv[VPT][4];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = threadIdx.x + u * 512;
+        wv[u][0] = wv[u][1] = wv[u][2] = wv[u][3] = 0.f;
+        if (i < n4) {
+            if (w_dt == RS_F32) {
+                const float4 f = reinterpret_cast<const float4*>(w)[i];
+                wv[u][0] = f.x; wv[u][1] = f.y; wv[u][2] = f.z; wv[u][3] = f.w;
+            } else {
+                const uint2 h = reinterpret_cast<const uint2*>(w)[i];
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&h.x), b = *reinterpret_cast<const __nv_bfloat162*>(&h.y);
+                wv[u][0] = __low2float(a); wv[u][1] = __high2float(a); wv[u][2] = __low2float(b); wv[u][3] = __high2float(b);
+            }
+        }
+    }
     pdl_wait();
     const int r = blockIdx.x;
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * x_stride);
-    const int n4 = n >> 2;
     float4 v[VPT];
     float ss = 0.f;
 #pragma unroll
@@ -83,17 +100,8 @@ __global__ void __launch_bounds__(512) rmsnorm_bf16_vec_kernel(const float* x, l
     for (int u = 0; u < VPT; ++u) {
         const int i = threadIdx.x + u * 512;
         if (i < n4) {
-            float w0, w1, w2, w3;
-            if (w_dt == RS_F32) {
-                const float4 wv = reinterpret_cast<const float4*>(w)[i];
-                w0 = wv.x; w1 = wv.y; w2 = wv.z; w3 = wv.w;
-            } else {
-                const uint2 wv = reinterpret_cast<const uint2*>(w)[i];
-                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&wv.x), b = *reinterpret_cast<const __nv_bfloat162*>(&wv.y);
-                w0 = __low2float(a); w1 = __high2float(a); w2 = __low2float(b); w3 = __high2float(b);
-            }
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * s * w0, v[u].y * s * w1);
-            const __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * s * w2, v[u].w * s * w3);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * s * wv[u][0], v[u].y * s * wv[u][1]);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * s * wv[u][2], v[u].w * s * wv[u][3]);
             uint2 pk;
             pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
             reinterpret_cast<uint2*>(o)[i] = pk;
@@ -203,7 +211,8 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
                                             int n_tokens, int lanes_per_head, int* status) {
     struct alignas(2 * E) Vec { uint32_t w[E / 2]; };           // E bfloat16 values
     pdl_launch_dependents();
-    pdl_wait();
+    // Positions, block tables, norm weights and the rotation table are in place before the step's first kernel, so they
+    // are fetched here, while the projection before this kernel is still at work; only qkv has to wait for it.
     const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
     const int heads_per_warp = 32 / lanes_per_head;
     const int lane = threadIdx.x & 31;
@@ -246,6 +255,20 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     };
     const int i = sub * E;
     const bool mine = ok && i < half;
+    float wa[E], wb[E], cc[E], sv[E];
+#pragma unroll
+    for (int u = 0; u < E; ++u) { wa[u] = wb[u] = 1.f; cc[u] = sv[u] = 0.f; }
+    if (mine && !is_v) {
+        if (w != nullptr) { unpack(*reinterpret_cast<const Vec*>(w + i), wa); unpack(*reinterpret_cast<const Vec*>(w + half + i), wb); }
+#pragma unroll
+        for (int u = 0; u < E; u += 4) {
+            const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i + u);
+            const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i + u);
+            cc[u] = c.x; cc[u + 1] = c.y; cc[u + 2] = c.z; cc[u + 3] = c.w;
+            sv[u] = sn.x; sv[u + 1] = sn.y; sv[u + 2] = sn.z; sv[u + 3] = sn.w;
+        }
+    }
+    pdl_wait();
     Vec ua, ub;
 #pragma unroll
     for (int k = 0; k < E / 2; ++k) ua.w[k] = ub.w[k] = 0u;
@@ -263,18 +286,6 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // within the head's lanes
     if (!mine || is_v) return;
     const float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;
-    float wa[E], wb[E];
-#pragma unroll
-    for (int u = 0; u < E; ++u) wa[u] = wb[u] = 1.f;
-    if (w != nullptr) { unpack(*reinterpret_cast<const Vec*>(w + i), wa); unpack(*reinterpret_cast<const Vec*>(w + half + i), wb); }
-    float cc[E], sv[E];
-#pragma unroll
-    for (int u = 0; u < E; u += 4) {
-        const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i + u);
-        const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i + u);
-        cc[u] = c.x; cc[u + 1] = c.y; cc[u + 2] = c.z; cc[u + 3] = c.w;
-        sv[u] = sn.x; sv[u + 1] = sn.y; sv[u + 2] = sn.z; sv[u + 3] = sn.w;
-    }
     float ra[E], rb[E];
 #pragma unroll
     for (int u = 0; u < E; ++u) {

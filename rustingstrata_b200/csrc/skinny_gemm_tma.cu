@@ -46,7 +46,7 @@ struct SkinnyParams {
     void* C; long ldc;
     int M, N, K;
     int stages;
-    float* workspace;          // [grid][2][CONSUMER_WARPS][NT * 4][32] float32 partials
+    float* workspace;          // [grid][2][8 NT activation rows][TILE_N] float32 partials
     int* status;
 };
 
@@ -228,11 +228,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 } else {
                     // shared with other CTAs: my float32 partial goes to the workspace; skinny_reduce_kernel adds them up
                     const int slot = (u0 >= tile_first) ? 0 : 1;            // 0: the tile my range starts in
-                    float* mine = p.workspace + ((((size_t)blockIdx.x * 2 + slot) * CONSUMER_WARPS + warp) * (NT * 4)) * 32;
+                    float* mine = p.workspace + ((size_t)blockIdx.x * 2 + slot) * (8 * NT * TILE_N) + 16 * warp + g;
 #pragma unroll
                     for (int j = 0; j < NT; ++j)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) __stcg(mine + (j * 4 + i) * 32 + lane, acc[j][i]);
+                        for (int i = 0; i < 4; ++i) __stcg(mine + (8 * j + 2 * t + (i & 1)) * TILE_N + 8 * (i >> 1), acc[j][i]);
                 }
 #pragma unroll
                 for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
@@ -255,17 +255,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 template <int NT, int EPI>
 __global__ void __launch_bounds__(CONSUMER_WARPS * 32) skinny_reduce_kernel(const SkinnyParams p, int G) {
     pdl_launch_dependents();
-    pdl_wait();
+    // who shares which tile follows from the shape alone: worked out while the product is still running
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int KB = (p.K + TILE_K - 1) / TILE_K;
     const int U = ((p.N + TILE_N - 1) / TILE_N) * KB;
     const int b = blockIdx.x + 1;                              // boundary between CTA b - 1 and CTA b
     const int ub = first_unit(b, U, G);
-    if (ub % KB == 0) return;                                  // on a tile's edge: nobody shares because of it
     const int tile = ub / KB, tile_first = tile * KB;
-    if (first_unit(b - 1, U, G) > tile_first) return;          // an earlier boundary lies in this tile: its CTA acts
-    const int c_first = b - 1, c_last = cta_of_unit(tile_first + KB - 1, U, G);
+    // on a tile's edge nobody shares because of this boundary; if an earlier boundary lies in the tile, its CTA acts
+    const bool acts = ub % KB != 0 && first_unit(b - 1, U, G) <= tile_first;
+    const int c_first = b - 1, c_last = acts ? cta_of_unit(tile_first + KB - 1, U, G) : b - 1;
+    pdl_wait();                                                // every CTA waits, so that this grid never ends before the product
+    if (!acts) return;
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
@@ -276,11 +278,11 @@ __global__ void __launch_bounds__(CONSUMER_WARPS * 32) skinny_reduce_kernel(cons
         for (int cc = 0; cc < CH; ++cc) {
             const int c = min(c0 + cc, c_last);
             const int cslot = (first_unit(c, U, G) >= tile_first) ? 0 : 1;
-            const float* src = p.workspace + ((((size_t)c * 2 + cslot) * CONSUMER_WARPS + warp) * (NT * 4)) * 32;
+            const float* src = p.workspace + ((size_t)c * 2 + cslot) * (8 * NT * TILE_N) + 16 * warp + g;
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) v[cc][j][i] = ld_dep(src + (j * 4 + i) * 32 + lane);
+                for (int i = 0; i < 4; ++i) v[cc][j][i] = ld_dep(src + (8 * j + 2 * t + (i & 1)) * TILE_N + 8 * (i >> 1));
         }
 #pragma unroll
         for (int cc = 0; cc < CH; ++cc)
@@ -294,10 +296,108 @@ __global__ void __launch_bounds__(CONSUMER_WARPS * 32) skinny_reduce_kernel(cons
     store_tile<NT, EPI>(p, acc, tile, warp, g, t);
 }
 
+// RMSNorm of the rows of C straight after a product with the f32 += epilogue whose shared tiles were left unfinished
+// (`defer`): one CTA per row does what skinny_reduce_kernel<1, EPI_ADD_F32> and the row norm would do one after the
+// other, with the same arithmetic in the same order (partials from zero in CTA order, then added to C; the sum of
+// squares by thread-strided float4 partials and a tree), so the bits are those of the two kernels.  It saves a kernel
+// boundary and a round trip to memory between two small dependent kernels.  Rows of up to 512 * 4 * VPT values, M <= 8.
+template <int VPT>
+__global__ void __launch_bounds__(512) skinny_finish_rmsnorm_kernel(const SkinnyParams p, int G, const void* __restrict__ w, int w_dt,
+                                                                    float eps, __nv_bfloat16* __restrict__ out, long out_stride) {
+    constexpr int MAX_TILES = 512 * 4 * VPT / TILE_N;
+    __shared__ float scratch[33];
+    __shared__ int2 sharers[MAX_TILES];                        // per row tile: first and last CTA of the product that worked on it
+    pdl_launch_dependents();
+    // Nothing before the wait reads what the product wrote: who shared which tile follows from the shape, and the
+    // norm's weights are the model's.  So this part runs while the product is still at work.
+    const int m = blockIdx.x;
+    const int KB = (p.K + TILE_K - 1) / TILE_K;
+    const int n_tiles = (p.N + TILE_N - 1) / TILE_N;
+    const int U = n_tiles * KB;
+    const int per_cta = U / G, extra = U % G;                  // the first `extra` CTAs take one unit more
+    for (int tile = threadIdx.x; tile < n_tiles; tile += 512)
+        sharers[tile] = make_int2(cta_of_unit(tile * KB, U, G), cta_of_unit(tile * KB + KB - 1, U, G));
+    const int n4 = p.N >> 2;
+    float wv[VPT][4];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        wv[u][0] = wv[u][1] = wv[u][2] = wv[u][3] = 0.f;
+        if (idx < n4) {
+            if (w_dt == RS_F32) {
+                const float4 f = reinterpret_cast<const float4*>(w)[idx];
+                wv[u][0] = f.x; wv[u][1] = f.y; wv[u][2] = f.z; wv[u][3] = f.w;
+            } else {
+                const uint2 h = reinterpret_cast<const uint2*>(w)[idx];
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&h.x), b = *reinterpret_cast<const __nv_bfloat162*>(&h.y);
+                wv[u][0] = __low2float(a); wv[u][1] = __high2float(a); wv[u][2] = __low2float(b); wv[u][3] = __high2float(b);
+            }
+        }
+    }
+    __syncthreads();
+    pdl_wait();
+    float* xr = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < n4) {
+            const int n0 = idx * 4;
+            v[u] = ld_dep(reinterpret_cast<const float4*>(xr) + idx);
+            const int tile = n0 / TILE_N, r = n0 % TILE_N;
+            const int tile_first = tile * KB;
+            const int c_first = sharers[tile].x, c_last = sharers[tile].y;
+            if (c_first != c_last) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                constexpr int CH = 4;                                     // contributors whose loads are in flight together
+                for (int c0 = c_first; c0 <= c_last; c0 += CH) {
+                    float4 q[CH];
+#pragma unroll
+                    for (int cc = 0; cc < CH; ++cc) {
+                        const int c = min(c0 + cc, c_last);
+                        const int cslot = (c * per_cta + min(c, extra) >= tile_first) ? 0 : 1;     // first_unit(c) without the division
+                        q[cc] = ld_dep(reinterpret_cast<const float4*>(p.workspace + ((size_t)c * 2 + cslot) * (8 * TILE_N) + m * TILE_N + r));
+                    }
+#pragma unroll
+                    for (int cc = 0; cc < CH; ++cc)
+                        if (c0 + cc <= c_last) { acc.x += q[cc].x; acc.y += q[cc].y; acc.z += q[cc].z; acc.w += q[cc].w; }
+                }
+                v[u].x += acc.x; v[u].y += acc.y; v[u].z += acc.z; v[u].w += acc.w;
+                reinterpret_cast<float4*>(xr)[idx] = v[u];
+            }
+        }
+        ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss); ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float sc = 1.0f / sqrtf(ss / (float)p.N + eps);
+    __nv_bfloat16* o = out + (size_t)m * out_stride;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        if (idx < n4) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * sc * wv[u][0], v[u].y * sc * wv[u][1]);
+            const __nv_bfloat162 hi2 = __floats2bfloat162_rn(v[u].z * sc * wv[u][2], v[u].w * sc * wv[u][3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi2);
+            reinterpret_cast<uint2*>(o)[idx] = pk;
+        }
+    }
+}
+
 template <int NT> constexpr int stage_bytes() { return W_BYTES + 8 * NT * TILE_K * 2; }
 
+// CTAs of the product: one per SM, at most max_ctas (if positive), at most one per unit of work
+long grid_of(int N, int K, int max_ctas) {
+    const long U = (long)((N + TILE_N - 1) / TILE_N) * ((K + TILE_K - 1) / TILE_K);
+    long grid = rs_tma::sm_count();
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    return grid > U ? U : grid;
+}
+
 template <int NT, int EPI>
-int launch(const CUtensorMap& mw, const CUtensorMap& ma, SkinnyParams p, int max_ctas, cudaStream_t s) {
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, SkinnyParams p, int max_ctas, bool defer, cudaStream_t s) {
     constexpr int SB = stage_bytes<NT>();
     int stages = SMEM_BUDGET / SB;
     if (stages > 24) stages = 24;
@@ -310,22 +410,19 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, SkinnyParams p, int max
         attr_set = true;
     }
     p.stages = stages;
-    const long U = (long)((p.N + TILE_N - 1) / TILE_N) * ((p.K + TILE_K - 1) / TILE_K);
-    long grid = rs_tma::sm_count();
-    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    if (grid > U) grid = U;
+    const long grid = grid_of(p.N, p.K, max_ctas);
     int rc = rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
-    if (rc != 0 || grid < 2) return rc;
+    if (rc != 0 || grid < 2 || defer) return rc;
     return rs_launch_pdl(skinny_reduce_kernel<NT, EPI>, dim3((unsigned)(grid - 1)), dim3(CONSUMER_WARPS * 32), 0, s, p, (int)grid);
 }
 
 template <int NT>
-int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const SkinnyParams& p, int max_ctas, cudaStream_t s) {
+int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const SkinnyParams& p, int max_ctas, bool defer, cudaStream_t s) {
     switch (epi) {
-        case EPI_STORE_BF16: return launch<NT, EPI_STORE_BF16>(mw, ma, p, max_ctas, s);
-        case EPI_STORE_F32: return launch<NT, EPI_STORE_F32>(mw, ma, p, max_ctas, s);
-        case EPI_ADD_F32: return launch<NT, EPI_ADD_F32>(mw, ma, p, max_ctas, s);
-        case EPI_SWIGLU_BF16: return launch<NT, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, s);
+        case EPI_STORE_BF16: return launch<NT, EPI_STORE_BF16>(mw, ma, p, max_ctas, defer, s);
+        case EPI_STORE_F32: return launch<NT, EPI_STORE_F32>(mw, ma, p, max_ctas, defer, s);
+        case EPI_ADD_F32: return launch<NT, EPI_ADD_F32>(mw, ma, p, max_ctas, defer, s);
+        case EPI_SWIGLU_BF16: return launch<NT, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, defer, s);
     }
     return (int)cudaErrorInvalidValue;
 }
@@ -338,14 +435,18 @@ RS_EXPORT long rs_skinny_gemm_workspace_floats() { return (long)rs_tma::sm_count
 
 // C[M, N] (=|+=) A[M, K] . W[N, K]^T for M <= 64, bf16 inputs; same epilogue codes as rs_gemm_bf16_tc.  a_rows is the
 // row capacity of A's buffer.  workspace as sized above.  Launches that share a workspace must not overlap on the GPU.
+// defer != 0 (f32 += epilogue, M <= 8 only): the tiles that several CTAs share stay unfinished in the workspace until
+// rs_skinny_finish or rs_skinny_finish_rmsnorm is launched with the same C, shape, workspace and max_ctas; no other
+// product may use the workspace in between.
 RS_EXPORT int rs_skinny_gemm_bf16(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M,
-                                  int N, int K, int epi, float* workspace, int max_ctas, int* status,
+                                  int N, int K, int epi, float* workspace, int max_ctas, int defer, int* status,
                                   void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
         workspace == nullptr)
         return (int)cudaErrorInvalidValue;
     if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
+    if (defer && (epi != EPI_ADD_F32 || M > 8)) return (int)cudaErrorInvalidValue;
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
     CUtensorMap mw, ma;
     int rc = rs_tma::get_map(W, N, K, ldw, TILE_N, &mw);
@@ -357,11 +458,44 @@ RS_EXPORT int rs_skinny_gemm_bf16(const void* A, long lda, long a_rows, const vo
     p.status = status;
     cudaStream_t s = (cudaStream_t)stream;
     switch (nt) {
-        case 1: return launch_epi<1>(epi, mw, ma, p, max_ctas, s);
-        case 2: return launch_epi<2>(epi, mw, ma, p, max_ctas, s);
-        case 4: return launch_epi<4>(epi, mw, ma, p, max_ctas, s);
-        default: return launch_epi<8>(epi, mw, ma, p, max_ctas, s);
+        case 1: return launch_epi<1>(epi, mw, ma, p, max_ctas, defer != 0, s);
+        case 2: return launch_epi<2>(epi, mw, ma, p, max_ctas, false, s);
+        case 4: return launch_epi<4>(epi, mw, ma, p, max_ctas, false, s);
+        default: return launch_epi<8>(epi, mw, ma, p, max_ctas, false, s);
     }
+}
+
+// Finishes a deferred product: C += the partials of the shared tiles.
+RS_EXPORT int rs_skinny_finish(void* C, long ldc, int M, int N, int K, float* workspace, int max_ctas, void* stream) {
+    if (M <= 0 || M > 8 || N <= 0 || K <= 0 || workspace == nullptr) return (int)cudaErrorInvalidValue;
+    SkinnyParams p;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.status = nullptr;
+    const long grid = grid_of(N, K, max_ctas);
+    if (grid < 2) return 0;
+    return rs_launch_pdl(skinny_reduce_kernel<1, EPI_ADD_F32>, dim3((unsigned)(grid - 1)), dim3(CONSUMER_WARPS * 32), 0,
+                         (cudaStream_t)stream, p, (int)grid);
+}
+
+// Whether rs_skinny_finish_rmsnorm takes a row of this width with these pitches and pointers.
+RS_EXPORT int rs_skinny_finish_rmsnorm_supported(const void* C, long ldc, int N, const void* w, const void* out, long out_stride) {
+    return N > 0 && N % 4 == 0 && N <= 512 * 4 * 4 && ldc % 4 == 0 && out_stride % 4 == 0 && ((long)C & 15) == 0 &&
+           ((long)out & 7) == 0 && ((long)w & 15) == 0;
+}
+
+// Finishes a deferred product and writes out[m] = RMSNorm(C[m]) * w as bfloat16, in one kernel.
+RS_EXPORT int rs_skinny_finish_rmsnorm(void* C, long ldc, int M, int N, int K, float* workspace, int max_ctas, const void* w,
+                                       int w_dt, float eps, void* out, long out_stride, void* stream) {
+    if (M <= 0 || M > 8 || K <= 0 || workspace == nullptr || (w_dt != RS_F32 && w_dt != RS_BF16) ||
+        !rs_skinny_finish_rmsnorm_supported(C, ldc, N, w, out, out_stride))
+        return (int)cudaErrorInvalidValue;
+    SkinnyParams p;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.status = nullptr;
+    const int G = (int)grid_of(N, K, max_ctas);
+    auto* o = (__nv_bfloat16*)out;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (N <= 512 * 4) return rs_launch_pdl(skinny_finish_rmsnorm_kernel<1>, dim3(M), dim3(512), 0, s, p, G, w, w_dt, eps, o, out_stride);
+    if (N <= 512 * 8) return rs_launch_pdl(skinny_finish_rmsnorm_kernel<2>, dim3(M), dim3(512), 0, s, p, G, w, w_dt, eps, o, out_stride);
+    return rs_launch_pdl(skinny_finish_rmsnorm_kernel<4>, dim3(M), dim3(512), 0, s, p, G, w, w_dt, eps, o, out_stride);
 }
 
 // Turns programmatic dependent launch on or off for every kernel of this library (default on).

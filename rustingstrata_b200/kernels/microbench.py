@@ -43,7 +43,7 @@ def timed(fn, n_bufs: int, iters: int, once: bool) -> float:
     return e0.elapsed_time(e1) / iters * 1000.0
 
 
-def bench_linear(kind: str, M: int, N: int, K: int, epilogue: str, bn: int, iters: int, once: bool):
+def bench_linear(kind: str, M: int, N: int, K: int, epilogue: str, bn: int, iters: int, once: bool, then_norm: str = ""):
     nb = max(2, int(400e6 / (N * K * 2)) + 1)
     ws = [(torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(nb)]
     rows = max(M, 128)
@@ -57,7 +57,18 @@ def bench_linear(kind: str, M: int, N: int, K: int, epilogue: str, bn: int, iter
         out, kw = torch.zeros(rows, N, device=DEV), dict(accumulate=True)
     else:
         out, kw = torch.zeros(rows, N // 2, device=DEV, dtype=torch.bfloat16), dict(swiglu=True)
-    if kind == "skinny":
+    if kind == "skinny" and then_norm:
+        # the product into the residual stream and the row norm behind it: as two kernels and a small one between
+        # them ("apart"), or with the norm adding up the product's shared tiles ("owed")
+        nw = torch.ones(N, device=DEV, dtype=torch.bfloat16)
+        h = torch.empty(rows, N, device=DEV, dtype=torch.bfloat16)
+
+        def both(i):
+            owed = ops.skinny_gemm_bf16(a, ws[i], out, M, accumulate=True, defer=then_norm == "owed")
+            ops.rmsnorm(out, nw, 1e-6, h, n_rows=M, pending=owed)
+        us = timed(both, nb, iters, once)
+        epilogue = f"add then norm ({then_norm})"
+    elif kind == "skinny":
         us = timed(lambda i: ops.skinny_gemm_bf16(a, ws[i], out, M, **kw), nb, iters, once)
     elif kind == "mid":
         us = timed(lambda i: ops.mid_gemm_bf16(a, ws[i], out, M, **kw), nb, iters, once)
@@ -125,10 +136,12 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--force", default="", help="prefill_attention: tc | mma | simt instead of the default choice")
+    ap.add_argument("--then-norm", default="", choices=["", "apart", "owed"],
+                    help="skinny with --epilogue add: time the product together with the RMSNorm of its rows")
     ap.add_argument("--once", action="store_true", help="a few plain launches, no graph and no timing (for profilers)")
     a = ap.parse_args(argv)
     if a.kernel in ("skinny", "mid", "gemm"):
-        bench_linear(a.kernel, a.m, a.n, a.k, a.epilogue, a.bn, a.iters, a.once)
+        bench_linear(a.kernel, a.m, a.n, a.k, a.epilogue, a.bn, a.iters, a.once, a.then_norm)
     elif a.kernel == "decode_attention":
         bench_decode_attention(a.batch, a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size, a.iters, a.once)
     elif a.kernel == "prefill_attention":

@@ -128,9 +128,26 @@ def gather_i32(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor, n: int) 
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
-    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight.  x float32 [*, n]."""
+            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None, pending=None) -> None:
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight.  x float32 [*, n].
+
+    ``pending``: a :class:`PendingSum` still owed to ``x``.  If it covers exactly the rows that are normed, one kernel
+    adds the partial sums and norms the rows (the same bits as the two kernels in turn); else it is finished first."""
     _cuda(x, weight, out, rows)
+    if pending is not None and not pending.done:
+        nr = n_rows if n_rows is not None else (out.shape[0] if rows is not None else x.shape[0])
+        lib = bf16lib()
+        if (rows is None and pending.out.data_ptr() == x.data_ptr() and pending.out.stride(0) == x.stride(0)
+                and pending.n_rows == nr and pending.N == x.shape[1] == weight.numel() == out.shape[1]
+                and x.dtype == torch.float32 and out.dtype == torch.bfloat16 and weight.is_contiguous()
+                and weight.dtype in (torch.float32, torch.bfloat16) and nr <= out.shape[0] and x.stride(1) == 1 and out.stride(1) == 1
+                and lib.rs_skinny_finish_rmsnorm_supported(_ptr(x), x.stride(0), pending.N, _ptr(weight), _ptr(out), out.stride(0))):
+            pending.done = True
+            _check(lib.rs_skinny_finish_rmsnorm(_ptr(x), x.stride(0), nr, pending.N, pending.K, _ptr(pending.workspace),
+                                                pending.max_ctas, _ptr(weight), dtype_code(weight), float(eps), _ptr(out),
+                                                out.stride(0), _stream()), "skinny_finish_rmsnorm")
+            return
+        pending.finish()
     _rows_contiguous(x, "rmsnorm x")
     _rows_contiguous(out, "rmsnorm out")
     n = x.shape[1]
@@ -236,8 +253,12 @@ def bf16lib():
         lib.rs_gemm_bf16_tc.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_void_p, c_void_p]
         lib.rs_skinny_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
-                                            c_int, c_void_p, c_int, c_void_p, c_void_p]
+                                            c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.rs_skinny_gemm_workspace_floats.restype = c_long
+        lib.rs_skinny_finish.argtypes = [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+        lib.rs_skinny_finish_rmsnorm_supported.argtypes = [c_void_p, c_long, c_int, c_void_p, c_void_p, c_long]
+        lib.rs_skinny_finish_rmsnorm.argtypes = [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                                 c_float, c_void_p, c_long, c_void_p]
         lib.rs_mid_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                          c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_mid_gemm_workspace_floats.restype = c_long
@@ -334,11 +355,36 @@ def _skinny_scratch(device):
     return ws
 
 
+class PendingSum:
+    """A product into the float32 residual stream whose last step is still owed: the partial sums of the weight tiles
+    that several CTAs shared lie in the product's workspace and have not been added to ``out`` yet.  Whoever reads
+    ``out`` next either takes the object along (``rmsnorm(..., pending=...)`` adds the partials while it reads the
+    rows) or calls :meth:`finish` first.  No other product may run in between: it would overwrite the workspace."""
+
+    def __init__(self, out: torch.Tensor, n_rows: int, N: int, K: int, workspace: torch.Tensor, max_ctas: int):
+        self.out, self.n_rows, self.N, self.K, self.workspace, self.max_ctas = out, n_rows, N, K, workspace, max_ctas
+        self.done = False
+
+    def finish(self) -> None:
+        """out += the partial sums (the small kernel that the product would have launched itself)."""
+        if not self.done:
+            self.done = True
+            _check(bf16lib().rs_skinny_finish(_ptr(self.out), self.out.stride(0), self.n_rows, self.N, self.K,
+                                              _ptr(self.workspace), self.max_ctas, _stream()), "skinny_finish")
+
+
+SKINNY_DEFER_ROWS = 8    # the deferred form exists for the thread layout of up to 8 rows
+
+
 def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
-                     swiglu: bool = False, status: Optional[torch.Tensor] = None, max_ctas: int = 0) -> None:
+                     swiglu: bool = False, status: Optional[torch.Tensor] = None, max_ctas: int = 0,
+                     defer: bool = False) -> Optional[PendingSum]:
     """out[:n_rows] (=|+=) a[:n_rows] @ weight.T for n_rows <= 64: persistent CTAs stream the weight through a
-    TMA-fed ring of shared-memory stages (csrc/skinny_gemm_tma.cu)."""
+    TMA-fed ring of shared-memory stages (csrc/skinny_gemm_tma.cu).  With ``defer`` (float32 +=, up to 8 rows) the
+    kernel that adds up the shared tiles is not launched and a :class:`PendingSum` is returned instead."""
     N, K = _check_product(a, weight, out, n_rows, swiglu)
+    if defer and not (accumulate and out.dtype == torch.float32 and n_rows <= SKINNY_DEFER_ROWS):
+        raise KernelError("skinny_gemm_bf16 defers only a float32 += of up to 8 rows")
     if n_rows > SKINNY_MAX_ROWS or not tensor_core_shape_ok(a, weight) or N <= 0:
         raise KernelError(f"skinny_gemm_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
                           f"{tuple(weight.shape)} {weight.dtype}: at most {SKINNY_MAX_ROWS} rows, bfloat16, 16-byte aligned")
@@ -347,7 +393,8 @@ def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n
     ws = _skinny_scratch(a.device)
     _check(bf16lib().rs_skinny_gemm_bf16(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
                                          out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), _ptr(ws),
-                                         max_ctas, _ptr(status), _stream()), "skinny_gemm_bf16", 2)
+                                         max_ctas, 1 if defer else 0, _ptr(status), _stream()), "skinny_gemm_bf16", 1 if defer else 2)
+    return PendingSum(out, n_rows, N, K, ws, max_ctas) if defer else None
 
 
 MID_MAX_ROWS = 128       # what the stream-K tcgen05 kernel takes; the engine uses it from SKINNY_ROWS + 1 rows up to here
@@ -393,14 +440,16 @@ def _default_status(device) -> torch.Tensor:
 
 
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
-           status: Optional[torch.Tensor] = None) -> None:
+           status: Optional[torch.Tensor] = None, may_defer: bool = False) -> Optional[PendingSum]:
     """The engine's matrix product: the tensor-core kernels for bfloat16 operands whose rows are 16-byte
     aligned (skinny kernel up to 8 rows, stream-K tcgen05 kernel up to 128, tiled tcgen05 kernel above), the
     CUDA-core kernel for everything else
-    (the 32-bit engine, float32-stored weights, odd widths)."""
+    (the 32-bit engine, float32-stored weights, odd widths).  ``may_defer``: the caller hands a :class:`PendingSum`
+    on to the next reader of ``out`` if the kernel that runs can leave one (else None comes back and ``out`` is whole)."""
     if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
         if n_rows <= SKINNY_ROWS and weight.numel() < SKINNY_MAX_WEIGHT:
-            skinny_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)
+            defer = may_defer and accumulate and out.dtype == torch.float32 and n_rows <= SKINNY_DEFER_ROWS
+            return skinny_gemm_bf16(a, weight, out, n_rows, accumulate, status=status, defer=defer)
         elif n_rows <= MID_MAX_ROWS:
             mid_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)
         else:

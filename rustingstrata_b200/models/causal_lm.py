@@ -126,8 +126,14 @@ class CausalLM:
         rt = self.runtime
         residual = rt.get_scratch("residual", torch.float32)[:, : self.spec.hidden_size]
         self.embedding.forward(ctx, residual)
-        for info in self.calls:
+        for k, info in enumerate(self.calls):
+            # a block's last product may leave its final sum to the next block's first norm, if that norm can take it
+            ctx.next_block_takes_owed = (k + 1 < len(self.calls)
+                                         and self.blocks[self.calls[k + 1].layer].first_reader_takes_owed)
             self.blocks[info.layer].forward(residual, ctx, info)
+        if ctx.owed is not None:
+            ctx.owed.finish()
+            ctx.owed = None
         if ctx.n_logit_rows == 0:
             return None
         R = ctx.n_logit_rows

@@ -167,4 +167,4 @@ class PagedAttention(Mixer):
                                  max_splits=plan["max_splits"], split_start=plan["split_start"],
                                  total_splits=plan["total_splits"],
                                  partial=rt.get_scratch("attn_partial", torch.float32), **common)
-        ops.linear(out, self.w_o, residual, T, accumulate=True, status=ctx.status)
+        ctx.owed = ops.linear(out, self.w_o, residual, T, accumulate=True, status=ctx.status, may_defer=ctx.may_owe)

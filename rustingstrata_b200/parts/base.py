@@ -117,6 +117,13 @@ class StepContext:
     status: torch.Tensor           # [1] error bits set by kernels
     host: HostBatch
     plans: Dict[Any, Dict[str, Any]] = field(default_factory=dict)   # per plan key: device arrays + host scalars
+    # A product into the residual stream may leave its last step (adding up partial sums) to the next reader of the
+    # stream.  ``may_owe``: set by the block around a mixer's or feed-forward's call when that reader can take it;
+    # ``owed``: what the mixer or feed-forward left (an object with finish()), taken by the block for the next norm;
+    # ``next_block_takes_owed``: set by the model before each block, for the block's last product.
+    may_owe: bool = False
+    owed: Any = None
+    next_block_takes_owed: bool = False
 
 
 class Part:
@@ -172,7 +179,11 @@ class FeedForward(Part):
 
 
 class Norm(Part):
-    """Normalisation of the float32 residual stream into the activation type."""
+    """Normalisation of the float32 residual stream into the activation type.
+
+    A norm whose ``takes_owed`` is true has a keyword ``owed`` in ``forward``: a sum still owed to ``x`` (see
+    StepContext), which it adds while it reads the rows."""
+    takes_owed = False
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
@@ -189,5 +200,22 @@ class Block(Part):
         super().__init__(spec, runtime)
         self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
 
+    @property
+    def first_reader_takes_owed(self) -> bool:
+        """Whether the first thing this block does with the residual stream is a norm that takes an owed sum; only
+        then may the block before it leave one."""
+        return False
+
     def forward(self, residual: torch.Tensor, ctx: StepContext, call: CallInfo) -> None:
         raise NotImplementedError
+
+    @staticmethod
+    def norm_of_stream(norm: Norm, residual: torch.Tensor, out: torch.Tensor, ctx: StepContext) -> None:
+        """norm(residual) → out for the step's tokens, settling what is owed to the stream on the way."""
+        owed, ctx.owed = ctx.owed, None
+        if owed is not None and getattr(norm, "takes_owed", False):
+            norm.forward(residual, out, ctx.n_tokens, owed=owed)
+            return
+        if owed is not None:
+            owed.finish()
+        norm.forward(residual, out, ctx.n_tokens)

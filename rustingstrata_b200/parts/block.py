@@ -18,9 +18,17 @@ class PreNormBlock(Block):
         self.hidden = int(spec.params["hidden"])
         runtime.scratch("normed", runtime.max_batch_tokens, self.hidden)
 
+    @property
+    def first_reader_takes_owed(self):
+        return getattr(self.mixer_norm, "takes_owed", False)
+
     def forward(self, residual, ctx, call):
         h = self.runtime.get_scratch("normed")[:, : self.hidden]
-        self.mixer_norm.forward(residual, h, ctx.n_tokens)
+        self.norm_of_stream(self.mixer_norm, residual, h, ctx)
+        ctx.may_owe = getattr(self.ff_norm, "takes_owed", False)
         self.mixer.forward(h, residual, ctx, call)
-        self.ff_norm.forward(residual, h, ctx.n_tokens)
+        ctx.may_owe = False
+        self.norm_of_stream(self.ff_norm, residual, h, ctx)
+        ctx.may_owe = ctx.next_block_takes_owed
         self.feed_forward.forward(h, residual, ctx)
+        ctx.may_owe = False

@@ -61,4 +61,4 @@ class GatedMLP(FeedForward):
         else:
             ops.linear(h, self.w_gate_up, gate_up, T)
             ops.silu_mul(gate_up, act, T)
-        ops.linear(act, self.w_down, residual, T, accumulate=True, status=ctx.status)
+        ctx.owed = ops.linear(act, self.w_down, residual, T, accumulate=True, status=ctx.status, may_defer=ctx.may_owe)

@@ -13,6 +13,7 @@ from .spec import TensorNeed
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     """params: width, eps.  tensors: weight."""
+    takes_owed = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -26,5 +27,5 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.weight = tensors[self.spec.tensors["weight"]].contiguous()
 
-    def forward(self, x, out, n_rows, rows=None):
-        ops.rmsnorm(x, self.weight, self.eps, out, rows=rows, n_rows=n_rows)
+    def forward(self, x, out, n_rows, rows=None, owed=None):
+        ops.rmsnorm(x, self.weight, self.eps, out, rows=rows, n_rows=n_rows, pending=owed)

@@ -233,6 +233,29 @@ def test_steps_launched_ahead_change_nothing(tiny_models, dtype):
     assert slow_e[1][1] == "eos" and len(slow_e[1][0]) <= 10
 
 
+def test_sums_left_to_the_next_norm_change_no_bit(tiny_models, monkeypatch):
+    """In small decode steps the output and down projections leave the adding-up of their shared tiles to the norm
+    that reads the residual stream next.  Fewer kernels run, and the tokens and logits are the same bits as with
+    every product finishing itself."""
+    from rustingstrata_b200.kernels import ops
+    cfg, w = P.read_model(tiny_models["D"])
+    prompts = [random_tokens(cfg["vocab_size"], n, 70 + n) for n in (3, 12, 20)]
+
+    def run():
+        eng = engine(tiny_models, "D", "bfloat16")
+        n0 = ops.launch_count()
+        outs = eng.generate(prompts, max_new_tokens=12)
+        n = ops.launch_count() - n0
+        eng.runner.check_status()
+        return outs, n
+
+    with_owed, n_owed = run()
+    monkeypatch.setattr(ops, "SKINNY_DEFER_ROWS", 0)
+    without, n_plain = run()
+    assert with_owed == without
+    assert n_owed < n_plain
+
+
 def test_bench_method_of_the_entry_point(tiny_models):
     eng = engine(tiny_models, "D", "bfloat16")
     recs = eng.bench(pp=[20, 130], tg=6, reps=2, batch=3)

@@ -156,6 +156,64 @@ def test_streaming_skinny_kernel_any_split_of_the_work(max_ctas):
         assert err(f1, want) < 1e-5 and torch.equal(f1, f2)
 
 
+@pytest.mark.parametrize("M", [1, 2, 5, 8])
+@pytest.mark.parametrize("max_ctas", [0, 1, 3, 50, 147])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (4096, 12288), (1000, 1000), (100, 72), (5120, 640), (8192, 256), (64, 2048)])
+@pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32])
+def test_product_that_leaves_its_last_sum_to_the_norm(M, max_ctas, N, K, w_dtype):
+    """x += a W^T with the shared tiles left in the workspace, then one kernel that adds them and norms the rows:
+    the same bits, in x and in the normed rows, as the product that finishes itself followed by the row norm.
+    Tiles shared by two to many CTAs, tiles owned whole, widths that end inside a tile."""
+    o = ops()
+    a, w = make(M, N, K, cap=M + 2, seed=M + N)
+    base = torch.randn(M + 2, N, device=DEV)
+    nw = (1 + 0.1 * torch.randn(N, device=DEV)).to(w_dtype)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x1, x2, x3 = base.clone(), base.clone(), base.clone()
+    h1 = torch.full((M + 2, N), 3.0, device=DEV, dtype=torch.bfloat16)
+    h2 = h1.clone()
+    assert o.skinny_gemm_bf16(a, w, x1, M, accumulate=True, status=st, max_ctas=max_ctas) is None
+    o.rmsnorm(x1, nw, 1e-6, h1, n_rows=M)
+    owed = o.skinny_gemm_bf16(a, w, x2, M, accumulate=True, status=st, max_ctas=max_ctas, defer=True)
+    o.rmsnorm(x2, nw, 1e-6, h2, n_rows=M, pending=owed)
+    assert owed.done and torch.equal(x1, x2) and torch.equal(h1, h2) and torch.all(h2[M:] == 3.0)
+    owed = o.skinny_gemm_bf16(a, w, x3, M, accumulate=True, status=st, max_ctas=max_ctas, defer=True)
+    owed.finish()
+    owed.finish()                                           # a second call does nothing
+    assert torch.equal(x1, x3) and st.item() == 0
+
+
+def test_owed_sum_is_finished_first_when_the_norm_cannot_take_it():
+    """Other rows than the product's (a gather), another buffer, a float32 output: the sum is added by its own kernel
+    and the plain norm runs."""
+    o = ops()
+    M, N, K = 4, 4096, 1024
+    a, w = make(M, N, K, seed=3)
+    base = torch.randn(M, N, device=DEV)
+    nw = torch.ones(N, device=DEV, dtype=torch.bfloat16)
+    want_x = base.clone()
+    o.skinny_gemm_bf16(a, w, want_x, M, accumulate=True)
+    rows = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    for kind in ("gather", "f32", "fewer"):
+        x = base.clone()
+        owed = o.skinny_gemm_bf16(a, w, x, M, accumulate=True, defer=True)
+        if kind == "gather":
+            h, want = torch.empty(2, N, device=DEV, dtype=torch.bfloat16), torch.empty(2, N, device=DEV, dtype=torch.bfloat16)
+            o.rmsnorm(x, nw, 1e-6, h, rows=rows, n_rows=2, pending=owed)
+            o.rmsnorm(want_x, nw, 1e-6, want, rows=rows, n_rows=2)
+        elif kind == "f32":
+            h, want = torch.empty(M, N, device=DEV), torch.empty(M, N, device=DEV)
+            o.rmsnorm(x, nw, 1e-6, h, pending=owed)
+            o.rmsnorm(want_x, nw, 1e-6, want)
+        else:
+            h, want = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16), torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+            o.rmsnorm(x, nw, 1e-6, h, n_rows=2, pending=owed)
+            o.rmsnorm(want_x, nw, 1e-6, want, n_rows=2)
+        assert owed.done and torch.equal(x, want_x) and torch.equal(h, want)
+    with pytest.raises(o.KernelError):
+        o.skinny_gemm_bf16(a, w, torch.zeros(M, N, device=DEV, dtype=torch.bfloat16), M, defer=True)
+
+
 @pytest.mark.parametrize("M", [1, 17, 33, 40, 64, 65, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 128), (100, 72), (4096, 4096), (6144, 4096), (1000, 1000), (24576, 4096),
                                  (4096, 12288), (151936, 256), (70, 8), (130, 136)])
