@@ -172,8 +172,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    pdl_launch_dependents();
     if (warp == TMA_WARP) {
         // ------------------------------------------------------------ TMA producer: lane i loads page i of a block
+        pdl_wait();                                           // q and the portion's keys and values come from the kernel before
         if (lane == 0) {
             mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
 #pragma unroll
@@ -496,8 +498,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    kern<<<dim3(n_work, p.n_kv * (p.group / p.pack)), THREADS, smem, s>>>(mq, mkv, p);
-    return rs_launch_result();
+    return rs_launch_pdl(kern, dim3(n_work, p.n_kv * (p.group / p.pack)), dim3(THREADS), (size_t)smem, s, mq, mkv, p);
 }
 }  // namespace
 

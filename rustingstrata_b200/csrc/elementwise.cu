@@ -223,13 +223,13 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     const int pos = positions[t];
     __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
     __nv_bfloat16* dst = src;
-    bool is_v = false, ok = live;
+    bool is_v = false, ok = live, bad_page = false;
     if (h >= n_q) {
         const int kvh = (h - n_q) % n_kv;
         is_v = (h - n_q) / n_kv != 0;
         const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
         if (page < 0 || page >= num_pages) {
-            if (sub == 0 && live) atomicOr(status, RS_STATUS_BAD_PAGE);
+            bad_page = sub == 0 && live;
             ok = false;
         } else {
             dst = cache + (size_t)page * page_stride + ((size_t)((is_v ? 1 : 0) * n_kv + kvh) * page_size + (pos % page_size)) * hd;
@@ -269,6 +269,7 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
         }
     }
     pdl_wait();
+    if (bad_page) atomicOr(status, RS_STATUS_BAD_PAGE);         // nothing is written before the wait
     Vec ua, ub;
 #pragma unroll
     for (int k = 0; k < E / 2; ++k) ua.w[k] = ub.w[k] = 0u;

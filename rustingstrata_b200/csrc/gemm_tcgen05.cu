@@ -204,15 +204,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    // Launched with programmatic stream serialization the kernel may have come this far while its predecessor in the
+    // stream is still running.  The weights are nobody's output: the producer starts the first ring of W tiles, then
+    // waits for the predecessor before it touches A; the epilogue warps wait before they touch C.
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int s = 0; uint32_t phase = 0;
+            const int pre = num_kb < C::STAGES ? num_kb : C::STAGES;              // stages of the first tile started early
+            {
+                const int n0 = (blockIdx.x / tiles_m) * bn;
+                for (int kb = 0; kb < pre; ++kb) {
+                    mbar_expect_tx(full_bar(kb), A_BYTES + bn * BK * 2);
+                    tma_load_2d(base + kb * C::STAGE_BYTES + A_BYTES, &map_w, kb * BK, n0, full_bar(kb));
+                }
+                pdl_wait();
+                const int m0 = (blockIdx.x % tiles_m) * BM;
+                for (int kb = 0; kb < pre; ++kb) tma_load_2d(base + kb * C::STAGE_BYTES, &map_a, kb * BK, m0, full_bar(kb));
+            }
+            int s = pre == C::STAGES ? 0 : pre; uint32_t phase = pre == C::STAGES ? 1u : 0u;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * bn;       // m fastest: neighbours share W
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = t == (int)blockIdx.x ? pre : 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), A_BYTES + bn * BK * 2);
                     const uint32_t sa = base + s * C::STAGE_BYTES;
@@ -253,6 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;                            // TMEM lanes [32 * quarter, +32) belong to this warp
         int local = 0;
         bool ok = true;
+        pdl_wait();
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
             const int buf = local & 1;
             const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * bn;
@@ -301,8 +317,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, in
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + p.bn - 1) / p.bn);
     int grid = tiles < sm_count() ? tiles : sm_count();
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    kern<<<grid, THREADS, Cfg<BN>::SMEM_BYTES, s>>>(ma, mw, p);
-    return rs_launch_result();
+    return rs_launch_pdl(kern, dim3(grid), dim3(THREADS), (size_t)Cfg<BN>::SMEM_BYTES, s, ma, mw, p);
 }
 
 template <int BN>

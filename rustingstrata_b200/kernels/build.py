@@ -33,7 +33,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "core": {"sources": ["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "sampling.cu"], "link": []},
     # tensor-core paths of the bfloat16 engine; the 32-bit engine never loads this library
-    "bf16": {"sources": ["gemm_tcgen05.cu", "skinny_gemm_tma.cu", "mid_gemm_tcgen05.cu", "attention_decode_mma.cu", "attention_prefill_mma.cu", "attention_prefill_tc.cu", "attention_prefill_tc2.cu"], "link": []},
+    "bf16": {"sources": ["gemm_tcgen05.cu", "skinny_gemm_tma.cu", "mid_gemm_tcgen05.cu", "attention_decode_mma.cu", "attention_prefill_mma.cu", "attention_prefill_tc.cu"], "link": []},
 }
 
 

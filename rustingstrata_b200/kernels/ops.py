@@ -275,9 +275,6 @@ def bf16lib():
                                                 c_int, c_float, c_void_p, c_void_p]
         lib.rs_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_tc_q_per_cta.argtypes = [c_int, c_int]
-        lib.rs_attention_prefill_tc2.argtypes = lib.rs_attention_prefill_tc.argtypes
-        lib.rs_attention_prefill_tc2_supported.argtypes = [c_int, c_int, c_int, c_int]
-        lib.rs_attention_prefill_tc2_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_attention_prefill_bf16_supported.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16_q_per_cta.argtypes = [c_int, c_int]
         _bf16 = lib
@@ -536,8 +533,6 @@ def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_di
     kind = attention_prefill_kernel(dtype, n_q, n_kv, head_dim, page_size, force)
     if kind == "tc":
         return int(bf16lib().rs_attention_prefill_tc_q_per_cta(n_q, n_kv))
-    if kind == "tc2":
-        return int(bf16lib().rs_attention_prefill_tc2_q_per_cta(n_q, n_kv))
     if kind == "mma":
         return int(bf16lib().rs_attention_prefill_bf16_q_per_cta(n_q, n_kv))
     return attention_q_per_cta(n_q, n_kv)
@@ -565,8 +560,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
         if t.dtype != torch.int32:
             raise KernelError(f"attention_prefill: {name} must be int32")
-    if kind in ("tc", "tc2"):
-        fn = bf16lib().rs_attention_prefill_tc if kind == "tc" else bf16lib().rs_attention_prefill_tc2
+    if kind == "tc":
+        fn = bf16lib().rs_attention_prefill_tc
         _check(fn(
             _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0],
             page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv,

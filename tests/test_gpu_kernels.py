@@ -390,21 +390,6 @@ def test_prefill_tcgen05_kernel(n_q, n_kv, hd, page, window):
     close(fast, want, 1.5e-2)
 
 
-@pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (16, 1, 64, 8), (10, 2, 64, 16), (3, 3, 128, 32),
-                                              (4, 1, 64, 128)])
-@pytest.mark.parametrize("window", [0, 70, 200])
-def test_prefill_tcgen05_kernel_with_two_query_tiles_per_cta(n_q, n_kv, hd, page, window):
-    """Portions that fill both tiles, only the first, or end inside either; the second tile sees keys the first does not."""
-    seqs = [(37, 37), (300, 2), (65, 20), (128, 128), (129, 128), (200, 33), (256, 2), (700, 257), (2, 2), (1000, 3), (513, 200),
-            (1500, 700)]
-    torch.manual_seed(6)
-    fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, prefill="tc2")
-    close(fast, want, 1.5e-2)
-    torch.manual_seed(6)
-    one, _ = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, prefill="tc")
-    close(fast, one.double().cpu(), 1.5e-2)
-
-
 def test_attention_refuses_unsupported_sizes():
     from rustingstrata_b200.kernels.ops import KernelError
     with pytest.raises(KernelError, match="head size"):
