@@ -28,12 +28,16 @@
 // cores, each weight read once for up to 4 inputs.
 #include "tma_helpers.cuh"
 #include "mma_helpers.cuh"
+#include "skinny_partials.cuh"
 
 namespace {
-constexpr int TILE_N = 64;                 // rows of W per unit
+using rs_skinny::TILE_N;                   // rows of W per unit
+using rs_skinny::TILE_K;                   // k per unit
+using rs_skinny::first_unit;
+using rs_skinny::cta_of_unit;
 constexpr int BOX_K = 64;                  // k per TMA box (one 128-byte swizzle row)
 constexpr int BOXES = 2;                   // boxes per unit
-constexpr int TILE_K = BOX_K * BOXES;      // k per unit
+static_assert(TILE_K == BOX_K * BOXES, "a unit is two boxes deep");
 constexpr int W_BOX_BYTES = TILE_N * BOX_K * 2;
 constexpr int W_BYTES = W_BOX_BYTES * BOXES;
 constexpr int CONSUMER_WARPS = 4;
@@ -54,13 +58,6 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
-}
-
-// first unit of CTA c when U units are dealt to G CTAs as evenly as possible
-__device__ __forceinline__ int first_unit(int c, int U, int G) { return c * (U / G) + (c < U % G ? c : U % G); }
-__device__ __forceinline__ int cta_of_unit(int u, int U, int G) {
-    const int base = U / G, rem = U % G;
-    return u < rem * (base + 1) ? u / (base + 1) : rem + (u - rem * (base + 1)) / base;
 }
 
 template <int NT, int EPI>
@@ -316,7 +313,7 @@ __global__ void __launch_bounds__(512) skinny_finish_rmsnorm_kernel(const Skinny
     const int U = n_tiles * KB;
     const int per_cta = U / G, extra = U % G;                  // the first `extra` CTAs take one unit more
     for (int tile = threadIdx.x; tile < n_tiles; tile += 512)
-        sharers[tile] = make_int2(cta_of_unit(tile * KB, U, G), cta_of_unit(tile * KB + KB - 1, U, G));
+        sharers[tile] = rs_skinny::sharers_of_tile(tile, KB, U, G);
     const int n4 = p.N >> 2;
     float wv[VPT][4];
 #pragma unroll
@@ -338,35 +335,28 @@ __global__ void __launch_bounds__(512) skinny_finish_rmsnorm_kernel(const Skinny
     pdl_wait();
     float* xr = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc;
     float4 v[VPT];
-    float ss = 0.f;
+    rs_skinny::OwedBatch part[VPT];
+    int2 sh[VPT];
+    // every load first: the row's values and the first four contributors' partials of each of this thread's columns
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
         const int idx = threadIdx.x + u * 512;
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sh[u] = make_int2(0, 0);
         if (idx < n4) {
-            const int n0 = idx * 4;
             v[u] = ld_dep(reinterpret_cast<const float4*>(xr) + idx);
-            const int tile = n0 / TILE_N, r = n0 % TILE_N;
-            const int tile_first = tile * KB;
-            const int c_first = sharers[tile].x, c_last = sharers[tile].y;
-            if (c_first != c_last) {
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                constexpr int CH = 4;                                     // contributors whose loads are in flight together
-                for (int c0 = c_first; c0 <= c_last; c0 += CH) {
-                    float4 q[CH];
+            sh[u] = sharers[idx * 4 / TILE_N];
+            if (sh[u].x != sh[u].y) rs_skinny::owed_begin4(part[u], p.workspace, m, idx * 4, KB, per_cta, extra, sh[u].x, sh[u].y);
+        }
+    }
+    float ss = 0.f;
 #pragma unroll
-                    for (int cc = 0; cc < CH; ++cc) {
-                        const int c = min(c0 + cc, c_last);
-                        const int cslot = (c * per_cta + min(c, extra) >= tile_first) ? 0 : 1;     // first_unit(c) without the division
-                        q[cc] = ld_dep(reinterpret_cast<const float4*>(p.workspace + ((size_t)c * 2 + cslot) * (8 * TILE_N) + m * TILE_N + r));
-                    }
-#pragma unroll
-                    for (int cc = 0; cc < CH; ++cc)
-                        if (c0 + cc <= c_last) { acc.x += q[cc].x; acc.y += q[cc].y; acc.z += q[cc].z; acc.w += q[cc].w; }
-                }
-                v[u].x += acc.x; v[u].y += acc.y; v[u].z += acc.z; v[u].w += acc.w;
-                reinterpret_cast<float4*>(xr)[idx] = v[u];
-            }
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        if (idx < n4 && sh[u].x != sh[u].y) {
+            const float4 acc = rs_skinny::owed_end4(part[u], p.workspace, m, idx * 4, KB, per_cta, extra, sh[u].x, sh[u].y);
+            v[u].x += acc.x; v[u].y += acc.y; v[u].z += acc.z; v[u].w += acc.w;
+            reinterpret_cast<float4*>(xr)[idx] = v[u];
         }
         ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss); ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
     }
