@@ -18,10 +18,10 @@
 //                       buffered in tensor memory, tcgen05.commit frees the stage;
 //   warps 2-5         - epilogue: tcgen05.ld of their 32 accumulator lanes (one row of W per thread).  A row tile
 //                       whose k range this CTA covers alone is finished at once; otherwise the float32 partial
-//                       goes to a workspace and bumps the tile's counter.  The contributor that arrives last
-//                       finishes the tile after its own last segment: bulk copies bring all partials into the
-//                       then idle ring at once, they are added in CTA order (fixed by the shape alone), the
-//                       epilogue is applied and the counter reset.  Nobody waits for anybody.
+//                       goes to a workspace and the CTA is done with it.
+// A second, small kernel launched behind this one (mid_reduce_kernel) adds the partials of every shared tile in CTA
+// order (fixed by the shape alone) and applies the epilogue, so that every CTA of the product does the same work and
+// none stays behind adding up a tile.  Nobody waits for anybody.
 // Epilogues: store bf16 | store f32 | f32 += (residual add) | SiLU(gate)*up over interleaved rows of W.
 // Every wait on an mbarrier is bounded (tma_helpers.cuh).
 //
@@ -48,7 +48,6 @@ struct MidParams {
     int stages;
     int vec_ok;                // rows of C allow 16-byte (f32) / 8-byte (bf16) access at every fourth column
     float* workspace;          // [grid][2][MP][128] float32 partials
-    int* counters;             // [row tiles], zero between launches
     int* status;
 };
 
@@ -86,7 +85,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 __device__ __forceinline__ uint32_t make_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // first unit of CTA c when U units are dealt to G CTAs as evenly as possible
 __device__ __forceinline__ int first_unit(int c, int U, int G) { return c * (U / G) + (c < U % G ? c : U % G); }
@@ -160,16 +158,14 @@ mid_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - raw);
     const int stages = p.stages;
-    // barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2], fix; then tensor-memory base, abort flag, fix_tile[2]
+    // barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2]; then tensor-memory base, abort flag
     const uint32_t bar0 = base + stages * STAGE_BYTES;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
     auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * stages + b); };
     auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * stages + 2 + b); };
-    const uint32_t fix_bar = bar0 + 8u * (2 * stages + 4);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (size_t)stages * STAGE_BYTES + 8 * (2 * stages + 5));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* fix_tile = abort_flag + 1;                          // [2]: the tile to finish for each of my two partial segments, or -1
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = (p.K + TILE_K - 1) / TILE_K;
@@ -181,8 +177,6 @@ mid_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
         *abort_flag = 0;
-        fix_tile[0] = fix_tile[1] = -1;
-        mbar_init(fix_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -273,8 +267,6 @@ mid_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int nl = quarter * 32 + lane;                          // row of W within the tile
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         pdl_wait();                                                  // C and the workspace belong to earlier kernels until now
-        // A warp whose wait ran out keeps walking its segments without touching them, so that the named barrier of
-        // the four epilogue warps below always finds all of them.
         bool ok = true;
         int seg = 0;
         int u = u0;
@@ -311,86 +303,8 @@ mid_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(buf));         // the accumulator may be overwritten
             }
-            if (!whole) {
-                // my share of this tile is in the workspace: count it.  Whoever counts last will finish the tile,
-                // but only after its own last segment, so that nobody's partial is held up by somebody's additions.
-                __threadfence();
-                epilogue_sync();
-                if (threadIdx.x == 64) {
-                    const int contributors = cta_of_unit(tile_first + KB - 1, U, G) - cta_of_unit(tile_first, U, G) + 1;
-                    fix_tile[slot] = (ok && atomicAdd(p.counters + tile, 1) == contributors - 1) ? tile : -1;
-                }
-            }
             u = seg_end;
             ++seg;
-        }
-        epilogue_sync();                                             // fix_tile is written; every stage of the ring is idle
-        uint32_t fix_phase = 0;
-#pragma unroll 1
-        for (int slot = 0; slot < 2; ++slot) {
-            const int tile = fix_tile[slot];
-            if (tile < 0) continue;                                  // the same for all four warps
-            // The partials of all contributors come into the idle ring with bulk copies, all in flight at once,
-            // and are added in CTA order from there.
-            const int tile_first = tile * KB;
-            const int c_first = cta_of_unit(tile_first, U, G), c_last = cta_of_unit(tile_first + KB - 1, U, G);
-            const int nc = c_last - c_first + 1;
-            int rows = (stages * STAGE_BYTES) / (nc * TILE_N * 4);   // rows of A per pass
-            if (rows > p.M) rows = p.M;
-            __threadfence();
-            for (int m0 = 0; m0 < p.M; m0 += rows) {                  // every warp makes every pass, whatever its waits said
-                const int r_now = min(rows, p.M - m0);
-                const uint32_t bytes = (uint32_t)r_now * TILE_N * 4;
-                if (threadIdx.x == 64 && ok) {
-                    asm volatile("fence.proxy.async;" ::: "memory");
-                    mbar_expect_tx(fix_bar, bytes * nc);
-                    for (int c = c_first; c <= c_last; ++c) {
-                        const int cslot = (first_unit(c, U, G) >= tile_first) ? 0 : 1;
-                        const float* src = p.workspace + (((size_t)c * 2 + cslot) * MP + m0) * TILE_N;
-                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                     ::"r"(base + (uint32_t)(c - c_first) * bytes), "l"(src), "r"(bytes), "r"(fix_bar) : "memory");
-                    }
-                }
-                if (ok) ok = mbar_wait(fix_bar, fix_phase, abort_flag, p.status);
-                fix_phase ^= 1u;
-                if (ok) {
-                    const float4* st = reinterpret_cast<const float4*>(aligned);
-                    const int per = r_now * (TILE_N / 4);            // float4 values of one contributor
-                    // four positions per thread at a time, so that the reads of C (when the epilogue adds) are in flight together
-#pragma unroll 1
-                    for (int i0 = threadIdx.x - 64; i0 < per; i0 += 4 * 128) {
-                        float4 acc[4], old[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int i = i0 + q * 128;
-                            old[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (i < per) {
-                                acc[q] = st[i];
-                                const int m = m0 + i / (TILE_N / 4), n0 = tile * TILE_N + (i % (TILE_N / 4)) * 4;
-                                if (EPI == EPI_ADD_F32 && p.vec_ok && n0 + 3 < p.N)
-                                    old[q] = *reinterpret_cast<const float4*>((const float*)p.C + (size_t)m * p.ldc + n0);
-                            }
-                        }
-                        for (int c = 1; c < nc; ++c) {
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int i = i0 + q * 128;
-                                if (i < per) {
-                                    const float4 v = st[c * per + i];
-                                    acc[q].x += v.x; acc[q].y += v.y; acc[q].z += v.z; acc[q].w += v.w;
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int i = i0 + q * 128;
-                            if (i < per) store_four<EPI>(p, acc[q], old[q], m0 + i / (TILE_N / 4), tile * TILE_N + (i % (TILE_N / 4)) * 4);
-                        }
-                    }
-                }
-                epilogue_sync();                                     // the ring is read before the next pass overwrites it
-            }
-            if (threadIdx.x == 64) p.counters[tile] = 0;
         }
     }
     __syncthreads();
@@ -402,6 +316,68 @@ mid_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Finishes the row tiles that several CTAs of mid_gemm_kernel shared: one CTA per CTA boundary of the product (G its
+// grid); it acts if its boundary is the first one inside a tile.  The contributors' float32 partials ([row of A][128] per
+// CTA and slot) are added in CTA order, which the shape alone fixes, and the epilogue is applied.  Who shares which tile
+// is worked out before the wait for the product; for every four positions of a thread the first two contributors'
+// values and what C holds are asked for together.
+template <int MP, int EPI>
+__global__ void __launch_bounds__(256) mid_reduce_kernel(const MidParams p, int G) {
+    pdl_launch_dependents();
+    const int KB = (p.K + TILE_K - 1) / TILE_K;
+    const int U = ((p.N + TILE_N - 1) / TILE_N) * KB;
+    const int b = blockIdx.x + 1;                              // boundary between CTA b - 1 and CTA b
+    const int ub = first_unit(b, U, G);
+    const int tile = ub / KB, tile_first = tile * KB;
+    // on a tile's edge nobody shares because of this boundary; if an earlier boundary lies in the tile, its CTA acts
+    const bool acts = ub % KB != 0 && first_unit(b - 1, U, G) <= tile_first;
+    const int c_first = b - 1, c_last = acts ? cta_of_unit(tile_first + KB - 1, U, G) : b - 1;
+    const int per_cta = U / G, extra = U % G;
+    auto partial_of = [&](int c) {                             // contributor c's partial of this tile
+        const int cslot = (c * per_cta + min(c, extra) >= tile_first) ? 0 : 1;
+        return reinterpret_cast<const float4*>(p.workspace + ((size_t)c * 2 + cslot) * MP * TILE_N);
+    };
+    pdl_wait();                                                // every CTA waits, so that this grid never ends before the product
+    if (!acts) return;
+    const float4* first = partial_of(c_first);
+    const float4* second = partial_of(c_first + 1);            // a shared tile has at least two contributors
+    const int per = p.M * (TILE_N / 4);                        // float4 positions of the tile
+    constexpr int Q = 4;
+#pragma unroll 1
+    for (int i0 = threadIdx.x; i0 < per; i0 += Q * 256) {
+        float4 acc[Q], nxt[Q], old[Q];
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+            const int i = i0 + q * 256;
+            old[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < per) {
+                acc[q] = ld_dep(first + i);
+                nxt[q] = ld_dep(second + i);
+                const int m = i / (TILE_N / 4), n0 = tile * TILE_N + (i % (TILE_N / 4)) * 4;
+                if (EPI == EPI_ADD_F32 && p.vec_ok && n0 + 3 < p.N)
+                    old[q] = ld_dep(reinterpret_cast<const float4*>((const float*)p.C + (size_t)m * p.ldc + n0));
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+            if (i0 + q * 256 < per) { acc[q].x += nxt[q].x; acc[q].y += nxt[q].y; acc[q].z += nxt[q].z; acc[q].w += nxt[q].w; }
+        for (int c = c_first + 2; c <= c_last; ++c) {
+            const float4* more = partial_of(c);
+#pragma unroll
+            for (int q = 0; q < Q; ++q)
+                if (i0 + q * 256 < per) nxt[q] = ld_dep(more + i0 + q * 256);
+#pragma unroll
+            for (int q = 0; q < Q; ++q)
+                if (i0 + q * 256 < per) { acc[q].x += nxt[q].x; acc[q].y += nxt[q].y; acc[q].z += nxt[q].z; acc[q].w += nxt[q].w; }
+        }
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+            const int i = i0 + q * 256;
+            if (i < per) store_four<EPI>(p, acc[q], old[q], i / (TILE_N / 4), tile * TILE_N + (i % (TILE_N / 4)) * 4);
+        }
     }
 }
 
@@ -422,7 +398,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, MidParams p, int max_ct
     long grid = rs_tma::sm_count();
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
     if (grid > U) grid = U;
-    return rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
+    int rc = rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
+    if (rc != 0 || grid < 2) return rc;
+    return rs_launch_pdl(mid_reduce_kernel<MP, EPI>, dim3((unsigned)(grid - 1)), dim3(256), 0, s, p, (int)grid);
 }
 
 template <int MP>
@@ -439,18 +417,16 @@ int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const MidP
 
 RS_EXPORT int rs_mid_gemm_max_rows() { return 128; }
 
-// float32 values of workspace and ints of counters a launch needs (for any M <= 128 and this N).
+// float32 values of workspace a launch needs (for any M <= 128).
 RS_EXPORT long rs_mid_gemm_workspace_floats() { return (long)rs_tma::sm_count() * 2 * 128 * TILE_N; }
-RS_EXPORT long rs_mid_gemm_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
 
 // C[M, N] (=|+=) A[M, K] . W[N, K]^T for M <= 128, bf16 inputs; same epilogue codes as rs_gemm_bf16_tc.  a_rows is the
-// row capacity of A's buffer.  workspace/counters as sized above; counters must be zero before the first launch and
-// are left zero.  Launches that share a workspace must not overlap on the GPU.
+// row capacity of A's buffer.  workspace as sized above.  Launches that share a workspace must not overlap on the GPU.
 RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M, int N,
-                               int K, int epi, float* workspace, int* counters, int max_ctas, int* status, void* stream) {
+                               int K, int epi, float* workspace, int max_ctas, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 128 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
-        workspace == nullptr || counters == nullptr)
+        workspace == nullptr)
         return (int)cudaErrorInvalidValue;
     if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
     const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
@@ -460,7 +436,7 @@ RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void*
     rc = rs_tma::get_map(A, a_rows, K, lda, mp, &ma);
     if (rc) return rc;
     MidParams p;
-    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.counters = counters;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace;
     p.status = status;
     const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;

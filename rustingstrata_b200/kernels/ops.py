@@ -260,7 +260,7 @@ def bf16lib():
         lib.rs_skinny_finish_rmsnorm.argtypes = [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
                                                  c_float, c_void_p, c_long, c_void_p]
         lib.rs_mid_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
-                                         c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+                                         c_int, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_mid_gemm_workspace_floats.restype = c_long
         lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -399,13 +399,12 @@ _MID_SCRATCH = {}
 
 
 def _mid_scratch(device):
-    """Workspace and tile counters of the stream-K tcgen05 product, one pair per device, made at the first call."""
-    sc = _MID_SCRATCH.get(device)
-    if sc is None:
-        ws = torch.empty(int(bf16lib().rs_mid_gemm_workspace_floats()), dtype=torch.float32, device=device)
-        counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
-        sc = _MID_SCRATCH[device] = (ws, counters)
-    return sc
+    """Workspace of the stream-K tcgen05 product, one per device, made at the first call."""
+    ws = _MID_SCRATCH.get(device)
+    if ws is None:
+        ws = _MID_SCRATCH[device] = torch.empty(int(bf16lib().rs_mid_gemm_workspace_floats()), dtype=torch.float32,
+                                                device=device)
+    return ws
 
 
 def mid_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
@@ -414,15 +413,15 @@ def mid_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_ro
     (rows of the weight fill the 128-row side of the MMA) and the work dealt to the SMs in equal shares of k
     (csrc/mid_gemm_tcgen05.cu)."""
     N, K = _check_product(a, weight, out, n_rows, swiglu)
-    if n_rows > MID_MAX_ROWS or not tensor_core_shape_ok(a, weight) or N > 128 * (1 << 16):
+    if n_rows > MID_MAX_ROWS or not tensor_core_shape_ok(a, weight):
         raise KernelError(f"mid_gemm_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
                           f"{tuple(weight.shape)} {weight.dtype}: at most {MID_MAX_ROWS} rows, bfloat16, 16-byte aligned")
     if status is None:
         status = _default_status(a.device)
-    ws, counters = _mid_scratch(a.device)
+    ws = _mid_scratch(a.device)
     _check(bf16lib().rs_mid_gemm_bf16(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
                                       out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), _ptr(ws),
-                                      _ptr(counters), max_ctas, _ptr(status), _stream()), "mid_gemm_bf16")
+                                      max_ctas, _ptr(status), _stream()), "mid_gemm_bf16", 2)
 
 
 _STATUS = {}
