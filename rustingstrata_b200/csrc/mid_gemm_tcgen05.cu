@@ -28,6 +28,7 @@
 // Reference counterpart: gemvn_bf16 / gemm_bf16 (src/cuda/kernels.cu:826-853,1062-1231); the reference has no
 // kernel of its own for this range of rows.
 #include "tma_helpers.cuh"
+#include "stream_k_partials.cuh"
 
 namespace {
 constexpr int TILE_N = 128;                // rows of W per unit = M of the MMA
@@ -86,12 +87,8 @@ __device__ __forceinline__ uint32_t make_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// first unit of CTA c when U units are dealt to G CTAs as evenly as possible
-__device__ __forceinline__ int first_unit(int c, int U, int G) { return c * (U / G) + (c < U % G ? c : U % G); }
-__device__ __forceinline__ int cta_of_unit(int u, int U, int G) {
-    const int base = U / G, rem = U % G;
-    return u < rem * (base + 1) ? u / (base + 1) : rem + (u - rem * (base + 1)) / base;
-}
+using rs_streamk::first_unit;
+using rs_streamk::cta_of_unit;
 
 // one finished value of C: row m of A, row n of W (all 32 lanes of a warp call this together, n consecutive)
 template <int EPI>
@@ -381,8 +378,17 @@ __global__ void __launch_bounds__(256) mid_reduce_kernel(const MidParams p, int 
     }
 }
 
+// CTAs of the product: one per SM, at most max_ctas (if positive), at most one per unit of work
+long grid_of(int N, int K, int max_ctas) {
+    const long U = (long)((N + TILE_N - 1) / TILE_N) * ((K + TILE_K - 1) / TILE_K);
+    long grid = rs_tma::sm_count();
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    return grid > U ? U : grid;
+}
+int padded_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
 template <int MP, int EPI>
-int launch(const CUtensorMap& mw, const CUtensorMap& ma, MidParams p, int max_ctas, cudaStream_t s) {
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, MidParams p, int max_ctas, bool defer, cudaStream_t s) {
     constexpr int SB = W_BYTES + MP * TILE_K * 2;
     constexpr int stages = SMEM_BUDGET / SB;
     constexpr int smem = stages * SB + 1024 + 8 * (2 * stages + 5) + 64;
@@ -394,22 +400,19 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, MidParams p, int max_ct
         attr_set = true;
     }
     p.stages = stages;
-    const long U = (long)((p.N + TILE_N - 1) / TILE_N) * ((p.K + TILE_K - 1) / TILE_K);
-    long grid = rs_tma::sm_count();
-    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    if (grid > U) grid = U;
+    const long grid = grid_of(p.N, p.K, max_ctas);
     int rc = rs_launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), (size_t)smem, s, mw, ma, p);
-    if (rc != 0 || grid < 2) return rc;
+    if (rc != 0 || grid < 2 || defer) return rc;
     return rs_launch_pdl(mid_reduce_kernel<MP, EPI>, dim3((unsigned)(grid - 1)), dim3(256), 0, s, p, (int)grid);
 }
 
 template <int MP>
-int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const MidParams& p, int max_ctas, cudaStream_t s) {
+int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const MidParams& p, int max_ctas, bool defer, cudaStream_t s) {
     switch (epi) {
-        case EPI_STORE_BF16: return launch<MP, EPI_STORE_BF16>(mw, ma, p, max_ctas, s);
-        case EPI_STORE_F32: return launch<MP, EPI_STORE_F32>(mw, ma, p, max_ctas, s);
-        case EPI_ADD_F32: return launch<MP, EPI_ADD_F32>(mw, ma, p, max_ctas, s);
-        case EPI_SWIGLU_BF16: return launch<MP, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, s);
+        case EPI_STORE_BF16: return launch<MP, EPI_STORE_BF16>(mw, ma, p, max_ctas, defer, s);
+        case EPI_STORE_F32: return launch<MP, EPI_STORE_F32>(mw, ma, p, max_ctas, defer, s);
+        case EPI_ADD_F32: return launch<MP, EPI_ADD_F32>(mw, ma, p, max_ctas, defer, s);
+        case EPI_SWIGLU_BF16: return launch<MP, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, defer, s);
     }
     return (int)cudaErrorInvalidValue;
 }
@@ -422,14 +425,18 @@ RS_EXPORT long rs_mid_gemm_workspace_floats() { return (long)rs_tma::sm_count() 
 
 // C[M, N] (=|+=) A[M, K] . W[N, K]^T for M <= 128, bf16 inputs; same epilogue codes as rs_gemm_bf16_tc.  a_rows is the
 // row capacity of A's buffer.  workspace as sized above.  Launches that share a workspace must not overlap on the GPU.
+// defer != 0 (f32 += epilogue only): the tiles that several CTAs share stay unfinished in the workspace until
+// rs_mid_finish or rs_mid_finish_rmsnorm is launched with the same C, shape, workspace and max_ctas; no other product
+// of this kind may run in between.
 RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void* W, long ldw, void* C, long ldc, int M, int N,
-                               int K, int epi, float* workspace, int max_ctas, int* status, void* stream) {
+                               int K, int epi, float* workspace, int max_ctas, int defer, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 128 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
         workspace == nullptr)
         return (int)cudaErrorInvalidValue;
     if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
-    const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+    if (defer && epi != EPI_ADD_F32) return (int)cudaErrorInvalidValue;
+    const int mp = padded_rows(M);
     CUtensorMap mw, ma;
     int rc = rs_tma::get_map(W, N, K, ldw, TILE_N, &mw);
     if (rc) return rc;
@@ -441,8 +448,35 @@ RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void*
     const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (mp == 16) return launch_epi<16>(epi, mw, ma, p, max_ctas, s);
-    if (mp == 32) return launch_epi<32>(epi, mw, ma, p, max_ctas, s);
-    if (mp == 64) return launch_epi<64>(epi, mw, ma, p, max_ctas, s);
-    return launch_epi<128>(epi, mw, ma, p, max_ctas, s);
+    if (mp == 16) return launch_epi<16>(epi, mw, ma, p, max_ctas, defer != 0, s);
+    if (mp == 32) return launch_epi<32>(epi, mw, ma, p, max_ctas, defer != 0, s);
+    if (mp == 64) return launch_epi<64>(epi, mw, ma, p, max_ctas, defer != 0, s);
+    return launch_epi<128>(epi, mw, ma, p, max_ctas, defer != 0, s);
+}
+
+// Finishes a deferred product: C += the partials of the shared tiles.
+RS_EXPORT int rs_mid_finish(void* C, long ldc, int M, int N, int K, float* workspace, int max_ctas, void* stream) {
+    if (M <= 0 || M > 128 || N <= 0 || K <= 0 || workspace == nullptr) return (int)cudaErrorInvalidValue;
+    MidParams p;
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.status = nullptr;
+    p.vec_ok = (((long)C & 15) == 0 && (ldc * 4) % 16 == 0) ? 1 : 0;
+    const long grid = grid_of(N, K, max_ctas);
+    if (grid < 2) return 0;
+    const dim3 g((unsigned)(grid - 1)), b(256);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (padded_rows(M)) {
+        case 16: return rs_launch_pdl(mid_reduce_kernel<16, EPI_ADD_F32>, g, b, 0, s, p, (int)grid);
+        case 32: return rs_launch_pdl(mid_reduce_kernel<32, EPI_ADD_F32>, g, b, 0, s, p, (int)grid);
+        case 64: return rs_launch_pdl(mid_reduce_kernel<64, EPI_ADD_F32>, g, b, 0, s, p, (int)grid);
+        default: return rs_launch_pdl(mid_reduce_kernel<128, EPI_ADD_F32>, g, b, 0, s, p, (int)grid);
+    }
+}
+
+// Finishes a deferred product and writes out[m] = RMSNorm(C[m]) * w as bfloat16, in one kernel (one CTA per row).
+RS_EXPORT int rs_mid_finish_rmsnorm(void* C, long ldc, int M, int N, int K, float* workspace, int max_ctas, const void* w,
+                                    int w_dt, float eps, void* out, long out_stride, void* stream) {
+    if (M <= 0 || M > 128) return (int)cudaErrorInvalidValue;
+    const rs_streamk::Layout L = {TILE_N, TILE_K, padded_rows(M)};
+    return rs_streamk::launch_finish_rmsnorm(C, ldc, M, N, K, workspace, (int)grid_of(N, K, max_ctas), L, w, w_dt, eps, out, out_stride,
+                                             (cudaStream_t)stream);
 }

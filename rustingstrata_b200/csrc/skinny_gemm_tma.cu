@@ -28,16 +28,15 @@
 // cores, each weight read once for up to 4 inputs.
 #include "tma_helpers.cuh"
 #include "mma_helpers.cuh"
-#include "skinny_partials.cuh"
+#include "stream_k_partials.cuh"
 
 namespace {
-using rs_skinny::TILE_N;                   // rows of W per unit
-using rs_skinny::TILE_K;                   // k per unit
-using rs_skinny::first_unit;
-using rs_skinny::cta_of_unit;
+using rs_streamk::first_unit;
+using rs_streamk::cta_of_unit;
+constexpr int TILE_N = 64;                 // rows of W per unit
 constexpr int BOX_K = 64;                  // k per TMA box (one 128-byte swizzle row)
 constexpr int BOXES = 2;                   // boxes per unit
-static_assert(TILE_K == BOX_K * BOXES, "a unit is two boxes deep");
+constexpr int TILE_K = BOX_K * BOXES;      // k per unit
 constexpr int W_BOX_BYTES = TILE_N * BOX_K * 2;
 constexpr int W_BYTES = W_BOX_BYTES * BOXES;
 constexpr int CONSUMER_WARPS = 4;
@@ -293,89 +292,6 @@ __global__ void __launch_bounds__(CONSUMER_WARPS * 32) skinny_reduce_kernel(cons
     store_tile<NT, EPI>(p, acc, tile, warp, g, t);
 }
 
-// RMSNorm of the rows of C straight after a product with the f32 += epilogue whose shared tiles were left unfinished
-// (`defer`): one CTA per row does what skinny_reduce_kernel<1, EPI_ADD_F32> and the row norm would do one after the
-// other, with the same arithmetic in the same order (partials from zero in CTA order, then added to C; the sum of
-// squares by thread-strided float4 partials and a tree), so the bits are those of the two kernels.  It saves a kernel
-// boundary and a round trip to memory between two small dependent kernels.  Rows of up to 512 * 4 * VPT values, M <= 8.
-template <int VPT>
-__global__ void __launch_bounds__(512) skinny_finish_rmsnorm_kernel(const SkinnyParams p, int G, const void* __restrict__ w, int w_dt,
-                                                                    float eps, __nv_bfloat16* __restrict__ out, long out_stride) {
-    constexpr int MAX_TILES = 512 * 4 * VPT / TILE_N;
-    __shared__ float scratch[33];
-    __shared__ int2 sharers[MAX_TILES];                        // per row tile: first and last CTA of the product that worked on it
-    pdl_launch_dependents();
-    // Nothing before the wait reads what the product wrote: who shared which tile follows from the shape, and the
-    // norm's weights are the model's.  So this part runs while the product is still at work.
-    const int m = blockIdx.x;
-    const int KB = (p.K + TILE_K - 1) / TILE_K;
-    const int n_tiles = (p.N + TILE_N - 1) / TILE_N;
-    const int U = n_tiles * KB;
-    const int per_cta = U / G, extra = U % G;                  // the first `extra` CTAs take one unit more
-    for (int tile = threadIdx.x; tile < n_tiles; tile += 512)
-        sharers[tile] = rs_skinny::sharers_of_tile(tile, KB, U, G);
-    const int n4 = p.N >> 2;
-    float wv[VPT][4];
-#pragma unroll
-    for (int u = 0; u < VPT; ++u) {
-        const int idx = threadIdx.x + u * 512;
-        wv[u][0] = wv[u][1] = wv[u][2] = wv[u][3] = 0.f;
-        if (idx < n4) {
-            if (w_dt == RS_F32) {
-                const float4 f = reinterpret_cast<const float4*>(w)[idx];
-                wv[u][0] = f.x; wv[u][1] = f.y; wv[u][2] = f.z; wv[u][3] = f.w;
-            } else {
-                const uint2 h = reinterpret_cast<const uint2*>(w)[idx];
-                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&h.x), b = *reinterpret_cast<const __nv_bfloat162*>(&h.y);
-                wv[u][0] = __low2float(a); wv[u][1] = __high2float(a); wv[u][2] = __low2float(b); wv[u][3] = __high2float(b);
-            }
-        }
-    }
-    __syncthreads();
-    pdl_wait();
-    float* xr = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc;
-    float4 v[VPT];
-    rs_skinny::OwedBatch part[VPT];
-    int2 sh[VPT];
-    // every load first: the row's values and the first four contributors' partials of each of this thread's columns
-#pragma unroll
-    for (int u = 0; u < VPT; ++u) {
-        const int idx = threadIdx.x + u * 512;
-        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        sh[u] = make_int2(0, 0);
-        if (idx < n4) {
-            v[u] = ld_dep(reinterpret_cast<const float4*>(xr) + idx);
-            sh[u] = sharers[idx * 4 / TILE_N];
-            if (sh[u].x != sh[u].y) rs_skinny::owed_begin4(part[u], p.workspace, m, idx * 4, KB, per_cta, extra, sh[u].x, sh[u].y);
-        }
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int u = 0; u < VPT; ++u) {
-        const int idx = threadIdx.x + u * 512;
-        if (idx < n4 && sh[u].x != sh[u].y) {
-            const float4 acc = rs_skinny::owed_end4(part[u], p.workspace, m, idx * 4, KB, per_cta, extra, sh[u].x, sh[u].y);
-            v[u].x += acc.x; v[u].y += acc.y; v[u].z += acc.z; v[u].w += acc.w;
-            reinterpret_cast<float4*>(xr)[idx] = v[u];
-        }
-        ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss); ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
-    }
-    ss = block_sum(ss, scratch);
-    const float sc = 1.0f / sqrtf(ss / (float)p.N + eps);
-    __nv_bfloat16* o = out + (size_t)m * out_stride;
-#pragma unroll
-    for (int u = 0; u < VPT; ++u) {
-        const int idx = threadIdx.x + u * 512;
-        if (idx < n4) {
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * sc * wv[u][0], v[u].y * sc * wv[u][1]);
-            const __nv_bfloat162 hi2 = __floats2bfloat162_rn(v[u].z * sc * wv[u][2], v[u].w * sc * wv[u][3]);
-            uint2 pk;
-            pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi2);
-            reinterpret_cast<uint2*>(o)[idx] = pk;
-        }
-    }
-}
-
 template <int NT> constexpr int stage_bytes() { return W_BYTES + 8 * NT * TILE_K * 2; }
 
 // CTAs of the product: one per SM, at most max_ctas (if positive), at most one per unit of work
@@ -466,26 +382,121 @@ RS_EXPORT int rs_skinny_finish(void* C, long ldc, int M, int N, int K, float* wo
                          (cudaStream_t)stream, p, (int)grid);
 }
 
-// Whether rs_skinny_finish_rmsnorm takes a row of this width with these pitches and pointers.
-RS_EXPORT int rs_skinny_finish_rmsnorm_supported(const void* C, long ldc, int N, const void* w, const void* out, long out_stride) {
+namespace rs_streamk {
+// RMSNorm of the rows of C straight after a product with the f32 += epilogue whose shared tiles were left unfinished:
+// one CTA per row does what the product's small finishing kernel and the row norm would do one after the other, with
+// the same arithmetic in the same order (partials in CTA order, then added to C; the sum of squares by thread-strided
+// float4 partials and a tree), so the bits are those of the two kernels.  It saves a kernel boundary and a round trip
+// to memory between two small dependent kernels.  Rows of up to 512 * 4 * VPT values.
+// C[M, N] float32 with row pitch ldc; workspace, N, K, G, L: the product's; w: the norm's weights (float32 or bfloat16).
+template <int VPT>
+__global__ void __launch_bounds__(512) finish_rmsnorm_kernel(float* C, long ldc, int N, int K, const float* workspace, int G,
+                                                             const Layout L, const void* __restrict__ w, int w_dt, float eps,
+                                                             __nv_bfloat16* __restrict__ out, long out_stride) {
+    constexpr int MAX_TILES = 512 * 4 * VPT / 64;              // tiles are at least 64 wide
+    __shared__ float scratch[33];
+    __shared__ int2 sharers[MAX_TILES];                        // per row tile: first and last CTA of the product that worked on it
+    pdl_launch_dependents();
+    // Nothing before the wait reads what the product wrote: who shared which tile follows from the shape, and the
+    // norm's weights are the model's.  So this part runs while the product is still at work.
+    const int m = blockIdx.x;
+    const int KB = (K + L.tile_k - 1) / L.tile_k;
+    const int n_tiles = (N + L.tile_n - 1) / L.tile_n;
+    const int U = n_tiles * KB;
+    const int per_cta = U / G, extra = U % G;                  // the first `extra` CTAs take one unit more
+    for (int tile = threadIdx.x; tile < n_tiles; tile += 512) sharers[tile] = sharers_of_tile(tile, KB, U, G);
+    const int n4 = N >> 2;
+    float wv[VPT][4];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        wv[u][0] = wv[u][1] = wv[u][2] = wv[u][3] = 0.f;
+        if (idx < n4) {
+            if (w_dt == RS_F32) {
+                const float4 f = reinterpret_cast<const float4*>(w)[idx];
+                wv[u][0] = f.x; wv[u][1] = f.y; wv[u][2] = f.z; wv[u][3] = f.w;
+            } else {
+                const uint2 h = reinterpret_cast<const uint2*>(w)[idx];
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&h.x), b = *reinterpret_cast<const __nv_bfloat162*>(&h.y);
+                wv[u][0] = __low2float(a); wv[u][1] = __high2float(a); wv[u][2] = __low2float(b); wv[u][3] = __high2float(b);
+            }
+        }
+    }
+    __syncthreads();
+    pdl_wait();
+    float* xr = C + (size_t)m * ldc;
+    float4 v[VPT];
+    OwedBatch part[VPT];
+    int2 sh[VPT];
+    // every load first: the row's values and the first four contributors' partials of each of this thread's columns
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sh[u] = make_int2(0, 0);
+        if (idx < n4) {
+            v[u] = ld_dep(reinterpret_cast<const float4*>(xr) + idx);
+            sh[u] = sharers[idx * 4 / L.tile_n];
+            if (sh[u].x != sh[u].y) owed_begin4(part[u], workspace, L, m, idx * 4, KB, per_cta, extra, sh[u].x, sh[u].y);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        if (idx < n4 && sh[u].x != sh[u].y) {
+            const float4 acc = owed_end4(part[u], workspace, L, m, idx * 4, KB, per_cta, extra, sh[u].x, sh[u].y);
+            v[u].x += acc.x; v[u].y += acc.y; v[u].z += acc.z; v[u].w += acc.w;
+            reinterpret_cast<float4*>(xr)[idx] = v[u];
+        }
+        ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss); ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float sc = 1.0f / sqrtf(ss / (float)N + eps);
+    __nv_bfloat16* o = out + (size_t)m * out_stride;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * 512;
+        if (idx < n4) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * sc * wv[u][0], v[u].y * sc * wv[u][1]);
+            const __nv_bfloat162 hi2 = __floats2bfloat162_rn(v[u].z * sc * wv[u][2], v[u].w * sc * wv[u][3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi2);
+            reinterpret_cast<uint2*>(o)[idx] = pk;
+        }
+    }
+}
+
+bool finish_rmsnorm_supported(const void* C, long ldc, int N, const void* w, const void* out, long out_stride) {
     return N > 0 && N % 4 == 0 && N <= 512 * 4 * 4 && ldc % 4 == 0 && out_stride % 4 == 0 && ((long)C & 15) == 0 &&
            ((long)out & 7) == 0 && ((long)w & 15) == 0;
+}
+
+int launch_finish_rmsnorm(void* C, long ldc, int M, int N, int K, const float* workspace, int G, Layout L, const void* w,
+                                 int w_dt, float eps, void* out, long out_stride, cudaStream_t s) {
+    if (M <= 0 || M > L.rows_padded || K <= 0 || workspace == nullptr || G < 1 || (w_dt != RS_F32 && w_dt != RS_BF16) ||
+        L.tile_n < 64 || L.tile_n % 4 || !finish_rmsnorm_supported(C, ldc, N, w, out, out_stride))
+        return (int)cudaErrorInvalidValue;
+    float* c = (float*)C;
+    auto* o = (__nv_bfloat16*)out;
+    if (N <= 512 * 4) return rs_launch_pdl(finish_rmsnorm_kernel<1>, dim3(M), dim3(512), 0, s, c, ldc, N, K, workspace, G, L, w, w_dt, eps, o, out_stride);
+    if (N <= 512 * 8) return rs_launch_pdl(finish_rmsnorm_kernel<2>, dim3(M), dim3(512), 0, s, c, ldc, N, K, workspace, G, L, w, w_dt, eps, o, out_stride);
+    return rs_launch_pdl(finish_rmsnorm_kernel<4>, dim3(M), dim3(512), 0, s, c, ldc, N, K, workspace, G, L, w, w_dt, eps, o, out_stride);
+}
+}  // namespace rs_streamk
+
+// Whether rs_skinny_finish_rmsnorm takes a row of this width with these pitches and pointers.
+RS_EXPORT int rs_skinny_finish_rmsnorm_supported(const void* C, long ldc, int N, const void* w, const void* out, long out_stride) {
+    return rs_streamk::finish_rmsnorm_supported(C, ldc, N, w, out, out_stride) ? 1 : 0;
 }
 
 // Finishes a deferred product and writes out[m] = RMSNorm(C[m]) * w as bfloat16, in one kernel.
 RS_EXPORT int rs_skinny_finish_rmsnorm(void* C, long ldc, int M, int N, int K, float* workspace, int max_ctas, const void* w,
                                        int w_dt, float eps, void* out, long out_stride, void* stream) {
-    if (M <= 0 || M > 8 || K <= 0 || workspace == nullptr || (w_dt != RS_F32 && w_dt != RS_BF16) ||
-        !rs_skinny_finish_rmsnorm_supported(C, ldc, N, w, out, out_stride))
-        return (int)cudaErrorInvalidValue;
-    SkinnyParams p;
-    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace; p.status = nullptr;
-    const int G = (int)grid_of(N, K, max_ctas);
-    auto* o = (__nv_bfloat16*)out;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (N <= 512 * 4) return rs_launch_pdl(skinny_finish_rmsnorm_kernel<1>, dim3(M), dim3(512), 0, s, p, G, w, w_dt, eps, o, out_stride);
-    if (N <= 512 * 8) return rs_launch_pdl(skinny_finish_rmsnorm_kernel<2>, dim3(M), dim3(512), 0, s, p, G, w, w_dt, eps, o, out_stride);
-    return rs_launch_pdl(skinny_finish_rmsnorm_kernel<4>, dim3(M), dim3(512), 0, s, p, G, w, w_dt, eps, o, out_stride);
+    if (M > 8) return (int)cudaErrorInvalidValue;
+    const rs_streamk::Layout L = {TILE_N, TILE_K, 8};
+    return rs_streamk::launch_finish_rmsnorm(C, ldc, M, N, K, workspace, (int)grid_of(N, K, max_ctas), L, w, w_dt, eps, out, out_stride,
+                                             (cudaStream_t)stream);
 }
 
 // Turns programmatic dependent launch on or off for every kernel of this library (default on).

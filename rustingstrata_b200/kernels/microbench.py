@@ -57,14 +57,15 @@ def bench_linear(kind: str, M: int, N: int, K: int, epilogue: str, bn: int, iter
         out, kw = torch.zeros(rows, N, device=DEV), dict(accumulate=True)
     else:
         out, kw = torch.zeros(rows, N // 2, device=DEV, dtype=torch.bfloat16), dict(swiglu=True)
-    if kind == "skinny" and then_norm:
+    if kind in ("skinny", "mid") and then_norm:
         # the product into the residual stream and the row norm behind it: as two kernels and a small one between
         # them ("apart"), or with the norm adding up the product's shared tiles ("owed")
         nw = torch.ones(N, device=DEV, dtype=torch.bfloat16)
         h = torch.empty(rows, N, device=DEV, dtype=torch.bfloat16)
 
         def both(i):
-            owed = ops.skinny_gemm_bf16(a, ws[i], out, M, accumulate=True, defer=then_norm == "owed")
+            product = ops.skinny_gemm_bf16 if kind == "skinny" else ops.mid_gemm_bf16
+            owed = product(a, ws[i], out, M, accumulate=True, defer=then_norm == "owed")
             ops.rmsnorm(out, nw, 1e-6, h, n_rows=M, pending=owed)
         us = timed(both, nb, iters, once)
         epilogue = f"add then norm ({then_norm})"
@@ -137,7 +138,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--force", default="", help="prefill_attention: tc | mma | simt instead of the default choice")
     ap.add_argument("--then-norm", default="", choices=["", "apart", "owed"],
-                    help="skinny with --epilogue add: time the product together with the RMSNorm of its rows")
+                    help="skinny or mid with --epilogue add: time the product together with the RMSNorm of its rows")
     ap.add_argument("--once", action="store_true", help="a few plain launches, no graph and no timing (for profilers)")
     a = ap.parse_args(argv)
     if a.kernel in ("skinny", "mid", "gemm"):

@@ -142,10 +142,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                 and x.dtype == torch.float32 and out.dtype == torch.bfloat16 and weight.is_contiguous()
                 and weight.dtype in (torch.float32, torch.bfloat16) and nr <= out.shape[0] and x.stride(1) == 1 and out.stride(1) == 1
                 and lib.rs_skinny_finish_rmsnorm_supported(_ptr(x), x.stride(0), pending.N, _ptr(weight), _ptr(out), out.stride(0))):
-            pending.done = True
-            _check(lib.rs_skinny_finish_rmsnorm(_ptr(x), x.stride(0), nr, pending.N, pending.K, _ptr(pending.workspace),
-                                                pending.max_ctas, _ptr(weight), dtype_code(weight), float(eps), _ptr(out),
-                                                out.stride(0), _stream()), "skinny_finish_rmsnorm")
+            pending.finish_with_rmsnorm(weight, eps, out)
             return
         pending.finish()
     _rows_contiguous(x, "rmsnorm x")
@@ -260,7 +257,9 @@ def bf16lib():
         lib.rs_skinny_finish_rmsnorm.argtypes = [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
                                                  c_float, c_void_p, c_long, c_void_p]
         lib.rs_mid_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
-                                         c_int, c_void_p, c_int, c_void_p, c_void_p]
+                                         c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_mid_finish.argtypes = lib.rs_skinny_finish.argtypes
+        lib.rs_mid_finish_rmsnorm.argtypes = lib.rs_skinny_finish_rmsnorm.argtypes
         lib.rs_mid_gemm_workspace_floats.restype = c_long
         lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -356,21 +355,33 @@ class PendingSum:
     """A product into the float32 residual stream whose last step is still owed: the partial sums of the weight tiles
     that several CTAs shared lie in the product's workspace and have not been added to ``out`` yet.  Whoever reads
     ``out`` next either takes the object along (``rmsnorm(..., pending=...)`` adds the partials while it reads the
-    rows) or calls :meth:`finish` first.  No other product may run in between: it would overwrite the workspace."""
+    rows) or calls :meth:`finish` first.  No other product of the same kind may run in between: it would overwrite the
+    workspace.  ``kind``: "skinny" (up to 8 rows) or "mid" (the stream-K tcgen05 product, up to 128 rows)."""
 
-    def __init__(self, out: torch.Tensor, n_rows: int, N: int, K: int, workspace: torch.Tensor, max_ctas: int):
-        self.out, self.n_rows, self.N, self.K, self.workspace, self.max_ctas = out, n_rows, N, K, workspace, max_ctas
+    def __init__(self, kind: str, out: torch.Tensor, n_rows: int, N: int, K: int, workspace: torch.Tensor, max_ctas: int):
+        self.kind, self.out, self.n_rows, self.N, self.K = kind, out, n_rows, N, K
+        self.workspace, self.max_ctas = workspace, max_ctas
         self.done = False
 
     def finish(self) -> None:
         """out += the partial sums (the small kernel that the product would have launched itself)."""
         if not self.done:
             self.done = True
-            _check(bf16lib().rs_skinny_finish(_ptr(self.out), self.out.stride(0), self.n_rows, self.N, self.K,
-                                              _ptr(self.workspace), self.max_ctas, _stream()), "skinny_finish")
+            fn = bf16lib().rs_skinny_finish if self.kind == "skinny" else bf16lib().rs_mid_finish
+            _check(fn(_ptr(self.out), self.out.stride(0), self.n_rows, self.N, self.K, _ptr(self.workspace), self.max_ctas,
+                      _stream()), self.kind + "_finish")
+
+    def finish_with_rmsnorm(self, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        """The same and out[r] = RMSNorm(self.out[r]) * weight, in one kernel."""
+        self.done = True
+        fn = bf16lib().rs_skinny_finish_rmsnorm if self.kind == "skinny" else bf16lib().rs_mid_finish_rmsnorm
+        _check(fn(_ptr(self.out), self.out.stride(0), self.n_rows, self.N, self.K, _ptr(self.workspace), self.max_ctas,
+                  _ptr(weight), dtype_code(weight), float(eps), _ptr(out), out.stride(0), _stream()),
+               self.kind + "_finish_rmsnorm")
 
 
 SKINNY_DEFER_ROWS = 8    # the deferred form exists for the thread layout of up to 8 rows
+DEFER_SUMS = True        # whether linear() lets a product leave its last sum to the next reader when the caller allows it
 
 
 def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
@@ -391,7 +402,7 @@ def skinny_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n
     _check(bf16lib().rs_skinny_gemm_bf16(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
                                          out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), _ptr(ws),
                                          max_ctas, 1 if defer else 0, _ptr(status), _stream()), "skinny_gemm_bf16", 1 if defer else 2)
-    return PendingSum(out, n_rows, N, K, ws, max_ctas) if defer else None
+    return PendingSum("skinny", out, n_rows, N, K, ws, max_ctas) if defer else None
 
 
 MID_MAX_ROWS = 128       # what the stream-K tcgen05 kernel takes; the engine uses it from SKINNY_ROWS + 1 rows up to here
@@ -408,11 +419,15 @@ def _mid_scratch(device):
 
 
 def mid_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
-                  swiglu: bool = False, status: Optional[torch.Tensor] = None, max_ctas: int = 0) -> None:
+                  swiglu: bool = False, status: Optional[torch.Tensor] = None, max_ctas: int = 0,
+                  defer: bool = False) -> Optional[PendingSum]:
     """out[:n_rows] (=|+=) a[:n_rows] @ weight.T for n_rows <= 128 on the tensor cores with the operands swapped
     (rows of the weight fill the 128-row side of the MMA) and the work dealt to the SMs in equal shares of k
-    (csrc/mid_gemm_tcgen05.cu)."""
+    (csrc/mid_gemm_tcgen05.cu).  With ``defer`` (float32 += only) the kernel that adds up the shared tiles is not
+    launched and a :class:`PendingSum` is returned instead."""
     N, K = _check_product(a, weight, out, n_rows, swiglu)
+    if defer and not (accumulate and out.dtype == torch.float32):
+        raise KernelError("mid_gemm_bf16 defers only a float32 +=")
     if n_rows > MID_MAX_ROWS or not tensor_core_shape_ok(a, weight):
         raise KernelError(f"mid_gemm_bf16 refuses {n_rows} rows of a {tuple(a.shape)} {a.dtype} x weight "
                           f"{tuple(weight.shape)} {weight.dtype}: at most {MID_MAX_ROWS} rows, bfloat16, 16-byte aligned")
@@ -421,7 +436,9 @@ def mid_gemm_bf16(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_ro
     ws = _mid_scratch(a.device)
     _check(bf16lib().rs_mid_gemm_bf16(_ptr(a), a.stride(0), a.shape[0], _ptr(weight), weight.stride(0), _ptr(out),
                                       out.stride(0), n_rows, N, K, _epilogue_code(out, accumulate, swiglu), _ptr(ws),
-                                      max_ctas, _ptr(status), _stream()), "mid_gemm_bf16", 2)
+                                      max_ctas, 1 if defer else 0, _ptr(status), _stream()), "mid_gemm_bf16",
+           1 if defer else 2)
+    return PendingSum("mid", out, n_rows, N, K, ws, max_ctas) if defer else None
 
 
 _STATUS = {}
@@ -444,10 +461,11 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int
     on to the next reader of ``out`` if the kernel that runs can leave one (else None comes back and ``out`` is whole)."""
     if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
         if n_rows <= SKINNY_ROWS and weight.numel() < SKINNY_MAX_WEIGHT:
-            defer = may_defer and accumulate and out.dtype == torch.float32 and n_rows <= SKINNY_DEFER_ROWS
+            defer = may_defer and DEFER_SUMS and accumulate and out.dtype == torch.float32 and n_rows <= SKINNY_DEFER_ROWS
             return skinny_gemm_bf16(a, weight, out, n_rows, accumulate, status=status, defer=defer)
         elif n_rows <= MID_MAX_ROWS:
-            mid_gemm_bf16(a, weight, out, n_rows, accumulate, status=status)
+            return mid_gemm_bf16(a, weight, out, n_rows, accumulate, status=status,
+                                 defer=may_defer and DEFER_SUMS and accumulate and out.dtype == torch.float32)
         else:
             gemm_bf16_tc(a, weight, out, n_rows, accumulate, status=status)
     else:

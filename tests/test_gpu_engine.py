@@ -234,9 +234,9 @@ def test_steps_launched_ahead_change_nothing(tiny_models, dtype):
 
 
 def test_sums_left_to_the_next_norm_change_no_bit(tiny_models, monkeypatch):
-    """In small decode steps the output and down projections leave the adding-up of their shared tiles to the norm
-    that reads the residual stream next.  Fewer kernels run, and the tokens and logits are the same bits as with
-    every product finishing itself."""
+    """In steps of up to 128 tokens the output and down projections leave the adding-up of their shared tiles to the
+    norm that reads the residual stream next.  Fewer kernels run, and the tokens are the same as with every product
+    finishing itself."""
     from rustingstrata_b200.kernels import ops
     cfg, w = P.read_model(tiny_models["D"])
     prompts = [random_tokens(cfg["vocab_size"], n, 70 + n) for n in (3, 12, 20)]
@@ -250,7 +250,7 @@ def test_sums_left_to_the_next_norm_change_no_bit(tiny_models, monkeypatch):
         return outs, n
 
     with_owed, n_owed = run()
-    monkeypatch.setattr(ops, "SKINNY_DEFER_ROWS", 0)
+    monkeypatch.setattr(ops, "DEFER_SUMS", False)
     without, n_plain = run()
     assert with_owed == without
     assert n_owed < n_plain

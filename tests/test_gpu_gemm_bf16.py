@@ -183,6 +183,32 @@ def test_product_that_leaves_its_last_sum_to_the_norm(M, max_ctas, N, K, w_dtype
     assert torch.equal(x1, x3) and st.item() == 0
 
 
+@pytest.mark.parametrize("M", [1, 9, 16, 33, 64, 100, 128])
+@pytest.mark.parametrize("max_ctas", [0, 3, 50])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (4096, 12288), (1000, 1000), (100, 72), (5120, 640), (128, 2048)])
+def test_stream_k_tcgen05_product_that_leaves_its_last_sum_to_the_norm(M, max_ctas, N, K):
+    """The same for the product of up to 128 rows: its shared tiles (128 rows of W, partials of 16 to 128 rows) are
+    added by the norm, one CTA per row; x and the normed rows are the bits of product, finishing kernel and norm in turn."""
+    o = ops()
+    a, w = make(M, N, K, cap=M + 2, seed=M + N)
+    base = torch.randn(M + 2, N, device=DEV)
+    nw = (1 + 0.1 * torch.randn(N, device=DEV)).to(torch.bfloat16)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x1, x2, x3 = base.clone(), base.clone(), base.clone()
+    h1 = torch.full((M + 2, N), 3.0, device=DEV, dtype=torch.bfloat16)
+    h2 = h1.clone()
+    assert o.mid_gemm_bf16(a, w, x1, M, accumulate=True, status=st, max_ctas=max_ctas) is None
+    o.rmsnorm(x1, nw, 1e-6, h1, n_rows=M)
+    owed = o.mid_gemm_bf16(a, w, x2, M, accumulate=True, status=st, max_ctas=max_ctas, defer=True)
+    o.rmsnorm(x2, nw, 1e-6, h2, n_rows=M, pending=owed)
+    assert owed.done and torch.equal(x1, x2) and torch.equal(h1, h2) and torch.all(h2[M:] == 3.0)
+    owed = o.mid_gemm_bf16(a, w, x3, M, accumulate=True, status=st, max_ctas=max_ctas, defer=True)
+    owed.finish()
+    assert torch.equal(x1, x3) and torch.equal(x3[M:], base[M:]) and st.item() == 0
+    with pytest.raises(o.KernelError):
+        o.mid_gemm_bf16(a, w, torch.zeros(M, N, device=DEV, dtype=torch.bfloat16), M, defer=True)
+
+
 def test_owed_sum_is_finished_first_when_the_norm_cannot_take_it():
     """Other rows than the product's (a gather), another buffer, a float32 output: the sum is added by its own kernel
     and the plain norm runs."""
