@@ -53,6 +53,7 @@ struct DecodeParams {
     float scale_log2;                  // scale * log2(e)
     const int* split_start;
     float* partial;                    // [slot][n_q][hd + 2]: acc, max (log2 units), sum
+    int partial_slots;                 // slots `partial` holds; a slot beyond it is flagged and not written
     int* status;
     int n_work, max_splits, total;     // total = n_work * n_kv * max_splits items, dead ones included
     int groups, depth;                 // consumer groups and stages per group
@@ -374,7 +375,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
                 const size_t slot = (size_t)__ldg(p.split_start + it.w) + it.split_local;
                 float* dst = p.partial + (slot * p.n_q + (size_t)it.kvh * p.group) * (HD + 2);
                 auto lds = [&](uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; };
-                for (int i = gw * 32 + lane; i < p.group * (HD + 2); i += GROUP_WARPS * 32) {
+                const bool in_workspace = slot < (size_t)p.partial_slots;
+                if (!in_workspace && gw == 0 && lane == 0) atomicOr(p.status, RS_STATUS_BAD_PLAN);
+                for (int i = gw * 32 + lane; in_workspace && i < p.group * (HD + 2); i += GROUP_WARPS * 32) {
                     const int r = i / (HD + 2), d = i % (HD + 2);
                     float mw[GROUP_WARPS], M = -INFINITY;
 #pragma unroll
@@ -431,6 +434,10 @@ __global__ void __launch_bounds__(TG * HD) decode_merge_kernel(const DecodeParam
     const size_t stride = (size_t)p.n_q * (HD + 2);
     __nv_bfloat16* const out_row = p.out + (size_t)__ldg(p.q_start + seq) * p.out_stride + (size_t)h * HD;
     pdl_wait();
+    if ((size_t)__ldg(p.split_start + w) + n_splits > (size_t)p.partial_slots) {      // flagged by the split kernel too
+        if (tid == 0) atomicOr(p.status, RS_STATUS_BAD_PLAN);
+        return;
+    }
     // Everything the first round needs is asked for at once, before anything is waited for: the splits' maxima and
     // sums (kept in registers when there is at most one split per thread) and the first accumulators of this
     // thread's chain(s).  The arithmetic and its order are the same as if they were loaded where they are used.
@@ -600,11 +607,11 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
                                        long page_stride, int num_pages, int page_size, const int* block_table,
                                        int table_stride, const int* q_start, const int* kv_len, const int* work,
                                        int n_work, int n_q, int n_kv, int hd, int window, float scale, int split_keys,
-                                       int max_splits, const int* split_start, float* partial, int* status,
-                                       void* stream) {
+                                       int max_splits, const int* split_start, float* partial, int partial_slots,
+                                       int* status, void* stream) {
     if (n_work <= 0) return 0;
     if (!rs_attention_decode_bf16_supported(n_q, n_kv, hd, page_size) || split_keys != SPLIT || max_splits <= 0 ||
-        partial == nullptr || split_start == nullptr || (q_stride % 8) || ((long)q & 15) || ((long)cache & 15) ||
+        partial == nullptr || partial_slots <= 0 || split_start == nullptr || (q_stride % 8) || ((long)q & 15) || ((long)cache & 15) ||
         page_stride != (long)2 * n_kv * page_size * hd || (long)n_work * n_kv * max_splits > 0x7fff0000L)
         return (int)cudaErrorInvalidValue;
     DecodeParams p;
@@ -613,7 +620,8 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
     p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
     p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.split_start = split_start; p.partial = partial; p.status = status; p.n_work = n_work; p.max_splits = max_splits;
+    p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
+    p.n_work = n_work; p.max_splits = max_splits;
     p.total = n_work * n_kv * max_splits;
     p.groups = p.depth = 0;
     CUtensorMap mkv;

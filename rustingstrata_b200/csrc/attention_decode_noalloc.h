@@ -20,9 +20,19 @@
 //  * Limit: total_splits * n_q * (hd + 2) must not exceed RS_NOALLOC_MAX_FLOATS.  A
 //    larger request is refused with RS_NOALLOC_TOO_LARGE before anything is launched;
 //    rs_attention_decode_noalloc_error() then returns a sentence with both numbers.
+//  * split_start lives in device memory, so the function cannot read it: it trusts
+//    that split_start[i] + (splits of sequence i) never exceeds total_splits, and
+//    checks total_splits against the limit.  Because the array is shared by every
+//    caller and cannot be resized, the kernels guard it themselves: a partial result
+//    whose slot lies beyond what the array holds for this shape is not written, the
+//    sequence's output is left untouched and bit RS_STATUS_BAD_PLAN (16) is set in
+//    *status.  Keep split_start[n_work] == total_splits.
 //  * The first call on each device looks up the array's device address (one runtime
 //    query, no allocation) and remembers it.  Make that first call outside any stream
 //    capture, with the device you will launch on made current.
+//  * The remembered address belongs to the device's current primary context.  After a
+//    cudaDeviceReset the remembered value is stale and this entry point must not be
+//    called again in that process (nothing here can notice the reset).
 //  * All calls share the one array and it keeps whatever the last call left there.
 //    The kernels write every slot they later read, so nothing has to be cleared
 //    between calls; but two calls whose kernels can overlap on the GPU (different

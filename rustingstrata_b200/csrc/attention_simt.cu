@@ -17,8 +17,10 @@
 // attn_decode_gqa_* :2571-2580, attn_merge :2594-2625; formulas src/model.rs:778-791.
 #include "common.cuh"
 #include <math.h>
+#include <atomic>
 
 namespace {
+constexpr int RS_MAX_DEVICES = 64;   // devices per process the per-device tables below have room for
 constexpr int KT = 32;        // keys per tile = lanes of a warp
 constexpr int WARPS = 4;
 constexpr int RPW = 4;        // query rows per warp
@@ -39,6 +41,7 @@ struct AttnParams {
     int decode, split_keys, max_splits;
     const int* split_start;                // decode: [n_work] first partial slot of each sequence
     float* partial;                        // decode: [slot][n_q][hd + 2], slot = split_start[w] + split
+    int partial_slots;                     // decode: slots `partial` holds; a slot beyond it is flagged, not written
     int* status;
 };
 
@@ -155,7 +158,12 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(const AttnP
         if (r >= n_rows) continue;
         const int tok = row0 + q_off + r / n_heads, h = head0 + r % n_heads;
         if (p.decode) {
-            float* dst = p.partial + (((size_t)p.split_start[blockIdx.x] + split_local) * p.n_q + h) * (hd + 2);
+            const size_t slot = (size_t)p.split_start[blockIdx.x] + split_local;
+            if (slot >= (size_t)p.partial_slots) {
+                if (lane == 0) atomicOr(p.status, RS_STATUS_BAD_PLAN);
+                continue;
+            }
+            float* dst = p.partial + (slot * p.n_q + h) * (hd + 2);
 #pragma unroll
             for (int i = 0; i < HDL; ++i) { const int d = lane + 32 * i; if (d < hd) dst[d] = acc[rr][i]; }
             if (lane == 0) { dst[hd] = m[rr]; dst[hd + 1] = l[rr]; }
@@ -177,6 +185,10 @@ __global__ void attention_merge_kernel(const AttnParams p) {
     const int key_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
     const int n_splits = (kv_len + p.split_keys - 1) / p.split_keys - key_lo / p.split_keys;
     const int hd = p.hd;
+    if ((size_t)p.split_start[w] + n_splits > (size_t)p.partial_slots) {       // flagged by the split kernel too
+        if (threadIdx.x == 0) atomicOr(p.status, RS_STATUS_BAD_PLAN);
+        return;
+    }
     const float* base = p.partial + ((size_t)p.split_start[w] * p.n_q + h) * (hd + 2);
     const size_t split_stride = (size_t)p.n_q * (hd + 2);
     float M = -INFINITY;
@@ -198,12 +210,19 @@ template <typename T, int HDL, bool PRECISE>
 int launch_attention(const AttnParams& p, int n_work, cudaStream_t s) {
     const size_t smem = ((size_t)2 * KT * (p.hd + 1) + (size_t)ROWS * p.hd) * sizeof(float);
     auto kern = paged_attention_kernel<T, HDL, PRECISE>;
-    static size_t smem_allowed = 0;              // raised once per size: not allowed while a stream is capturing
+    // The opt-in to more than 48 KB of shared memory is a property of (kernel, device): raised once per size on each
+    // device, and not while a stream is capturing (the engine runs every shape once eagerly before it captures).
+    static std::atomic<size_t> smem_allowed[RS_MAX_DEVICES];
     cudaError_t e;
-    if (smem > smem_allowed) {
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= RS_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    if (smem > smem_allowed[dev].load(std::memory_order_acquire)) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        smem_allowed = smem;
+        size_t seen = smem_allowed[dev].load(std::memory_order_relaxed);
+        while (seen < smem && !smem_allowed[dev].compare_exchange_weak(seen, smem, std::memory_order_release)) {}
     }
     dim3 grid(n_work, p.n_kv * p.chunks_per_group, p.decode ? p.max_splits : 1);
     kern<<<grid, WARPS * 32, smem, s>>>(p);
@@ -238,10 +257,12 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
                                 long page_stride, int num_pages, int page_size, const int* block_table,
                                 int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
                                 int n_q, int n_kv, int hd, int window, float scale, int decode, int split_keys,
-                                int max_splits, const int* split_start, float* partial, int* status, void* stream) {
+                                int max_splits, const int* split_start, float* partial, int partial_slots, int* status,
+                                void* stream) {
     if (n_work <= 0) return 0;
     if (hd % 16 || hd > 256 || hd <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
-    if (decode && (split_keys % KT || split_keys <= 0 || max_splits <= 0 || partial == nullptr || split_start == nullptr))
+    if (decode && (split_keys % KT || split_keys <= 0 || max_splits <= 0 || partial == nullptr || partial_slots <= 0 ||
+                   split_start == nullptr))
         return (int)cudaErrorInvalidValue;
     AttnParams p;
     p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
@@ -252,7 +273,7 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
     p.chunks_per_group = (p.group + p.heads_per_cta - 1) / p.heads_per_cta;
     p.q_per_cta = decode ? 1 : ROWS / p.heads_per_cta;
     p.window = window; p.scale = scale; p.decode = decode; p.split_keys = split_keys; p.max_splits = max_splits;
-    p.split_start = split_start; p.partial = partial; p.status = status;
+    p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RS_F32) return dispatch_hd<float, true>(p, n_work, s);
     if (dt == RS_BF16) return dispatch_hd<__nv_bfloat16, false>(p, n_work, s);
@@ -272,7 +293,7 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
 static __device__ __align__(256) float rs_noalloc_partial[RS_NOALLOC_MAX_FLOATS];
 
 namespace {
-constexpr int RS_NOALLOC_MAX_DEVICES = 64;
+constexpr int RS_NOALLOC_MAX_DEVICES = RS_MAX_DEVICES;
 float* g_noalloc_address[RS_NOALLOC_MAX_DEVICES] = {nullptr};
 std::mutex g_noalloc_mutex;
 thread_local char g_noalloc_error[256] = "";
@@ -340,6 +361,9 @@ RS_EXPORT int rs_attention_decode_noalloc(const void* q, long q_stride, void* ou
     p.q_per_cta = 1;
     p.window = window; p.scale = scale; p.decode = 1; p.split_keys = split_keys; p.max_splits = max_splits;
     p.split_start = split_start; p.partial = partial; p.status = status;
+    // what the array really holds for this shape, not what the caller said it would use: a split list that
+    // disagrees with total_splits is flagged by the kernels (RS_STATUS_BAD_PLAN) instead of written past the array
+    p.partial_slots = (int)((long)RS_NOALLOC_MAX_FLOATS / ((long)n_q * (hd + 2)));
     cudaStream_t s = (cudaStream_t)stream;
     int e;
     if (dt == RS_F32) e = dispatch_hd<float, true>(p, n_work, s);

@@ -18,6 +18,8 @@ enum RsStatus : int {
     RS_STATUS_BAD_TOKEN = 1,      // token id outside the vocabulary
     RS_STATUS_BAD_PAGE = 2,       // block table entry outside the pool where a live key was expected
     RS_STATUS_WAIT_EXPIRED = 4,   // a bounded wait on a barrier gave up
+    RS_STATUS_NON_FINITE = 8,     // a row of logits holds no finite maximum
+    RS_STATUS_BAD_PLAN = 16,      // a work list points outside a workspace (partial-result slot beyond its capacity)
 };
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);

@@ -14,7 +14,6 @@
 
 namespace {
 constexpr int THREADS = 1024;
-constexpr int RS_STATUS_NON_FINITE = 8;
 
 struct ArgPair { float v; int i; };
 

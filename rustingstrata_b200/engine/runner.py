@@ -354,5 +354,6 @@ class ModelRunner:
             what = [n for b, n in ((ops.STATUS_BAD_TOKEN, "token id outside the vocabulary"),
                                    (ops.STATUS_BAD_PAGE, "block table entry outside the page pool"),
                                    (ops.STATUS_WAIT_EXPIRED, "a bounded wait inside a kernel gave up"),
-                                   (ops.STATUS_NON_FINITE, "logits are not finite")) if code & b]
+                                   (ops.STATUS_NON_FINITE, "logits are not finite"),
+                                   (ops.STATUS_BAD_PLAN, "a work list points outside its workspace")) if code & b]
             raise StepError("device status: " + "; ".join(what))

@@ -11,13 +11,19 @@ tokens, this scheduler builds one mixed batch per step:
 2. what is left of the token budget goes to prompt portions, oldest request first
    (a portion may be cut anywhere);
 3. waiting requests are admitted in arrival order while a state slot is free and the
-   pools can hold the request's whole prompt plus one page of decoding.
+   pools can hold the request's whole prompt plus one page of decoding (or its whole
+   life, if that is less) on top of everything the running requests still have to
+   bring into the cache.
 
 When pages run out for a decode token, the most recently admitted running request is
 preempted: its pages are given back and it returns to the head of the waiting queue
-with prompt = original prompt + tokens generated so far, to be recomputed.  A request
-that can never fit (longer than the pool or than the model's positions) is rejected
-when it is added.  The scheduler is pure host logic over the cache manager.
+with prompt = original prompt + tokens generated so far, to be recomputed.  The same
+happens when no running request can take a single token (every one of them waits for
+pages another holds): the newest yields until the oldest can go on.  A request that
+can never fit (longer than the pool or than the model's positions) is rejected when it
+is added; what is accepted there can always be admitted into an empty engine.  So
+``schedule`` returns an empty batch only when every waiting request arrives later.
+The scheduler is pure host logic over the cache manager.
 """
 from __future__ import annotations
 
@@ -30,6 +36,11 @@ from ..cache import CacheManager, OutOfSlots
 
 class RequestRejected(ValueError):
     pass
+
+
+class SchedulerStuck(RuntimeError):
+    """Requests are running but none can take a token and nobody can yield (a fault of the bookkeeping, not a
+    state a workload can reach): raised instead of returning empty batches for ever."""
 
 
 @dataclass
@@ -91,11 +102,15 @@ class Scheduler:
         if total > self.max_positions:
             raise RequestRejected(f"request {req.rid!r}: context full ({total} tokens; the model has "
                                   f"{self.max_positions} positions)")
-        pool_tokens = min(p.num_pages for p in self.cache.pools) * self.cache.page_size
-        window_free = all(g.window is None for g in self.cache.groups)
-        if window_free and total > pool_tokens:
-            raise RequestRejected(f"request {req.rid!r}: context full ({total} tokens; the cache holds "
-                                  f"{pool_tokens})")
+        for g, (pool, need) in enumerate(zip(self.cache.pools, self.cache.groups)):
+            # a group that keeps every key must hold the whole request; a window group the window and the page
+            # that is being written
+            most = self._pages_for(total)
+            if need.window is not None:
+                most = min(most, self._pages_for(need.window) + 1)
+            if most > pool.num_pages:
+                raise RequestRejected(f"request {req.rid!r}: context full ({total} tokens; cache group {g} holds "
+                                      f"{pool.num_pages * self.cache.page_size})")
         self.waiting.append(req)
 
     def has_work(self) -> bool:
@@ -121,7 +136,38 @@ class Scheduler:
     # ---------------------------------------------------------------- one step
     def schedule(self) -> List[Scheduled]:
         """The next step's batch; reserves nothing (the runner's step reserves pages itself), but
-        guarantees the pages are there by preempting or deferring."""
+        guarantees the pages are there by preempting or deferring.  Empty only when nothing runs and every
+        waiting request arrives later."""
+        for _ in range(self.max_seqs + 2):
+            batch = self._schedule_once()
+            if batch or not self.running:
+                return batch
+            # requests are running and none can take a token: each waits for pages that another holds.  The
+            # newest yields (recomputed later) until the oldest can go on.
+            if not self._preempt_newest(keep=self.running[0]):
+                break
+        raise SchedulerStuck(f"{len(self.running)} running request(s) cannot take a token and nobody can yield "
+                             f"(free pages per group: {[p.n_free for p in self.cache.pools]})")
+
+    def _outstanding_pages(self) -> List[int]:
+        """Per group, the pages the running requests still need for every token they are known to have (the rest
+        of a prompt, the newest decoded token).  Window groups give pages back on the way, so this is an upper
+        bound there."""
+        out = [0] * len(self.cache.groups)
+        for r in self.running:
+            for g, k in enumerate(self.cache.pages_to_reserve(r.rid, len(r.all_tokens) - r.computed)):
+                out[g] += k
+        return out
+
+    def _admission_pages(self, req: Request) -> int:
+        """Pages a request must find free to be admitted: its whole prompt plus one page of decoding, or its
+        whole life if that is less (``add`` accepts what fits the pool, so the extra page must not push a
+        request that fills the pool's last page out for ever)."""
+        todo = len(req.all_tokens) - req.computed
+        life = max(todo, len(req.prompt) + req.max_new_tokens)
+        return min(self._pages_for(todo) + 1, self._pages_for(life))
+
+    def _schedule_once(self) -> List[Scheduled]:
         budget = self.max_batch_tokens
         batch: List[Scheduled] = []
         promised = [0] * len(self.cache.groups)      # pages this step will take, per group
@@ -161,15 +207,21 @@ class Scheduler:
             budget -= self._schedule_portion(req, budget, batch, fits, promise)
 
         # 3. admit waiting requests in arrival order
+        windowed = [g.window is not None for g in self.cache.groups]
+        owed = None
         while self.waiting and budget > 0 and len(self.running) < self.max_seqs:
             req = self.waiting[0]
             if req.arrival > self.step_index:
                 break
+            if owed is None:
+                owed = self._outstanding_pages()      # includes what this step has promised
             todo = len(req.all_tokens) - req.computed
-            # the whole prompt plus one page of decoding must fit in what is free and not promised
-            need_pages = self._pages_for(todo) + 1
-            windowed = [g.window is not None for g in self.cache.groups]
-            ok = all(windowed[g] or need_pages + promised[g] <= self.cache.n_free(g) for g in range(len(promised)))
+            # The whole prompt plus one page of decoding (the request's whole life, if that is less) must fit in
+            # what is free once the running requests have brought in all they still have to: a prompt that is
+            # cut into portions takes its pages over several steps, and two prompts admitted on the strength of
+            # the same free pages would starve each other.
+            need_pages = self._admission_pages(req)
+            ok = all(windowed[g] or need_pages + owed[g] <= self.cache.n_free(g) for g in range(len(promised)))
             if not ok:
                 break
             try:
@@ -178,6 +230,8 @@ class Scheduler:
                 break
             self.waiting.popleft()
             self.running.append(req)
+            for g, k in enumerate(self.cache.pages_to_reserve(req.rid, todo)):
+                owed[g] += k
             budget -= self._schedule_portion(req, budget, batch, fits, promise)
         return batch
 

@@ -22,6 +22,7 @@ STATUS_BAD_TOKEN = 1
 STATUS_BAD_PAGE = 2
 STATUS_WAIT_EXPIRED = 4
 STATUS_NON_FINITE = 8
+STATUS_BAD_PLAN = 16
 
 
 class KernelError(RuntimeError):
@@ -96,7 +97,7 @@ def core():
                                        c_int, c_int, c_int, c_int, c_void_p]
         lib.rs_attention_simt.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int,
                                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                           c_void_p]
         lib.rs_attention_simt_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_attention_simt_partial_floats.argtypes = [c_int, c_int, c_int]
@@ -263,7 +264,7 @@ def bf16lib():
         lib.rs_mid_gemm_workspace_floats.restype = c_long
         lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                 c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                 c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                                  c_void_p]
         lib.rs_attention_decode_bf16_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
@@ -497,7 +498,13 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
                    head_dim: int, page_size: int, window: int, scale: float, decode: bool, status: torch.Tensor,
                    split_keys: int = 128, max_splits: int = 1, split_start: Optional[torch.Tensor] = None,
                    total_splits: int = 0, partial: Optional[torch.Tensor] = None) -> None:
-    """Paged causal attention (see csrc/attention_simt.cu).  q/out: [T, >= n_q*head_dim] views."""
+    """Paged causal attention (see csrc/attention_simt.cu).  q/out: [T, >= n_q*head_dim] views.
+
+    Decode form: ``partial`` is the workspace of un-normalised partial results, one slot of n_q * (head_dim + 2)
+    float32 values per (sequence, split); ``split_start[w]`` is the first slot of sequence w and ``total_splits`` the
+    slots the caller knows the step uses (0 when it cannot say, as for a captured step whose lengths change from
+    replay to replay).  The kernels are told how many slots the workspace holds and flag a slot beyond it
+    (STATUS_BAD_PLAN) instead of writing there."""
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
@@ -512,18 +519,29 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
         if t.dtype != torch.int32:
             raise KernelError(f"attention: {name} must be int32")
+    slots = 0
     if decode:
-        need = attention_partial_floats(total_splits, n_q, head_dim)
         if split_start is None or split_start.dtype != torch.int32:
             raise KernelError("attention: the decode form needs int32 split_start")
-        if partial is None or partial.dtype != torch.float32 or partial.numel() < need:
-            raise KernelError(f"attention: the decode form needs {need} float32 values of partial workspace")
+        slots = _partial_slots(partial, total_splits, n_q, head_dim, "attention")
     _check(core().rs_attention_simt(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q), _ptr(cache), cache.stride(0), cache.shape[0],
         page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q,
         n_kv, head_dim, int(window), float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start),
-        _ptr(partial),
+        _ptr(partial), slots,
         _ptr(status), _stream()), "attention_simt")
+
+
+def _partial_slots(partial: Optional[torch.Tensor], total_splits: int, n_q: int, head_dim: int, who: str) -> int:
+    """Slots of partial results the workspace holds; raises if the step is known to need more."""
+    if partial is None or partial.dtype != torch.float32 or not partial.is_contiguous():
+        raise KernelError(f"{who}: the decode form needs a contiguous float32 workspace of partial results")
+    slots = min(partial.numel() // (n_q * (head_dim + 2)), 0x7FFFFFFF)
+    if slots < max(1, total_splits):
+        raise KernelError(f"{who}: the step's {max(1, total_splits)} (sequence, split) pairs need "
+                          f"{attention_partial_floats(max(1, total_splits), n_q, head_dim)} float32 values of partial "
+                          f"workspace, {partial.numel()} were given")
+    return int(slots)
 
 
 def attention_prefill_kernel(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int, force: str = "") -> str:
@@ -626,14 +644,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                     ("split_start", split_start)):
         if t.dtype != torch.int32:
             raise KernelError(f"attention_decode: {name} must be int32")
-    need = attention_partial_floats(total_splits, n_q, head_dim)
-    if partial.dtype != torch.float32 or partial.numel() < need:
-        raise KernelError(f"attention_decode: needs {need} float32 values of partial workspace")
+    slots = _partial_slots(partial, total_splits, n_q, head_dim, "attention_decode")
     _check(bf16lib().rs_attention_decode_bf16(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
         _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv, head_dim,
-        int(window), float(scale), split_keys, max_splits, _ptr(split_start), _ptr(partial), _ptr(status), _stream()),
-        "attention_decode_bf16", 2)
+        int(window), float(scale), split_keys, max_splits, _ptr(split_start), _ptr(partial), slots, _ptr(status),
+        _stream()), "attention_decode_bf16", 2)
 
 
 # ----------------------------------------------------------------------------- sampling

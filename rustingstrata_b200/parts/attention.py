@@ -66,10 +66,11 @@ class PagedAttention(Mixer):
         rt = runtime
         rt.scratch("qkv", rt.max_batch_tokens, self.q_width + 2 * self.kv_width)
         rt.scratch("attn_out", rt.max_batch_tokens, self.q_width)
-        # every live sequence may have one partly filled split, and a captured step launches its splits
-        # rounded up to SPLIT_BUCKET
-        max_total_splits = rt.pool_tokens // SPLIT_KEYS + rt.max_seqs * (SPLIT_BUCKET + 1) + 1
-        rt.scratch("attn_partial", 1, max_total_splits * self.n_heads * (self.hd + 2), torch.float32)
+        # Partial results of the split form: one slot per (sequence, split).  The keys a step can see lie in the
+        # pool, so whole splits number at most pool_tokens / SPLIT_KEYS in all; beside them every sequence may have
+        # a partly filled split at either end of what it sees (the newest keys; the oldest ones inside a window).
+        self.partial_slots = rt.pool_tokens // SPLIT_KEYS + 2 * rt.max_seqs + 1
+        rt.scratch("attn_partial", 1, self.partial_slots * self.n_heads * (self.hd + 2), torch.float32)
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
 
     # ---------------------------------------------------------------- weights
@@ -131,10 +132,17 @@ class PagedAttention(Mixer):
             pre = pre[np.argsort(-last_pos, kind="stable")]
         max_splits = int(splits.max()) if len(dec) else 0
         total_splits = int(split_start[-1])
+        if total_splits > self.partial_slots:
+            raise ValueError(f"paged_attention: the step's single-token sequences span {total_splits} splits of "
+                             f"{SPLIT_KEYS} keys, the workspace was sized for {self.partial_slots} (more keys than "
+                             f"the cache pool holds?)")
         if batch.bucketed and len(dec):
-            # launch shapes of a captured step: splits beyond a sequence's own count exit at once
+            # A captured step: the number of splits launched per sequence is a launch shape, so it is rounded up (a
+            # split beyond a sequence's own count exits at once).  The slots really used change from replay to
+            # replay and always fit (checked above, every step); the launcher is told nothing about them (0), so
+            # that the captured layout does not depend on the lengths.
             max_splits = (max_splits + SPLIT_BUCKET - 1) // SPLIT_BUCKET * SPLIT_BUCKET
-            total_splits = len(dec) * max_splits
+            total_splits = 0
         return {"decode_work": dec, "split_start": split_start, "prefill_work": pre.reshape(-1),
                 "n_decode": int(len(dec)), "n_prefill": int(pre.shape[0]),
                 "max_splits": max_splits, "total_splits": total_splits}

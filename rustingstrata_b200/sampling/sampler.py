@@ -55,12 +55,16 @@ class SamplingParams:
     dry_base: float = 1.75
     dry_allowed_length: int = 2
 
+    def has_penalties(self) -> bool:
+        return (self.presence_penalty != 0 or self.frequency_penalty != 0 or self.repeat_penalty != 1.0
+                or self.dry_multiplier > 0)
+
     def needs_host(self) -> bool:
-        """Whether the choice needs the sorted-candidate algorithm (cuts or penalties)."""
-        if self.temp <= 0:
-            return False
-        return (self.top_k > 0 or self.top_p < 1.0 or self.presence_penalty != 0 or self.frequency_penalty != 0
-                or self.repeat_penalty != 1.0 or self.dry_multiplier > 0)
+        """Whether the choice needs the host sampler: the penalties change the logits before any choice, the greedy
+        one included (src/ops.rs:220-227), and the top-k/top-p cuts need the sorted candidates."""
+        if self.has_penalties():
+            return True
+        return self.temp > 0 and (self.top_k > 0 or self.top_p < 1.0)
 
 
 class XorShift64:

@@ -46,6 +46,15 @@ TINY = {
                 "sliding_window": 150, "layer_types": ["full_attention", "sliding_attention", "full_attention"],
                 "torch_dtype": "bfloat16"},
         seed=3, std=0.06, norm_std=0.05, page_size=16),
+    # head size 128 with four query heads on one kv head (the benchmark model's head shape) and room for thousands
+    # of positions: long sequences inside the engine, attention splits counted in dozens
+    "E": dict(
+        config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 1000, "hidden_size": 256,
+                "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 128,
+                "intermediate_size": 384, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+                "max_position_embeddings": 4096, "tie_word_embeddings": False, "use_sliding_window": False,
+                "torch_dtype": "bfloat16"},
+        seed=4, std=0.05, norm_std=0.05, page_size=16),
 }
 
 # Tolerances, as max |difference| / max |reference logit| over the compared rows.  The 32-bit engine

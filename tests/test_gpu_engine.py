@@ -139,16 +139,27 @@ def test_chunked_prefill_with_staggered_arrivals_and_temperature(tiny_models):
         rids = [eng.add_request(random_tokens(cfg["vocab_size"], n, 300 + n), 12, SamplingParams(temp=0.8, seed=9 + i),
                                 arrival=2 * i) for i, n in enumerate(lens)]
         done = {}
-        mixed_steps = 0
+        batches = []                                         # per step: (request, tokens in the step)
+        launch = eng._launch
+
+        def spy(batch, prev):
+            batches.append([(s.request.rid, len(s.tokens)) for s in batch])
+            return launch(batch, prev)
+        eng._launch = spy
         while eng.has_work():
-            batch_sizes = [len(s.tokens) for s in eng.scheduler.schedule()] if False else None
             for r in eng.step():
                 done[r.rid] = r.generated
-        return [done[r] for r in rids], eng
-    a, eng_a = run(32, 16)
-    b, _ = run(256, None)
+        return [done[r] for r in rids], eng, batches
+    a, eng_a, steps_a = run(32, 16)
+    b, _, steps_b = run(256, None)
     assert a == b and all(len(x) == 12 for x in a)           # the cut of the work does not change the draws
-    c, _ = run(32, 16)
+    # the small budget really cut prompts and ran their portions beside other requests' single tokens
+    mixed = [st for st in steps_a if any(n > 1 for _, n in st) and any(n == 1 for _, n in st)]
+    assert len(mixed) >= 5, steps_a
+    assert any(sum(1 for rid, n in sum(steps_a, []) if rid == r and n > 1) >= 3 for r in rids)   # a prompt in 3+ portions
+    assert max(sum(n for _, n in st) for st in steps_a) <= 32 and max(n for st in steps_a for _, n in st) <= 16
+    assert max(n for st in steps_b for _, n in st) == 120    # the roomy engine took the longest prompt whole
+    c, _, _ = run(32, 16)
     assert c == a                                            # same seeds, same tokens
     eng_a.runner.cache.check()
 
@@ -168,6 +179,61 @@ def test_sampling_with_cuts_goes_through_the_host_sampler(tiny_models):
         assert t in ids.tolist() and len(ids) <= 5
         smp.note(t)
         toks.append(t)
+
+
+def test_greedy_choice_sees_the_penalties(tiny_models):
+    """Greedy generation with a repeat penalty, a presence penalty and DRY: the penalties change the logits before
+    the arg-max (src/ops.rs:220-227), so the tokens are those of the host sampler on the plain logits, and they
+    differ from plain greedy tokens."""
+    from rustingstrata_b200.sampling import Sampler, SamplingParams
+    cfg, w = P.read_model(tiny_models["A"])
+    eng = engine(tiny_models, "A", "float32")
+    p = random_tokens(cfg["vocab_size"], 12, 3)
+    opts = dict(repeat_penalty=1.8, presence_penalty=0.4, dry_multiplier=0.8)
+    out = eng.generate(p, max_new_tokens=24, temperature=0.0, **opts)
+    smp = Sampler(SamplingParams(temp=0.0, **opts))
+    toks = list(p)
+    for i, t in enumerate(out):
+        row = P.forward_logits(cfg, w, toks)[-1].astype(np.float32)
+        assert t == smp.pick(row), f"token {i}"
+        toks.append(t)
+    assert out != eng.generate(p, max_new_tokens=24, temperature=0.0)
+    assert len(set(out)) == len(out)                         # a penalty this strong never repeats a token here
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_long_request_beside_short_ones_in_decode_steps(tiny_models, dtype):
+    """Steps of single tokens only (the ones the engine captures and replays) with one request at about 3,000 keys
+    beside seven at 20 to 40: the long one's splits outnumber the others' a hundred to one and its count crosses a
+    bucket of the captured launch shape (3,072 keys = 24 splits) on the way.  Every row against the plain
+    implementation."""
+    from rustingstrata_b200.engine import StepEntry
+    cfg, w = P.read_model(tiny_models["E"])
+    eng = engine(tiny_models, "E", dtype, max_tokens=3072 + 64 + 7 * 80, max_batch_tokens=512, max_seqs=8)
+    n_steps, long_prompt = 40, 3050
+    toks = {"long": random_tokens(cfg["vocab_size"], long_prompt + n_steps, 1)}
+    for i in range(7):
+        toks[f"s{i}"] = random_tokens(cfg["vocab_size"], 20 + 3 * i + n_steps, 10 + i)
+    ref = {k: P.forward_logits(cfg, w, t) for k, t in toks.items()}
+    scale = {k: np.max(np.abs(r)) for k, r in ref.items()}
+    for k, t in toks.items():                                  # prompts, in portions of at most 512 tokens
+        n = len(t) - n_steps
+        for a in range(0, n, 512):
+            eng.step_raw([StepEntry(k, t[a:min(a + 512, n)], [])])
+    assert eng.runner.length("long") == long_prompt
+    order = list(toks)
+    worst, replays0 = 0.0, eng.runner.graph_replays
+    for j in range(n_steps):
+        rows = eng.step_raw([StepEntry(k, [toks[k][len(toks[k]) - n_steps + j]], [0]) for k in order]).cpu().numpy()
+        for row, k in zip(rows, order):
+            pos = len(toks[k]) - n_steps + j
+            err = float(np.max(np.abs(row - ref[k][pos])) / scale[k])
+            assert err <= TOL[dtype], f"step {j} request {k} position {pos}: {err:.3e}"
+            worst = max(worst, err)
+    eng.runner.check_status()
+    assert eng.runner.length("long") == long_prompt + n_steps > 3072
+    assert eng.runner.graph_replays - replays0 >= n_steps - 6          # captured and replayed, on both sides of the bucket
+    print(f"{dtype}: worst {worst:.3e}")
 
 
 def test_step_errors_leave_the_cache_untouched(tiny_models):

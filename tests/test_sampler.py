@@ -93,3 +93,15 @@ def test_dry_penalises_the_token_that_would_extend_a_repeat():
     assert pen == {7: 1.0}                                         # "5 6" seen before, followed by 7; length 2 = allowed
     s.note(7)
     assert dict(s._dry_penalties()) == {9: 2.0}                    # match of length 3 → mult * base^(3-2)
+
+
+def test_penalties_need_the_host_sampler_also_for_greedy():
+    """The reference applies the penalties before the arg-max of temp <= 0 (src/ops.rs:220-227)."""
+    assert not SamplingParams().needs_host() and not SamplingParams(temp=0.7).needs_host()
+    assert not SamplingParams(temp=0.0, top_k=5, top_p=0.5).needs_host()        # cuts mean nothing to an arg-max
+    assert SamplingParams(temp=0.7, top_k=5).needs_host() and SamplingParams(temp=0.7, top_p=0.9).needs_host()
+    for opts in (dict(repeat_penalty=1.3), dict(presence_penalty=0.1), dict(frequency_penalty=0.1), dict(dry_multiplier=0.5)):
+        assert SamplingParams(temp=0.0, **opts).needs_host() and SamplingParams(temp=0.9, **opts).needs_host()
+    s = Sampler(SamplingParams(temp=0.0, repeat_penalty=2.0))
+    row = np.array([0.0, 3.0, 2.9, 1.0], dtype=np.float32)
+    assert s.pick(row) == 1 and s.pick(row) == 2 and s.pick(row) == 1          # 3.0/2 < 2.9, then 2.9/2 < 3.0/2

@@ -81,7 +81,7 @@ def test_staggered_arrivals_wait_for_their_step():
 def test_admission_needs_room_for_the_whole_prompt_and_a_decode_page():
     cache, sched = make(num_pages=6, page_size=4, budget=64)
     sched.add(Request("a", list(range(12)), 4))               # 3 pages + 1
-    sched.add(Request("b", list(range(9)), 2))                # 3 pages + 1 > what is left
+    sched.add(Request("b", list(range(9)), 4))                # 3 pages + 1 > what is left
     batch, _ = run_step(cache, sched)
     assert [s.request.rid for s in batch] == ["a"]
     assert [r.rid for r in sched.waiting] == ["b"]
@@ -261,3 +261,101 @@ def test_lookahead_leaves_out_requests_that_end_by_length_and_stops_when_pages_r
         cache.commit(s.request.rid, len(s.tokens))
     assert cache.n_free(0) == 1
     assert sch.lookahead(batch) is None                        # both need a new page and one is free: schedule() decides
+
+
+# ------------------------------------------------------------------ progress: no state in which schedule() returns nothing for ever
+def _drain(cache, sched, limit=2000):
+    """Runs to the end; every schedule() call with work to do and nobody arriving later must return a batch."""
+    steps = 0
+    while sched.has_work():
+        future = any(r.arrival > sched.step_index for r in sched.waiting)
+        batch, _ = run_step(cache, sched)
+        assert batch or future, "schedule() returned nothing although requests could run"
+        steps += 1
+        assert steps < limit, "the scheduler does not finish"
+    return steps
+
+
+def test_two_prompts_cut_into_portions_do_not_starve_each_other():
+    """Portions smaller than the budget: the second prompt must not be admitted on the strength of pages the first
+    one has yet to take (pool of 10 pages of 4, portions of 8, prompts of 30 and 20 tokens)."""
+    cache, sched = make(num_pages=10, page_size=4, budget=64, chunk=8)
+    a, b = Request("a", list(range(30)), 2), Request("b", list(range(20)), 2)
+    sched.add(a)
+    sched.add(b)
+    batch, _ = run_step(cache, sched)
+    assert [s.request.rid for s in batch] == ["a"]             # a's 8 pages + 1 are spoken for: b waits
+    _drain(cache, sched)
+    assert len(a.generated) == 2 and len(b.generated) == 2 and sched.preemptions == 0
+    assert cache.n_free(0) == 10
+
+
+def test_a_prompt_that_fills_the_last_page_is_admitted():
+    """What add() accepts must be admissible: 38 + 2 tokens are exactly the pool's 10 pages of 4."""
+    cache, sched = make(num_pages=10, page_size=4, budget=64)
+    a = Request("a", list(range(38)), 2)
+    sched.add(a)
+    batch, _ = run_step(cache, sched)
+    assert [len(s.tokens) for s in batch] == [38]
+    _drain(cache, sched)
+    assert len(a.generated) == 2 and cache.n_free(0) == 10
+
+
+def test_prefilling_requests_that_block_each_other_are_untangled_by_preemption():
+    """Two requests that are both in the middle of their prompts and hold all pages between them (a state admission
+    avoids, forced here by hand): the newest yields, the oldest goes on, both finish."""
+    cache, sched = make(num_pages=10, page_size=4, budget=64, chunk=8)
+    a, b = Request("a", list(range(30)), 2), Request("b", list(range(20)), 2)
+    for r, n in ((a, 24), (b, 16)):
+        cache.admit(r.rid)
+        cache.reserve(r.rid, n)
+        cache.commit(r.rid, n)
+        r.computed = n
+        sched.running.append(r)
+    assert cache.n_free(0) == 0
+    batch = sched.schedule()
+    assert [s.request.rid for s in batch] == ["a"] and sched.preemptions == 1 and b.computed == 0
+    for s in batch:
+        cache.reserve(s.request.rid, len(s.tokens))
+        cache.commit(s.request.rid, len(s.tokens))
+    sched.advance(batch, {s.request.rid: 1000 for s in batch if s.samples})
+    _drain(cache, sched)
+    assert len(a.generated) == 2 and len(b.generated) == 2 and cache.n_free(0) == 10
+
+
+def test_a_running_request_that_can_never_go_on_raises_instead_of_spinning():
+    from rustingstrata_b200.engine.scheduler import SchedulerStuck
+    cache, sched = make(num_pages=2, page_size=4, budget=64)
+    a = Request("a", list(range(6)), 2)
+    cache.admit("a")
+    sched.running.append(a)
+    cache.admit("thief")                                      # pages held by something the scheduler does not know
+    cache.reserve("thief", 8)
+    with pytest.raises(SchedulerStuck, match="cannot take a token"):
+        sched.schedule()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_workloads_always_finish(seed):
+    """Random prompts, lengths, arrivals, portion sizes, budgets and pool sizes (windowed groups too): every request
+    ends with all its tokens, no page is lost, and schedule() never returns nothing while somebody could run."""
+    import random
+    rng = random.Random(seed)
+    page = rng.choice([2, 4, 16])
+    pages = rng.randint(6, 40)
+    windows = rng.choice([(None,), (None,), (None, 3 * page), (None, page + 1)])
+    budget = rng.choice([4, 8, 32, 256])
+    chunk = rng.choice([None, 3, 8, 17])
+    cache, sched = make(num_pages=pages, page_size=page, budget=budget, max_seqs=rng.randint(1, 5), chunk=chunk,
+                        windows=windows, max_positions=10_000)
+    reqs = []
+    for i in range(rng.randint(3, 12)):
+        total = rng.randint(2, pages * page)
+        n_new = rng.randint(1, total - 1)
+        r = Request(i, list(range(total - n_new)), n_new, arrival=rng.randint(0, 20))
+        sched.add(r)
+        reqs.append(r)
+    _drain(cache, sched)
+    assert all(len(r.generated) == r.max_new_tokens and r.finished for r in reqs)
+    assert all(cache.n_free(g) == pages for g in range(len(windows)))
+    cache.check()

@@ -108,3 +108,26 @@ def test_requests_beyond_the_built_in_workspace_are_refused():
     pr["total"] = 2
     assert call_noalloc(lib, pr, out, n_q, n_kv, 24, page, 0, status) == -3      # head size the kernels refuse
     assert "multiple of 16" in lib.rs_attention_decode_noalloc_error().decode()
+
+
+def test_a_split_list_that_points_beyond_the_workspace_is_flagged_not_written():
+    """The function sees total_splits only; the first slot of each sequence lies in device memory.  A list that
+    disagrees with total_splits (a slot beyond what the array holds for this shape) is caught by the kernels: the
+    sequence's result is left alone and a status bit is set.  Nothing is written outside the array."""
+    from rustingstrata_b200.kernels import ops
+    lib = load()
+    n_q, n_kv, hd, page = 8, 2, 64, 16
+    pr = problem(4, torch.float32, n_q, n_kv, hd, page, [200, 300], 0)
+    slots = lib.rs_attention_decode_noalloc_capacity() // (n_q * (hd + 2))
+    good = torch.zeros(2, n_q * hd, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert call_noalloc(lib, pr, good, n_q, n_kv, hd, page, 0, status) == 0
+    start = pr["split_start"].cpu().numpy().copy()
+    start[1] = slots - 1                                       # the second sequence's splits would end past the array
+    pr["split_start"] = torch.from_numpy(start).to(DEV)
+    out = torch.full((2, n_q * hd), 7.0, device=DEV)
+    assert call_noalloc(lib, pr, out, n_q, n_kv, hd, page, 0, status) == 0
+    torch.cuda.synchronize()
+    assert status.item() == ops.STATUS_BAD_PLAN
+    assert torch.equal(out[0], good[0]) and torch.all(out[1] == 7.0)
+    status.zero_()
