@@ -156,7 +156,8 @@ def test_chunked_prefill_with_staggered_arrivals_and_temperature(tiny_models):
     # the small budget really cut prompts and ran their portions beside other requests' single tokens
     mixed = [st for st in steps_a if any(n > 1 for _, n in st) and any(n == 1 for _, n in st)]
     assert len(mixed) >= 5, steps_a
-    assert any(sum(1 for rid, n in sum(steps_a, []) if rid == r and n > 1) >= 3 for r in rids)   # a prompt in 3+ portions
+    flat = sum(steps_a, [])
+    assert any(sum(1 for rid, n in flat if rid == r and n > 1) >= 3 for r in {rid for rid, _ in flat})   # a prompt in 3+ portions
     assert max(sum(n for _, n in st) for st in steps_a) <= 32 and max(n for st in steps_a for _, n in st) <= 16
     assert max(n for st in steps_b for _, n in st) == 120    # the roomy engine took the longest prompt whole
     c, _, _ = run(32, 16)
