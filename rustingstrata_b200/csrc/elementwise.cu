@@ -386,5 +386,45 @@ RS_EXPORT int rs_gather_i32(int* dst, const int* src, const int* idx, int n, voi
     return rs_launch_pdl(gather_i32_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, dst, src, idx, n);
 }
 
+// ---- random weights ------------------------------------------------------------------------------------
+// Element i of a tensor's stream: z = mix64(key + (first + i + 1) * GOLDEN); floating tensors take
+// shift + scale * table[z >> 48] (table: 65,536 normal quantiles as float32, made on the host), integer
+// tables the low bit of z.  Integer arithmetic, one look-up, one float32 multiply and one float32 add, none of
+// them contracted: the host's numpy generator (weights/random_init.py) produces the same bits.
+namespace {
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+template <typename T>
+__global__ void fill_random_kernel(T* out, long n, unsigned long long key, long first, const float* table, float scale,
+                                   float shift) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const unsigned long long z = mix64(key + (unsigned long long)(first + i + 1) * 0x9E3779B97F4A7C15ull);
+        out[i] = from_f32<T>(__fadd_rn(__fmul_rn(scale, __ldg(table + (z >> 48))), shift));
+    }
+}
+
+__global__ void fill_random_bits_kernel(int* out, long n, unsigned long long key, long first) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        out[i] = (int)(mix64(key + (unsigned long long)(first + i + 1) * 0x9E3779B97F4A7C15ull) & 1ull);
+}
+}  // namespace
+
+// dt: RS_F32, RS_BF16, or 2 for an int32 table of random bits (table, scale and shift unused).
+RS_EXPORT int rs_fill_random(void* out, int dt, long n, unsigned long long key, long first, const float* table,
+                             float scale, float shift, void* stream) {
+    if (n <= 0) return 0;
+    if (dt != 2 && table == nullptr) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == 2) { fill_random_bits_kernel<<<blocks, threads, 0, s>>>((int*)out, n, key, first); return rs_launch_result(); }
+    RS_DISPATCH_DTYPE(dt, T, fill_random_kernel<T><<<blocks, threads, 0, s>>>((T*)out, n, key, first, table, scale, shift));
+    return rs_launch_result();
+}
+
 // Turns programmatic dependent launch on or off for every kernel of this library (default on).
 RS_EXPORT void rs_core_set_pdl(int on) { rs_pdl_switch() = on ? 1 : 0; }

@@ -106,35 +106,29 @@ class ModelRunner:
     @classmethod
     def from_random(cls, config_dict: Mapping, engine: EngineConfig, seed: int = 0, std: float = 0.02,
                     norm_std: float = 0.0) -> "ModelRunner":
-        """Weights drawn on the device (no file): projections and tables N(0, std) rounded to bfloat16,
-        norm scales 1 (+ N(0, norm_std)).  For benchmarks of sizes too large to write to disk first."""
+        """Weights drawn on the device (no file) by the generator of ``weights/random_init.py``: the same values,
+        bit for bit, that ``write_random_model`` writes for this configuration, seed, std and norm_std (stored as
+        bfloat16), so a folder made by ``init-random`` and this mode describe the same model.  For sizes too large
+        to write to disk first."""
+        from ..weights.random_init import normal_table, scale_shift, tensor_key
         arch = resolve_architecture(config_dict)
         config = arch.config_class.from_dict(config_dict)
 
         def loader(needs, dtype, device):
-            g = torch.Generator(device=device)
+            table = torch.from_numpy(normal_table().copy()).to(device)
             out = {}
-            for i, (name, need) in enumerate(needs.items()):
-                g.manual_seed((seed * 1000003 + i) & 0x7FFFFFFF)
-                if need.role == "norm":
-                    t = torch.ones(need.shape, dtype=torch.float32, device=device)
-                    if norm_std > 0:
-                        t += torch.randn(need.shape, generator=g, dtype=torch.float32, device=device) * norm_std
-                elif need.role == "int_table":
-                    t = torch.zeros(need.shape, dtype=torch.int32, device=device)
+            for name, need in needs.items():
+                if need.role == "int_table":
+                    t = torch.empty(need.shape, dtype=torch.int32, device=device)
+                    ops.fill_random(t, tensor_key(seed, name), None, 0.0, 0.0)
                 else:
+                    scale, shift = scale_shift(need, std, norm_std)
                     t = torch.empty(need.shape, dtype=torch.bfloat16, device=device)
-                    flat = t.view(-1)
-                    chunk = 1 << 26
-                    for s in range(0, flat.numel(), chunk):
-                        n = min(chunk, flat.numel() - s)
-                        flat[s:s + n] = (torch.randn(n, generator=g, dtype=torch.float32, device=device) * std
-                                         ).to(torch.bfloat16)
-                if dtype == torch.float32 and t.dtype == torch.bfloat16:
-                    t = t.to(torch.float32)
-                elif dtype == torch.bfloat16 and need.role == "norm":
-                    t = t.to(torch.bfloat16)
+                    ops.fill_random(t, tensor_key(seed, name), table, scale, shift)
+                    if dtype == torch.float32:
+                        t = t.to(torch.float32)
                 out[name] = t
+            torch.cuda.synchronize(device)
             return out
         return cls(arch, config, engine, loader)
 

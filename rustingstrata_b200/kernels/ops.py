@@ -102,6 +102,8 @@ def core():
         lib.rs_attention_simt_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_attention_simt_partial_floats.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_simt_partial_floats.restype = c_long
+        lib.rs_fill_random.argtypes = [c_void_p, c_int, c_long, ctypes.c_ulonglong, c_long, c_void_p, c_float, c_float,
+                                       c_void_p]
         lib.rs_sample.argtypes = [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         _core = lib
     return _core
@@ -223,6 +225,24 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor, n_rows: int) -> None:
         raise KernelError("residual_add: x must be contiguous float32 and delta contiguous of the same width")
     _check(core().rs_residual_add(_ptr(x), _ptr(delta), dtype_code(delta), n_rows * x.shape[1], _stream()),
            "residual_add")
+
+
+def fill_random(out: torch.Tensor, key: int, table: Optional[torch.Tensor], scale: float, shift: float,
+                first: int = 0) -> None:
+    """out.flatten()[i] = shift + scale * table[z_i >> 48] with z_i the 64-bit hash of (key, first + i): the device
+    half of the random-weights generator (weights/random_init.py is the host half and gives the same bits).
+    ``out`` float32 or bfloat16; int32 takes the low bit of z_i and needs no table."""
+    _cuda(out, table)
+    if not out.is_contiguous():
+        raise KernelError("fill_random: out must be contiguous")
+    if out.dtype == torch.int32:
+        code = 2
+    else:
+        code = dtype_code(out)
+        if table is None or table.dtype != torch.float32 or table.numel() != 1 << 16 or not table.is_contiguous():
+            raise KernelError("fill_random: table must be the 65,536 float32 normal quantiles")
+    _check(core().rs_fill_random(_ptr(out), code, out.numel(), key & 0xFFFFFFFFFFFFFFFF, first, _ptr(table), float(scale),
+                                 float(shift), _stream()), "fill_random")
 
 
 # ----------------------------------------------------------------------------- matrix products

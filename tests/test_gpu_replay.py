@@ -151,9 +151,15 @@ def test_replay_matches_plain(tiny_models, name, dtype, cutting):
 
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_mixed_replay_uses_pages_again(tiny_models, name):
-    """The mixed cutting runs 704 tokens of requests through a pool of at most 384."""
-    tr, parts, _, _, max_tokens, tokens = replayed(tiny_models, name, "float32")
+    """The mixed cutting runs 704 tokens of requests through a pool of at most 384: the pools say at the end of the
+    replay that pages were handed out more often than there are pages, that some had been used before, and that
+    every page came back."""
+    tr, parts, got, _, max_tokens, tokens = replayed(tiny_models, name, "float32")
     assert max_tokens <= 384 < sum(round64(len(t)) for t in tokens.values())
+    assert got.pools, "trace_run reported nothing about its page pools"
+    for pool in got.pools:
+        assert pool["pages"] * TINY[name]["page_size"] <= 384
+        assert pool["allocations"] > pool["pages"] and pool["reuses"] > 0 and pool["held_at_end"] == 0, pool
     live_peak = 0
     live = set()
     for k in parts["mixed"]:
