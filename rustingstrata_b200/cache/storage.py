@@ -2,8 +2,8 @@
 
 One tensor per cache group, [calls in the group, pages, 2 (K, V), kv heads, page_size,
 head_dim] in the engine's element type, so a (page, K|V, kv head) tile is one
-contiguous [page_size, head_dim] block; one float32 [max_seqs, numel] array per mixer
-call that keeps per-request state.
+contiguous [page_size, head_dim] block; one [max_seqs, numel] array per mixer call
+that keeps per-request state, in the element type the mixer asked for.
 """
 from __future__ import annotations
 
@@ -11,6 +11,7 @@ from typing import Dict, List, Sequence
 
 import torch
 
+from ..dtypes import element_type
 from ..parts.spec import CacheNeed, StateNeed
 
 
@@ -23,10 +24,12 @@ def allocate_caches(groups: Sequence[CacheNeed], group_calls: Sequence[Sequence[
     return out
 
 
-def allocate_states(needs: Dict[int, StateNeed], max_seqs: int, device) -> Dict[int, torch.Tensor]:
-    return {i: torch.zeros((max_seqs, n.numel), dtype=torch.float32, device=device) for i, n in needs.items()}
+def allocate_states(needs: Dict, max_seqs: int, device) -> Dict:
+    """needs: key (call index, mixer role) → StateNeed; returns the same keys → [max_seqs, numel] zeros."""
+    return {k: torch.zeros((max_seqs, n.numel), dtype=element_type(n.dtype).torch, device=device)
+            for k, n in needs.items()}
 
 
 def cache_bytes_per_token(groups: Sequence[CacheNeed], group_calls: Sequence[Sequence[int]], dtype: torch.dtype) -> int:
-    es = torch.empty((), dtype=dtype).element_size()
+    es = element_type(dtype).itemsize
     return sum(2 * n.n_kv_heads * n.head_dim * es * len(c) for n, c in zip(groups, group_calls))

@@ -8,7 +8,9 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-DTYPES = ("bfloat16", "float32")
+from ..dtypes import ENGINE_DTYPES, engine_dtype_name
+
+DTYPES = ENGINE_DTYPES
 
 
 @dataclass(frozen=True)
@@ -23,8 +25,7 @@ class EngineConfig:
     device: str = "cuda:0"
 
     def __post_init__(self):
-        if self.dtype not in DTYPES:
-            raise ValueError(f"dtype must be one of {DTYPES}, got {self.dtype!r}")
+        object.__setattr__(self, "dtype", engine_dtype_name(self.dtype))      # "bf16" and "fp32" are accepted
         if self.page_size <= 0:
             raise ValueError("page_size must be positive")
         for k in ("max_seqs", "max_batch_tokens", "max_logit_rows"):

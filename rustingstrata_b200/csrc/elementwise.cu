@@ -132,14 +132,16 @@ RS_EXPORT int rs_rmsnorm(const float* x, long x_stride, const int* rows, const v
 // [q heads | k heads | v heads], each head `hd` wide.  q heads and k heads get an
 // RMSNorm over hd with a weight shared by all heads (optional), then the NEOX rotation
 // of pairs (i, i + n_rot/2) with cos/sin taken from a table indexed by position
-// (optional).  q is written back in place; k and v go to the token's cache page:
+// (optional).  A token carries pos_stride position values ("streams"): stream 0 is its
+// place in the cache, and the rotation follows stream rot_stream (0 for plain text).  q is written back in place; k and v go to the token's cache page:
 //   cache[page][0 = K, 1 = V][kv head][slot in page][hd],  page = table[seq][pos / page_size].
 // With write_kv == 0 the call reads another call's cache and only q is processed.
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int n_q, int n_kv, int hd,
                                        const void* __restrict__ q_w, const void* __restrict__ k_w, int w_dt, float eps,
-                                       const float* __restrict__ cos_sin, int n_rot,
-                                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                       const float* __restrict__ cos_sin, int n_rot, int table_rows,
+                                       const int* __restrict__ positions, int pos_stride, int rot_stream,
+                                       const int* __restrict__ seq_of_token,
                                        const int* __restrict__ block_table, int table_stride, int page_size,
                                        T* __restrict__ cache, long page_stride, int num_pages, int write_kv,
                                        int n_tokens, int* status) {
@@ -151,7 +153,12 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int
     if (warp >= n_tokens * heads_per_token) return;
     const int t = warp / heads_per_token;
     const int h = warp % heads_per_token;
-    const int pos = positions[t];
+    const int pos = positions[(size_t)t * pos_stride];                  // stream 0: where the token lies in the cache
+    const int rpos = positions[(size_t)t * pos_stride + rot_stream];    // the stream this layer's rotation follows
+    if (cos_sin != nullptr && (rpos < 0 || rpos >= table_rows)) {
+        if (lane == 0) atomicOr(status, RS_STATUS_BAD_PLAN);
+        return;
+    }
     T* src = qkv + (size_t)t * row_stride + (size_t)h * hd;   // q heads, then k heads, then v heads are contiguous
 
     T* dst = src;                                              // q: in place
@@ -178,7 +185,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int
         scale = 1.0f / sqrtf(ss / (float)hd + eps);
     }
     const int half = n_rot / 2;
-    const float* cs = cos_sin ? cos_sin + (size_t)pos * n_rot : nullptr;   // [pos][cos(half) | sin(half)]
+    const float* cs = cos_sin ? cos_sin + (size_t)rpos * n_rot : nullptr;  // [position][cos(half) | sin(half)]
     for (int i = lane; i < half; i += 32) {
         float a = to_f32<T>(src[i]) * scale, b = to_f32<T>(src[i + half]) * scale;
         if (w != nullptr) { a *= load_any(w, w_dt, i); b *= load_any(w, w_dt, i + half); }
@@ -204,8 +211,9 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, long row_stride, int
 template <int E>
 __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride, int n_q, int n_kv, int hd,
                                             const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w,
-                                            float eps, const float* __restrict__ cos_sin,
-                                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                            float eps, const float* __restrict__ cos_sin, int table_rows,
+                                            const int* __restrict__ positions, int pos_stride, int rot_stream,
+                                            const int* __restrict__ seq_of_token,
                                             const int* __restrict__ block_table, int table_stride, int page_size,
                                             __nv_bfloat16* __restrict__ cache, long page_stride, int num_pages, int write_kv,
                                             int n_tokens, int lanes_per_head, int* status) {
@@ -220,10 +228,13 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     const int sub = lane % lanes_per_head;
     const bool live = unit < (long)n_tokens * heads_per_token;
     const int t = live ? (int)(unit / heads_per_token) : 0, h = live ? (int)(unit % heads_per_token) : 0;
-    const int pos = positions[t];
+    const int pos = positions[(size_t)t * pos_stride];                  // stream 0: where the token lies in the cache
+    const int rpos = positions[(size_t)t * pos_stride + rot_stream];    // the stream this layer's rotation follows
     __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
     __nv_bfloat16* dst = src;
     bool is_v = false, ok = live, bad_page = false;
+    const bool bad_pos = rpos < 0 || rpos >= table_rows;
+    if (bad_pos) ok = false;
     if (h >= n_q) {
         const int kvh = (h - n_q) % n_kv;
         is_v = (h - n_q) / n_kv != 0;
@@ -262,14 +273,15 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
         if (w != nullptr) { unpack(*reinterpret_cast<const Vec*>(w + i), wa); unpack(*reinterpret_cast<const Vec*>(w + half + i), wb); }
 #pragma unroll
         for (int u = 0; u < E; u += 4) {
-            const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + i + u);
-            const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + i + u);
+            const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)rpos * hd + i + u);
+            const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)rpos * hd + half + i + u);
             cc[u] = c.x; cc[u + 1] = c.y; cc[u + 2] = c.z; cc[u + 3] = c.w;
             sv[u] = sn.x; sv[u + 1] = sn.y; sv[u + 2] = sn.z; sv[u + 3] = sn.w;
         }
     }
     pdl_wait();
     if (bad_page) atomicOr(status, RS_STATUS_BAD_PAGE);         // nothing is written before the wait
+    if (bad_pos && live && sub == 0) atomicOr(status, RS_STATUS_BAD_PLAN);
     Vec ua, ub;
 #pragma unroll
     for (int k = 0; k < E / 2; ++k) ua.w[k] = ub.w[k] = 0u;
@@ -300,12 +312,16 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
 }
 
 RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, int n_kv, int hd, const void* q_w,
-                                 const void* k_w, int w_dt, float eps, const float* cos_sin, int n_rot,
-                                 const int* positions, const int* seq_of_token, const int* block_table,
+                                 const void* k_w, int w_dt, float eps, const float* cos_sin, int n_rot, int table_rows,
+                                 const int* positions, int pos_stride, int rot_stream, const int* seq_of_token,
+                                 const int* block_table,
                                  int table_stride, int page_size, void* cache, long page_stride, int num_pages,
                                  int write_kv, int n_tokens, int* status, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (n_rot % 2 || n_rot > hd) return (int)cudaErrorInvalidValue;
+    if (n_rot % 2 || n_rot > hd || pos_stride <= 0 || rot_stream < 0 || rot_stream >= pos_stride ||
+        (cos_sin != nullptr && table_rows <= 0))
+        return (int)cudaErrorInvalidValue;
+    if (cos_sin == nullptr) { rot_stream = 0; table_rows = 1 << 30; }
     const long warps = (long)n_tokens * (n_q + (write_kv ? 2 * n_kv : 0));
     const int threads = 256;
     const long blocks = (warps * 32 + threads - 1) / threads;
@@ -324,14 +340,14 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
         auto kern = wide ? qk_norm_rope_kv_bf16_kernel<8> : qk_norm_rope_kv_bf16_kernel<4>;
         return rs_launch_pdl(kern, dim3((unsigned)nblocks), dim3(threads), 0, (cudaStream_t)stream,
                              (__nv_bfloat16*)qkv, row_stride, n_q, n_kv, hd, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, eps,
-                             cos_sin, positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16*)cache,
-                             page_stride, num_pages, write_kv, n_tokens, lanes, status);
+                             cos_sin, table_rows, positions, pos_stride, rot_stream, seq_of_token, block_table, table_stride,
+                             page_size, (__nv_bfloat16*)cache, page_stride, num_pages, write_kv, n_tokens, lanes, status);
     }
     RS_DISPATCH_DTYPE(dt, T,
         return rs_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
-                             (T*)qkv, row_stride, n_q, n_kv, hd, q_w, k_w, w_dt, eps, cos_sin, n_rot, positions,
-                             seq_of_token, block_table, table_stride, page_size, (T*)cache, page_stride, num_pages,
-                             write_kv, n_tokens, status));
+                             (T*)qkv, row_stride, n_q, n_kv, hd, q_w, k_w, w_dt, eps, cos_sin, n_rot, table_rows, positions,
+                             pos_stride, rot_stream, seq_of_token, block_table, table_stride, page_size, (T*)cache,
+                             page_stride, num_pages, write_kv, n_tokens, status));
     return 0;
 }
 

@@ -21,12 +21,11 @@ import torch
 
 from ..cache import CacheManager, GroupNeed, OutOfPages, allocate_caches, allocate_states, cache_bytes_per_token
 from ..config import EngineConfig, load_model_config, resolve_architecture
+from ..dtypes import element_type
 from ..kernels import ops
 from ..models import CausalLM
 from ..parts import HostBatch, Runtime, StepContext
 from ..weights import load_checkpoint
-
-_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
 class StepError(RuntimeError):
@@ -35,10 +34,15 @@ class StepError(RuntimeError):
 
 @dataclass
 class StepEntry:
-    """One request's share of a step: its next tokens and the indices among them whose logits are wanted."""
+    """One request's share of a step: its next tokens and the indices among them whose logits are wanted.
+
+    ``stream_positions``: only for models whose position encodings follow more than the token count (their parts
+    say ``n_streams`` > 1): per token, the values of position streams 1, 2, ... (stream 0 is always the token's place
+    in its sequence, which the engine counts itself).  Left out, every stream equals stream 0."""
     rid: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    stream_positions: Optional[Sequence[Sequence[int]]] = None
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -54,7 +58,7 @@ class ModelRunner:
         self.arch, self.config, self.engine = arch, config, engine
         self.device = torch.device(engine.device)
         torch.cuda.set_device(self.device)
-        self.dtype = _TORCH_DTYPE[engine.dtype]
+        self.dtype = element_type(engine.dtype).torch
         self.spec = arch.build_spec(config)
         self.page_size = engine.page_size
         self.num_pages = engine.pool_pages()
@@ -199,6 +203,18 @@ class ModelRunner:
             for w in e.want:
                 if not 0 <= w < n:
                     raise StepError(f"request {e.rid!r}: wanted place {w} is not among its {n} tokens")
+        n_streams = self.model.n_position_streams
+        for e, n in zip(entries, q_lens):
+            if e.stream_positions is None:
+                continue
+            sp = np.asarray(e.stream_positions, dtype=np.int64)
+            if n_streams == 1:
+                raise StepError(f"request {e.rid!r} gives position streams, the model's position encodings use none")
+            if sp.shape != (n, n_streams - 1):
+                raise StepError(f"request {e.rid!r}: stream_positions must be [{n} tokens][{n_streams - 1} streams], got "
+                                f"shape {sp.shape}")
+            if (sp < 0).any() or (sp >= self.max_positions).any():
+                raise StepError(f"request {e.rid!r}: a stream position lies outside 0..{self.max_positions - 1}")
 
         admitted, reserved = [], []
         try:
@@ -284,8 +300,14 @@ class ModelRunner:
         q_start = np.zeros(S + 1, dtype=np.int32)
         np.cumsum(q_lens, out=q_start[1:])
         seq_of_token = np.repeat(np.arange(S, dtype=np.int32), q_lens)
-        positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start[:-1], q_lens) + np.repeat(old, q_lens)
-                     ).astype(np.int32)
+        place = (np.arange(T, dtype=np.int32) - np.repeat(q_start[:-1], q_lens) + np.repeat(old, q_lens)
+                 ).astype(np.int32)
+        n_streams = self.model.n_position_streams
+        positions = np.repeat(place[:, None], n_streams, axis=1)           # [T, streams]; stream 0 = place in the cache
+        if n_streams > 1:
+            for i, e in enumerate(entries):
+                if e.stream_positions is not None:
+                    positions[q_start[i]:q_start[i + 1], 1:] = np.asarray(e.stream_positions, dtype=np.int32)
         slots = np.array([self.cache.slot(e.rid) for e in entries], dtype=np.int32)
         logit_rows = np.array([q_start[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
         n_groups = len(self.cache.groups)
@@ -304,7 +326,7 @@ class ModelRunner:
                           max_blocks=[t.shape[1] for t in tables], bucketed=bucketed)
         plans = self.model.plan(batch)
 
-        arrays = [("token_ids", tokens.astype(np.int32)), ("positions", positions), ("seq_of_token", seq_of_token),
+        arrays = [("token_ids", tokens.astype(np.int32)), ("positions", positions.reshape(-1)), ("seq_of_token", seq_of_token),
                   ("q_start", q_start), ("kv_len", batch.kv_lens), ("state_slots", slots), ("logit_rows", logit_rows)]
         arrays += [(("table", g), t.reshape(-1)) for g, t in enumerate(tables)]
         for key, plan in plans.items():
@@ -331,7 +353,7 @@ class ModelRunner:
         block_tables = [view[("table", g)][: S * tables[g].shape[1]].view(S, tables[g].shape[1])
                         for g in range(n_groups)]
         ctx = StepContext(n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=view["token_ids"],
-                          positions=view["positions"], seq_of_token=view["seq_of_token"], q_start=view["q_start"],
+                          positions=view["positions"][: T * n_streams].view(T, n_streams), seq_of_token=view["seq_of_token"], q_start=view["q_start"],
                           kv_len=view["kv_len"], state_slots=view["state_slots"], logit_rows=view["logit_rows"],
                           block_tables=block_tables, status=self.status, host=batch, plans=dev_plans)
         scalars = tuple((repr(key), name, val) for key, plan in plans.items() for name, val in sorted(plan.items())

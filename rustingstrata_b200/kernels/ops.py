@@ -13,10 +13,10 @@ from typing import Optional
 
 import torch
 
+from ..dtypes import element_type
 from .build import load_library
 
-F32, BF16 = 0, 1
-_DT = {torch.float32: F32, torch.bfloat16: BF16}
+F32, BF16 = element_type("float32").code, element_type("bfloat16").code
 
 STATUS_BAD_TOKEN = 1
 STATUS_BAD_PAGE = 2
@@ -30,10 +30,9 @@ class KernelError(RuntimeError):
 
 
 def dtype_code(t: torch.Tensor) -> int:
-    try:
-        return _DT[t.dtype]
-    except KeyError:
-        raise KernelError(f"unsupported element type {t.dtype} (float32 and bfloat16 only)") from None
+    if t.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"unsupported element type {t.dtype} (float32 and bfloat16 only)")
+    return element_type(t.dtype).code
 
 
 def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
@@ -89,8 +88,8 @@ def core():
         lib.rs_rmsnorm.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_long,
                                    c_int, c_int, c_void_p]
         lib.rs_qk_norm_rope_kv.argtypes = [c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                                           c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                           c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p]
+                                           c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                           c_int, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p]
         lib.rs_silu_mul.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p]
         lib.rs_residual_add.argtypes = [c_void_p, c_void_p, c_int, c_long, c_void_p]
         lib.rs_linear_simt.argtypes = [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
@@ -169,11 +168,13 @@ def qk_norm_rope_kv(qkv: torch.Tensor, n_tokens: int, n_q: int, n_kv: int, head_
                     q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                     cos_sin: Optional[torch.Tensor], n_rot: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
                     block_table: torch.Tensor, page_size: int, cache: torch.Tensor, write_kv: bool,
-                    status: torch.Tensor) -> None:
+                    status: torch.Tensor, stream: int = 0) -> None:
     """Per-head norm and rotation of q (in place) and k, and the write of k and v into their pages.
 
     qkv: [T, (n_q + 2 n_kv) * head_dim] (only the q part when ``write_kv`` is false);
     cache: [pages, 2, n_kv, page_size, head_dim] of the same element type.
+    positions: [T] or [T, n_streams] int32; column 0 is the token's place in the cache, column ``stream`` the
+    position the rotation follows (a row of ``cos_sin``).
     """
     _cuda(qkv, q_weight, k_weight, cos_sin, positions, seq_of_token, block_table, cache, status)
     _rows_contiguous(qkv, "qkv")
@@ -199,9 +200,14 @@ def qk_norm_rope_kv(qkv: torch.Tensor, n_tokens: int, n_q: int, n_kv: int, head_
     for name, t in (("positions", positions), ("seq_of_token", seq_of_token), ("block_table", block_table)):
         if t.dtype != torch.int32:
             raise KernelError(f"qk_norm_rope_kv: {name} must be int32")
+    n_streams = 1 if positions.dim() == 1 else positions.shape[1]
+    if positions.dim() > 2 or not positions.is_contiguous() or positions.shape[0] < n_tokens or not 0 <= stream < n_streams:
+        raise KernelError(f"qk_norm_rope_kv: positions must be contiguous [tokens] or [tokens, streams] and hold stream "
+                          f"{stream}; got shape {tuple(positions.shape)}")
     _check(core().rs_qk_norm_rope_kv(
         _ptr(qkv), dtype_code(qkv), qkv.stride(0), n_q, n_kv, head_dim, _ptr(q_weight), _ptr(k_weight), w_dt,
-        float(eps), _ptr(cos_sin), n_rot, _ptr(positions), _ptr(seq_of_token), _ptr(block_table),
+        float(eps), _ptr(cos_sin), n_rot, 0 if cos_sin is None else cos_sin.shape[0], _ptr(positions), n_streams, stream,
+        _ptr(seq_of_token), _ptr(block_table),
         block_table.stride(0), page_size, _ptr(cache), cache.stride(0), cache.shape[0], 1 if write_kv else 0,
         n_tokens, _ptr(status), _stream()), "qk_norm_rope_kv")
 
@@ -236,7 +242,7 @@ def fill_random(out: torch.Tensor, key: int, table: Optional[torch.Tensor], scal
     if not out.is_contiguous():
         raise KernelError("fill_random: out must be contiguous")
     if out.dtype == torch.int32:
-        code = 2
+        code = element_type("int32").code
     else:
         code = dtype_code(out)
         if table is None or table.dtype != torch.float32 or table.numel() != 1 << 16 or not table.is_contiguous():

@@ -12,8 +12,8 @@ from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 
-from ..parts import (CallInfo, CacheNeed, HostBatch, LayerCall, ModelSpec, Runtime, StateNeed, StepContext, TensorNeed,
-                     part_class)
+from ..parts import (CallInfo, CacheNeed, HostBatch, LayerCall, LayerCallInfo, ModelSpec, Runtime, StateNeed, StepContext,
+                     TensorNeed, part_class)
 
 
 class CausalLM:
@@ -23,67 +23,101 @@ class CausalLM:
         mk = lambda cat, ps, *a, **k: part_class(cat, ps.kind)(ps, runtime, *a, **k)  # noqa: E731
         self.embedding = mk("embedding", spec.embedding)
         self.blocks = []
-        for ls in spec.layers:
-            pos = mk("position", ls.position) if ls.position is not None else None
-            mixer = mk("mixer", ls.mixer, position=pos) if pos is not None else mk("mixer", ls.mixer)
-            block = mk("block", ls.block, mk("norm", ls.mixer_norm), mixer, mk("norm", ls.feed_forward_norm),
-                       mk("feed_forward", ls.feed_forward))
-            self.blocks.append(block)
+        for li, ls in enumerate(spec.layers):
+            block_cls = part_class("block", ls.block.kind)
+            try:
+                block_cls.check_roles(ls.parts)
+            except ValueError as e:
+                raise ValueError(f"layer {li}: {e}") from None
+            cat = {role: block_cls.category_of(role) for role in ls.parts}
+            # position encodings first: a mixer is built with the one that belongs to it
+            built = {role: mk("position", ps) for role, ps in ls.parts.items() if cat[role] == "position"}
+            for role, ps in ls.parts.items():
+                if cat[role] == "mixer":
+                    pos = built.get(role + "_position", built.get("position"))
+                    built[role] = mk("mixer", ps, position=pos) if pos is not None else mk("mixer", ps)
+                elif cat[role] != "position":
+                    built[role] = mk(cat[role], ps)
+            self.blocks.append(block_cls(ls.block, runtime, built))
         self.final_norm = mk("norm", spec.final_norm)
         self.head = mk("head", spec.head)
         runtime.scratch("residual", runtime.max_batch_tokens, spec.hidden_size, torch.float32)
         runtime.scratch("head_in", runtime.max_logit_rows, spec.hidden_size)
         runtime.scratch("logits", runtime.max_logit_rows, spec.vocab_size, torch.float32)
+        # position values a step carries per token: the most any position encoding of the model asks for
+        self.n_position_streams = max([1] + [int(getattr(p, "n_streams", 1)) for p in self.parts()
+                                             if p.category == "position"])
 
-        # ---- the run order: which cache and state each call uses
+        # ---- the run order: which cache and state each mixer of each call uses
         if not spec.order:
             raise ValueError("model spec has an empty run order")
-        self.calls: List[CallInfo] = []
+        self.calls: List[LayerCallInfo] = []
         self.cache_groups: List[CacheNeed] = []        # distinct needs, in order of first use
-        self.group_calls: List[List[int]] = []         # per group: the calls that own a cache in it
-        self.state_needs: Dict[int, StateNeed] = {}    # call index → state need
-        self._cache_slot: Dict[int, Tuple[int, int]] = {}   # owning call → (group, index within group)
+        self.group_calls: List[List[Tuple[int, str]]] = []     # per group: the (call, mixer role) that own a cache in it
+        self.state_needs: Dict[Tuple[int, str], StateNeed] = {}     # (call index, mixer role) → state need
+        self._cache_slot: Dict[Tuple[int, str], Tuple[int, int]] = {}   # (call, role) → (group, index within group)
         for i, lc in enumerate(spec.order):
             if not 0 <= lc.layer < len(self.blocks):
                 raise ValueError(f"run order entry {i} names layer {lc.layer}, but the model has {len(self.blocks)}")
-            mixer = self.blocks[lc.layer].mixer
-            need = mixer.cache_need()
-            info = CallInfo(index=i, layer=lc.layer)
-            if need is not None:
-                if lc.cache is None:
-                    if need not in self.cache_groups:
-                        self.cache_groups.append(need)
-                        self.group_calls.append([])
-                    g = self.cache_groups.index(need)
-                    self._cache_slot[i] = (g, len(self.group_calls[g]))
-                    self.group_calls[g].append(i)
-                    info.cache_group, info.writes_cache = g, True
-                else:
-                    if not 0 <= lc.cache < i or lc.cache not in self._cache_slot:
-                        raise ValueError(f"run order entry {i} reads the cache of entry {lc.cache}, which is not an "
-                                         f"earlier entry that owns a cache")
-                    owner_need = self.cache_groups[self._cache_slot[lc.cache][0]]
-                    if (owner_need.n_kv_heads, owner_need.head_dim) != (need.n_kv_heads, need.head_dim):
-                        raise ValueError(f"run order entry {i} cannot read the cache of entry {lc.cache}: "
-                                         f"key/value shapes differ")
-                    self._cache_slot[i] = self._cache_slot[lc.cache]
-                    info.cache_group, info.writes_cache = self._cache_slot[lc.cache][0], False
-            elif lc.cache is not None:
+            mixers = self.blocks[lc.layer].mixers()
+            if isinstance(lc.cache, Mapping):
+                borrow = dict(lc.cache)
+                unknown = [r for r in borrow if r not in mixers]
+                if unknown:
+                    raise ValueError(f"run order entry {i} names a cache for {unknown}, which are no mixers of its layer")
+            else:
+                borrow = {r: lc.cache for r in mixers} if lc.cache is not None else {}
+            entry = LayerCallInfo(index=i, layer=lc.layer)
+            any_cache = False
+            for role, mixer in mixers.items():
+                need = mixer.cache_need()
+                info = CallInfo(index=i, layer=lc.layer, role=role)
+                src = borrow.get(role)
+                if need is not None:
+                    any_cache = True
+                    if src is None:
+                        if need not in self.cache_groups:
+                            self.cache_groups.append(need)
+                            self.group_calls.append([])
+                        g = self.cache_groups.index(need)
+                        self._cache_slot[(i, role)] = (g, len(self.group_calls[g]))
+                        self.group_calls[g].append((i, role))
+                        info.cache_group, info.writes_cache = g, True
+                    else:
+                        if not 0 <= src < i or (src, role) not in self._cache_slot:
+                            raise ValueError(f"run order entry {i} reads the cache of entry {src}, which is not an "
+                                             f"earlier entry that owns a cache")
+                        owner_need = self.cache_groups[self._cache_slot[(src, role)][0]]
+                        if (owner_need.n_kv_heads, owner_need.head_dim) != (need.n_kv_heads, need.head_dim):
+                            raise ValueError(f"run order entry {i} cannot read the cache of entry {src}: "
+                                             f"key/value shapes differ")
+                        self._cache_slot[(i, role)] = self._cache_slot[(src, role)]
+                        info.cache_group, info.writes_cache = self._cache_slot[(src, role)][0], False
+                sn = mixer.state_need()
+                if sn is not None:
+                    self.state_needs[(i, role)] = sn
+                entry.mixers[role] = info
+            if lc.cache is not None and not any_cache:
                 raise ValueError(f"run order entry {i} names a cache but its mixer keeps none")
-            sn = mixer.state_need()
-            if sn is not None:
-                self.state_needs[i] = sn
-            self.calls.append(info)
+            self.calls.append(entry)
 
     # ---------------------------------------------------------------- weights
     def parts(self):
-        yield self.embedding
+        """Every part of the model, each object once."""
+        seen = set()
+
+        def once(p):
+            if p is not None and id(p) not in seen:
+                seen.add(id(p))
+                yield p
+        yield from once(self.embedding)
         for b in self.blocks:
-            yield from (b, b.mixer_norm, b.mixer, b.ff_norm, b.feed_forward)
-            if getattr(b.mixer, "position", None) is not None:
-                yield b.mixer.position
-        yield self.final_norm
-        yield self.head
+            yield from once(b)
+            for p in b.parts.values():
+                yield from once(p)
+                yield from once(getattr(p, "position", None))
+        yield from once(self.final_norm)
+        yield from once(self.head)
 
     @property
     def capturable(self) -> bool:
@@ -104,13 +138,15 @@ class CausalLM:
             p.load(tensors)
 
     # ---------------------------------------------------------------- storage binding
-    def bind_storage(self, caches: List[torch.Tensor], states: Dict[int, torch.Tensor]) -> None:
-        """caches[g]: [calls in group g, pages, 2, n_kv, page_size, head_dim]; states[call]: [max_seqs, numel]."""
-        for i, info in enumerate(self.calls):
-            if i in self._cache_slot:
-                g, j = self._cache_slot[i]
-                info.cache = caches[g][j]
-            info.state = states.get(i)
+    def bind_storage(self, caches: List[torch.Tensor], states: Dict[Tuple[int, str], torch.Tensor]) -> None:
+        """caches[g]: [owners in group g, pages, 2, n_kv, page_size, head_dim]; states[(call, role)]: [max_seqs, numel]."""
+        for entry in self.calls:
+            for role, info in entry.mixers.items():
+                key = (entry.index, role)
+                if key in self._cache_slot:
+                    g, j = self._cache_slot[key]
+                    info.cache = caches[g][j]
+                info.state = states.get(key)
 
     # ---------------------------------------------------------------- one step
     def plan(self, batch: HostBatch) -> Dict:

@@ -37,9 +37,9 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
             "down_proj": p + "mlp.down_proj.weight",
         })
         norm = lambda name: PartSpec("rmsnorm", {"width": H, "eps": cfg.rms_norm_eps}, {"weight": p + name})  # noqa: E731
-        layers.append(LayerSpec(block=PartSpec("pre_norm", {"hidden": H}), mixer=mixer,
-                                mixer_norm=norm("input_layernorm.weight"), feed_forward=ff,
-                                feed_forward_norm=norm("post_attention_layernorm.weight"), position=position))
+        layers.append(LayerSpec(PartSpec("pre_norm", {"hidden": H}), {
+            "mixer_norm": norm("input_layernorm.weight"), "mixer": mixer, "position": position,
+            "feed_forward_norm": norm("post_attention_layernorm.weight"), "feed_forward": ff}))
     embed_name = "model.embed_tokens.weight"
     return ModelSpec(
         name="qwen3", vocab_size=cfg.vocab_size, hidden_size=H, max_positions=cfg.max_position_embeddings,

@@ -162,7 +162,8 @@ class PagedAttention(Mixer):
         pos = self.position
         ops.qk_norm_rope_kv(qkv, T, self.n_heads, self.n_kv, self.hd, self.q_norm_w, self.k_norm_w, self.eps,
                             pos.cos_sin if pos is not None else None, pos.n_rot if pos is not None else 0,
-                            ctx.positions, ctx.seq_of_token, table, rt.page_size, call.cache, write_kv, ctx.status)
+                            ctx.positions, ctx.seq_of_token, table, rt.page_size, call.cache, write_kv, ctx.status,
+                            stream=pos.stream if pos is not None else 0)
         out = rt.get_scratch("attn_out")[:, : self.q_width]
         plan = ctx.plans[self.plan_key()]
         common = dict(q=qkv, out=out, cache=call.cache, block_table=table, q_start=ctx.q_start, kv_len=ctx.kv_len,

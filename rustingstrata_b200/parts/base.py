@@ -91,13 +91,22 @@ class HostBatch:
 
 @dataclass
 class CallInfo:
-    """Where one entry of the run order keeps its things."""
+    """Where one mixer of one entry of the run order keeps its things (what ``Mixer.forward`` is handed)."""
     index: int                            # position in the run order
     layer: int
+    role: str = "mixer"                   # the mixer's role in its layer
     cache_group: Optional[int] = None     # page pool ("cache group") of the cache this call uses
     cache: Optional[torch.Tensor] = None  # [pages, 2, n_kv, page_size, head_dim] view of that cache
     writes_cache: bool = True             # False when the call reads another call's cache
-    state: Optional[torch.Tensor] = None  # [max_seqs, numel] float32 per-request state of this call
+    state: Optional[torch.Tensor] = None  # [max_seqs, numel] per-request state of this call, in the type it asked for
+
+
+@dataclass
+class LayerCallInfo:
+    """One entry of the run order: the layer it runs and the storage of each of the layer's mixers, by role."""
+    index: int
+    layer: int
+    mixers: Dict[str, CallInfo] = field(default_factory=dict)
 
 
 @dataclass
@@ -107,7 +116,10 @@ class StepContext:
     n_seqs: int
     n_logit_rows: int
     token_ids: torch.Tensor        # [T]
-    positions: torch.Tensor        # [T] position of each token in its sequence
+    positions: torch.Tensor        # [T, n_streams]: column 0 is the token's place in its sequence (and in the cache);
+                                   # further columns are position streams that the request supplied, for position
+                                   # encodings that follow something other than the token count (equal to column
+                                   # 0 where none were given).  One column for every model whose parts ask for one.
     seq_of_token: torch.Tensor     # [T] index of the token's sequence within this step
     q_start: torch.Tensor          # [S + 1]
     kv_len: torch.Tensor           # [S]
@@ -190,15 +202,49 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """What a mixer needs to encode positions; the mixer's kernels consume it."""
+    """What a mixer needs to encode positions; the mixer's kernels consume it.
+
+    ``n_streams``: how many position values per token the step must carry for this part (1: the token's place in its
+    sequence is all it needs); ``stream``: which of them its table is indexed by."""
+    n_streams = 1
+    stream = 0
 
 
 class Block(Part):
-    """Arrangement of norms, mixer and feed-forward around the residual stream."""
+    """Arrangement of a layer's parts around the residual stream.
 
-    def __init__(self, spec, runtime, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm, feed_forward: FeedForward):
+    ``roles`` (class attribute) names what the arrangement is made of: role → part category.  The model builds the
+    parts a layer's description lists, checks them against ``roles`` (every role listed must be known; every role
+    not in ``optional`` must be there) and hands them over as a mapping; the block is free in what it does with
+    them in ``forward``.  Roles of category "mixer" are the ones that can own a cache or state: the model asks each
+    for its needs, and ``forward`` finds each one's storage in ``call.mixers[role]``."""
+    roles: Mapping[str, str] = {}
+    optional: Tuple[str, ...] = ()
+
+    def __init__(self, spec, runtime, parts: Mapping[str, Part]):
         super().__init__(spec, runtime)
-        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
+        self.parts: Dict[str, Part] = dict(parts)
+
+    @classmethod
+    def check_roles(cls, given) -> None:
+        known = dict(cls.roles)
+        extra = [r for r in given if r not in known and not cls._is_position_role(r)]
+        lacking = [r for r in known if r not in given and r not in cls.optional]
+        if extra or lacking:
+            raise ValueError(f"block '{cls.kind}' is made of {sorted(known)}"
+                             + (f"; unknown roles: {sorted(extra)}" if extra else "")
+                             + (f"; missing roles: {sorted(lacking)}" if lacking else ""))
+
+    @classmethod
+    def _is_position_role(cls, role: str) -> bool:
+        return role == "position" or (role.endswith("_position") and cls.roles.get(role[: -len("_position")]) == "mixer")
+
+    @classmethod
+    def category_of(cls, role: str) -> str:
+        return "position" if cls._is_position_role(role) else cls.roles[role]
+
+    def mixers(self) -> Dict[str, Mixer]:
+        return {r: p for r, p in self.parts.items() if self.roles.get(r) == "mixer"}
 
     @property
     def first_reader_takes_owed(self) -> bool:
@@ -206,7 +252,7 @@ class Block(Part):
         then may the block before it leave one."""
         return False
 
-    def forward(self, residual: torch.Tensor, ctx: StepContext, call: CallInfo) -> None:
+    def forward(self, residual: torch.Tensor, ctx: StepContext, call: "LayerCallInfo") -> None:
         raise NotImplementedError
 
     @staticmethod

@@ -12,7 +12,7 @@ checkpoint's tensor names arrive in ``tensors``.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, Mapping, Optional, Tuple
+from typing import Any, Dict, Mapping, Optional, Tuple, Union
 
 
 @dataclass(frozen=True)
@@ -38,13 +38,26 @@ class TensorNeed:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the arrangement ("block") and the parts it arranges."""
+    """One layer: the arrangement ("block") and the parts it arranges, by role.
+
+    Which roles exist, and which category of part fills each, is the block kind's business (its class attribute
+    ``roles``): the pre-norm block wants ``mixer_norm``, ``mixer``, ``feed_forward_norm`` and ``feed_forward``; a
+    block with post-norms, with one norm before a parallel mixer and feed-forward, or with two mixers names other
+    roles.  A role whose category is "position" is handed to the mixers of the layer: ``<mixer role>_position`` to
+    that mixer, plain ``position`` to every mixer that has none of its own.
+    """
     block: PartSpec
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
-    position: Optional[PartSpec] = None
+    parts: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    @classmethod
+    def pre_norm(cls, block: PartSpec, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: PartSpec,
+                 feed_forward_norm: PartSpec, position: Optional[PartSpec] = None) -> "LayerSpec":
+        """The usual decoder layer: x += mixer(norm(x)); x += feed_forward(norm(x))."""
+        parts = {"mixer_norm": mixer_norm, "mixer": mixer, "feed_forward_norm": feed_forward_norm,
+                 "feed_forward": feed_forward}
+        if position is not None:
+            parts["position"] = position
+        return cls(block, parts)
 
 
 @dataclass(frozen=True)
@@ -53,10 +66,11 @@ class LayerCall:
 
     ``layer`` indexes ``ModelSpec.layers`` and may occur more than once.  ``cache``
     is None when the call owns a cache of its own, or the index (into the order) of
-    an earlier call whose cache this call reads without writing.
+    an earlier call whose cache this call reads without writing; in a layer with
+    several mixers it may be a mapping mixer role → index for the mixers that borrow.
     """
     layer: int
-    cache: Optional[int] = None
+    cache: Union[None, int, Mapping[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -87,5 +101,7 @@ class CacheNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Fixed-size per-request state of one mixer call (``numel`` float32 values, zeroed at admission)."""
+    """Fixed-size per-request state of one mixer call: ``numel`` values of element type ``dtype`` (a name of the
+    element-type table: "float32", "bfloat16", "int32"), zeroed at admission."""
     numel: int
+    dtype: str = "float32"

@@ -113,12 +113,13 @@ def test_spec_has_no_sizes_of_its_own():
         spec = arch.build_spec(c)
         assert len(spec.layers) == c.num_hidden_layers and [o.layer for o in spec.order] == list(range(c.num_hidden_layers))
         for i, ls in enumerate(spec.layers):
-            p = ls.mixer.params
+            assert sorted(ls.parts) == ["feed_forward", "feed_forward_norm", "mixer", "mixer_norm", "position"]
+            p = ls.parts["mixer"].params
             assert (p["n_heads"], p["n_kv_heads"], p["head_dim"], p["eps"]) == (
                 c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rms_norm_eps)
             assert p["window"] == (c.sliding_window if c.layer_types[i] == SLIDING_ATTENTION else None)
-            assert ls.position.params == {"n_rot": c.head_dim, "base": c.rope_theta}
-            assert ls.feed_forward.params["intermediate"] == c.intermediate_size
-            assert ls.mixer_norm.params["eps"] == c.rms_norm_eps
+            assert ls.parts["position"].params == {"n_rot": c.head_dim, "base": c.rope_theta}
+            assert ls.parts["feed_forward"].params["intermediate"] == c.intermediate_size
+            assert ls.parts["mixer_norm"].params["eps"] == c.rms_norm_eps
         tied = spec.head.tensors["weight"] == spec.embedding.tensors["weight"]
         assert tied == c.tie_word_embeddings

@@ -178,6 +178,48 @@ def test_qk_norm_rope_kv_write(dtype, n_q, n_kv, hd, n_rot, page):
     assert torch.all(untouched == 0)                       # nothing outside the tokens' own slots
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd,n_rot,page", [(4, 2, 16, 16, 4), (8, 2, 128, 128, 16), (6, 3, 80, 64, 5)])
+def test_rotation_follows_the_named_position_stream(dtype, n_q, n_kv, hd, n_rot, page):
+    """A token carries three position values; the cache place is stream 0 whatever stream the rotation follows.  A
+    stream value outside the rotation table is flagged, and that token is left alone."""
+    o = ops()
+    eps, base, T, n_pages = 1e-5, 777.0, 11, 8
+    place = torch.arange(20, 20 + T, dtype=torch.int32)
+    streams = torch.stack([place, (place * 7) % 50, 49 - torch.arange(T, dtype=torch.int32)], dim=1).contiguous()
+    seq_of = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.randperm(n_pages)[None, : (20 + T + page - 1) // page + 1].to(torch.int32)
+    src = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV).to(dtype)
+    qw = (1 + 0.2 * torch.randn(hd, device=DEV)).to(dtype)
+    kw = (1 + 0.2 * torch.randn(hd, device=DEV)).to(dtype)
+    n_pages = int(table.max()) + 1
+    for stream in (0, 1, 2):
+        qkv = src.clone()
+        cache = torch.zeros(n_pages, 2, n_kv, page, hd, device=DEV, dtype=dtype)
+        st = status()
+        o.qk_norm_rope_kv(qkv, T, n_q, n_kv, hd, qw, kw, eps, rope_table(50, n_rot, base), n_rot, streams.to(DEV), seq_of,
+                          table.to(DEV), page, cache, True, st, stream=stream)
+        assert st.item() == 0
+        s64 = src.double().cpu()
+        q_ref = ref_norm_rope(s64[:, : n_q * hd].reshape(T, n_q, hd), qw.cpu(), eps, streams[:, stream], n_rot, base)
+        k_ref = ref_norm_rope(s64[:, n_q * hd:(n_q + n_kv) * hd].reshape(T, n_kv, hd), kw.cpu(), eps, streams[:, stream], n_rot, base)
+        close(qkv[:, : n_q * hd].reshape(T, n_q, hd), q_ref, tol(dtype, 2e-6, 8e-3))
+        for t in range(T):
+            pos = int(place[t])
+            close(cache[int(table[0, pos // page]), 0, :, pos % page], k_ref[t], tol(dtype, 2e-6, 8e-3))
+    bad = streams.clone()
+    bad[3, 1] = 50                                            # one row beyond the table of 50
+    qkv = src.clone()
+    st = status()
+    o.qk_norm_rope_kv(qkv, T, n_q, n_kv, hd, qw, kw, eps, rope_table(50, n_rot, base), n_rot, bad.to(DEV), seq_of,
+                      table.to(DEV), page, torch.zeros(n_pages, 2, n_kv, page, hd, device=DEV, dtype=dtype), True, st, stream=1)
+    assert st.item() == o.STATUS_BAD_PLAN
+    assert torch.equal(qkv[3, : n_q * hd], src[3, : n_q * hd]) and not torch.equal(qkv[4], src[4])
+    with pytest.raises(o.KernelError, match="stream"):
+        o.qk_norm_rope_kv(qkv, T, n_q, n_kv, hd, qw, kw, eps, rope_table(50, n_rot, base), n_rot, streams.to(DEV), seq_of,
+                          table.to(DEV), page, torch.zeros(n_pages, 2, n_kv, page, hd, device=DEV, dtype=dtype), True, st, stream=3)
+
+
 def test_qk_without_norm_without_rope_and_without_kv():
     o = ops()
     T, n_q, n_kv, hd, page = 4, 2, 1, 32, 4

@@ -89,8 +89,8 @@ def test_attention_mixer_alone(tiny_models, name, layer, dtype):
     ls = spec.layers[layer]
     page = TINY[name]["page_size"]
     rt = runtime(dtype, page_size=page, max_positions=cfg["max_position_embeddings"])
-    pos = part_class("position", ls.position.kind)(ls.position, rt)
-    mixer = part_class("mixer", ls.mixer.kind)(ls.mixer, rt, position=pos)
+    pos = part_class("position", ls.parts["position"].kind)(ls.parts["position"], rt)
+    mixer = part_class("mixer", ls.parts["mixer"].kind)(ls.parts["mixer"], rt, position=pos)
     mixer.load(dev_tensors(w, mixer.tensor_needs(), dtype))
     T, H = 70, cfg["hidden_size"]
     h = np.random.default_rng(5).standard_normal((T, H))
@@ -144,7 +144,7 @@ def test_embedding_head_and_block_alone(tiny_models, dtype):
     """One whole layer (block arrangement) and the two ends of the model against the plain functions."""
     from rustingstrata_b200.config import resolve_architecture
     from rustingstrata_b200.models import CausalLM
-    from rustingstrata_b200.parts import CallInfo
+    from rustingstrata_b200.parts import CallInfo, LayerCallInfo
     cfg, w = P.read_model(tiny_models["A"])
     arch = resolve_architecture(cfg)
     spec = arch.build_spec(arch.config_class.from_dict(cfg))
@@ -159,7 +159,7 @@ def test_embedding_head_and_block_alone(tiny_models, dtype):
     x0 = P.embed(toks, w)
     np.testing.assert_array_equal(res[:50].cpu().numpy(), x0.astype(np.float32))
     cache = torch.zeros(16, 2, 2, 4, 16, device=DEV, dtype=DT[dtype])
-    model.blocks[1].forward(res, ctx, CallInfo(0, 1, 0, cache, True))
+    model.blocks[1].forward(res, ctx, LayerCallInfo(0, 1, {"mixer": CallInfo(0, 1, "mixer", 0, cache, True)}))
     want = P.block(x0, w, 1, cfg, np.arange(50), None)
     assert rel_err(res[:50].cpu().numpy(), want) < (2e-6 if dtype == "float32" else 1e-2)
     # head: tied to the token table in this configuration
@@ -185,9 +185,9 @@ def test_run_order_may_repeat_a_layer_and_share_a_cache():
     spec = arch.build_spec(arch.config_class.from_dict(cfg))
     spec2 = dataclasses.replace(spec, order=(LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(1, cache=1)))
     m = CausalLM(spec2, runtime("float32"))
-    assert len(m.cache_groups) == 1 and m.group_calls == [[0, 1, 2]]
-    assert [c.writes_cache for c in m.calls] == [True, True, True, False]
-    assert m._cache_slot[3] == m._cache_slot[1]
+    assert len(m.cache_groups) == 1 and m.group_calls == [[(0, "mixer"), (1, "mixer"), (2, "mixer")]]
+    assert [c.mixers["mixer"].writes_cache for c in m.calls] == [True, True, True, False]
+    assert m._cache_slot[(3, "mixer")] == m._cache_slot[(1, "mixer")]
     with pytest.raises(ValueError, match="earlier entry"):
         CausalLM(dataclasses.replace(spec, order=(LayerCall(0, cache=1), LayerCall(1))), runtime("float32"))
     with pytest.raises(ValueError, match="names layer"):

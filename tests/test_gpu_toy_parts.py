@@ -87,7 +87,7 @@ def define_toy():
                 pos = PartSpec("rope_neox", {"n_rot": 8, "base": 100.0})       # partial rotation
             ff = PartSpec("toy_scale", {"factor": 0.5}) if i == 0 else PartSpec(
                 "gated_mlp", {"hidden": H, "intermediate": 40}, {k: f"l{i}.{k}" for k in ("gate_proj", "up_proj", "down_proj")})
-            layers.append(LayerSpec(PartSpec("pre_norm", {"hidden": H}), mixer, norm(f"l{i}.n1"), ff, norm(f"l{i}.n2"), pos))
+            layers.append(LayerSpec.pre_norm(PartSpec("pre_norm", {"hidden": H}), mixer, norm(f"l{i}.n1"), ff, norm(f"l{i}.n2"), pos))
         return ModelSpec("toy", V, H, d["max_positions"], PartSpec("token_table", {"vocab": V, "width": H}, {"weight": "emb"}),
                          tuple(layers), tuple(LayerCall(i) for i in range(d["layers"])), norm("fn"),
                          PartSpec("linear", {"vocab": V, "width": H}, {"weight": "head"}))
@@ -144,7 +144,7 @@ def test_toy_architecture_with_stateful_mixer(tmp_path, dtype):
         w = P.read_safetensors(os.path.join(d, "model.safetensors"))
         runner = ModelRunner.from_dir(d, EngineConfig(dtype=dtype, page_size=4, num_pages=24, max_seqs=4,
                                                       max_batch_tokens=128, max_logit_rows=128))
-        assert len(runner.states) == 2 and len(runner.model.cache_groups) == 1     # two stateful calls, one cached
+        assert sorted(runner.states) == [(0, "mixer"), (2, "mixer")] and len(runner.model.cache_groups) == 1   # two stateful calls, one cached
         toks = {r: random_tokens(50, n, 20 + i) for i, (r, n) in enumerate((("a", 40), ("b", 23), ("c", 31)))}
         ref = {r: plain_toy(w, t) for r, t in toks.items()}
         # a whole; b and c in portions, mixed with each other, b finishing first and its slot reused by d
@@ -261,7 +261,9 @@ def define_routed():
                              {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
             pos = PartSpec("toy_squeezed_rope", {"n_rot": 16, "base": 30.0, "squeeze": 1.0 + i})
             ff = PartSpec("toy_top1_of_n", {"hidden": H, "experts": d["experts"]}, {"router": f"l{i}.router", "experts": f"l{i}.expert"})
-            layers.append(LayerSpec(PartSpec("pre_norm", {"hidden": H}), mixer, norm(f"l{i}.n1"), ff, norm(f"l{i}.n2"), pos))
+            layers.append(LayerSpec(PartSpec("pre_norm", {"hidden": H}), {
+                "mixer_norm": norm(f"l{i}.n1"), "mixer": mixer, "position": pos, "feed_forward_norm": norm(f"l{i}.n2"),
+                "feed_forward": ff}))
         return ModelSpec("routed", V, H, d["max_positions"], PartSpec("token_table", {"vocab": V, "width": H}, {"weight": "emb"}),
                          tuple(layers), tuple(LayerCall(i) for i in range(d["layers"])), norm("fn"),
                          PartSpec("linear", {"vocab": V, "width": H}, {"weight": "head"}))
@@ -340,3 +342,215 @@ def test_toy_architecture_with_routed_feed_forward_and_its_own_position_encoding
         unregister_architecture("ToyRoutedLM")
         unregister_part("feed_forward", "toy_top1_of_n")
         unregister_part("position", "toy_squeezed_rope")
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Another arrangement of a layer (four norms, two mixers side by side) and a position encoding that follows a
+# second stream of positions, again defined here only.
+
+def define_sandwich():
+    from rustingstrata_b200.config import register_architecture
+    from rustingstrata_b200.parts import (Block, LayerCall, LayerSpec, Mixer, ModelSpec, PartSpec, PositionEncoding,
+                                          StateNeed, TensorNeed, register_part)
+    from rustingstrata_b200.kernels import ops
+
+    @register_part("block", "toy_sandwich", replace=True)
+    class Sandwich(Block):
+        """x += post_a(attention(pre_a(x)) + count(pre_a(x)));  x += post_f(ff(pre_f(x))): a norm on either side of
+        both halves (four norms), and two mixers in the first half - the package's attention and a toy that only
+        keeps a per-request counter.  The halves write into a scratch stream first so that the post-norm can see
+        their output alone."""
+        roles = {"pre_a": "norm", "attention": "mixer", "count": "mixer", "post_a": "norm",
+                 "pre_f": "norm", "ff": "feed_forward", "post_f": "norm"}
+        optional = ("count",)
+
+        def __init__(self, spec, runtime, parts):
+            super().__init__(spec, runtime, parts)
+            self.hidden = int(spec.params["hidden"])
+            runtime.scratch("sandwich_h", runtime.max_batch_tokens, self.hidden)
+            runtime.scratch("sandwich_y", runtime.max_batch_tokens, self.hidden, torch.float32)
+
+        def forward(self, residual, ctx, call):
+            T, p = ctx.n_tokens, self.parts
+            h = self.runtime.get_scratch("sandwich_h")[:, : self.hidden]
+            y = self.runtime.get_scratch("sandwich_y", torch.float32)[:, : self.hidden]
+            self.norm_of_stream(p["pre_a"], residual, h, ctx)
+            y[:T].zero_()
+            p["attention"].forward(h, y, ctx, call.mixers["attention"])
+            if "count" in p:
+                p["count"].forward(h, y, ctx, call.mixers["count"])
+            self.norm_of_stream(p["post_a"], y, h, ctx)                 # settles anything the mixers left owed to y
+            residual[:T] += h[:T].float()
+            self.norm_of_stream(p["pre_f"], residual, h, ctx)
+            y[:T].zero_()
+            p["ff"].forward(h, y, ctx)
+            self.norm_of_stream(p["post_f"], y, h, ctx)
+            residual[:T] += h[:T].float()
+
+    @register_part("mixer", "toy_token_count", replace=True)
+    class TokenCount(Mixer):
+        """Adds gain * (tokens of the request seen so far, this one included) to every channel: its only memory is an
+        int32 counter per request."""
+        capturable = False
+
+        def __init__(self, spec, runtime, position=None):
+            super().__init__(spec, runtime)
+            self.gain = float(spec.params["gain"])
+
+        def state_need(self):
+            return StateNeed(1, "int32")
+
+        def forward(self, h, residual, ctx, call):
+            hb = ctx.host
+            assert call.state.dtype == torch.int32 and call.role == "count"
+            for s in range(hb.n_seqs):
+                a, b = int(hb.q_start[s]), int(hb.q_start[s + 1])
+                st = call.state[int(hb.state_slots[s])]
+                counts = st[0] + torch.arange(1, b - a + 1, device=st.device, dtype=torch.int32)
+                residual[a:b] += self.gain * counts.float()[:, None]
+                st += b - a
+
+    @register_part("position", "toy_second_stream_rope", replace=True)
+    class SecondStreamRope(PositionEncoding):
+        """The package's rotation table, indexed by the request's own position stream (stream 1) instead of the
+        token count: the step then carries two position values per token."""
+        n_streams = 2
+        stream = 1
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.n_rot, self.base = int(spec.params["n_rot"]), float(spec.params["base"])
+
+        @property
+        def cos_sin(self):
+            return self.runtime.shared(("toy_second_stream_rope", self.n_rot, self.base), self._table)
+
+        def _table(self):
+            half = self.n_rot // 2
+            inv = np.power(self.base, -2.0 * np.arange(half, dtype=np.float64) / self.n_rot)
+            theta = np.arange(self.runtime.max_positions, dtype=np.float64)[:, None] * inv[None, :]
+            return torch.from_numpy(np.concatenate([np.cos(theta), np.sin(theta)], axis=1).astype(np.float32)).to(self.runtime.device)
+
+    class SandwichConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d, where=""):
+            return cls(dict(d))
+
+    def build(cfg):
+        d = cfg.d
+        H, V = d["hidden_size"], d["vocab_size"]
+        norm = lambda n: PartSpec("rmsnorm", {"width": H, "eps": d["eps"]}, {"weight": n})  # noqa: E731
+        layers = []
+        for i in range(d["layers"]):
+            att = PartSpec("paged_attention", {"hidden": H, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "qk_norm": False,
+                                               "window": None}, {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+            parts = {"pre_a": norm(f"l{i}.pre_a"), "attention": att, "post_a": norm(f"l{i}.post_a"),
+                     "pre_f": norm(f"l{i}.pre_f"), "post_f": norm(f"l{i}.post_f"),
+                     "ff": PartSpec("gated_mlp", {"hidden": H, "intermediate": 24}, {k: f"l{i}.{k}" for k in ("gate_proj", "up_proj", "down_proj")}),
+                     # layer 0 rotates by the token count, layer 1 by the second stream
+                     "attention_position": PartSpec("rope_neox" if i == 0 else "toy_second_stream_rope", {"n_rot": 16, "base": 50.0})}
+            if i == 1:
+                parts["count"] = PartSpec("toy_token_count", {"gain": d["gain"]})
+            layers.append(LayerSpec(PartSpec("toy_sandwich", {"hidden": H}), parts))
+        return ModelSpec("sandwich", V, H, d["max_positions"], PartSpec("token_table", {"vocab": V, "width": H}, {"weight": "emb"}),
+                         tuple(layers), tuple(LayerCall(i) for i in range(d["layers"])), norm("fn"),
+                         PartSpec("linear", {"vocab": V, "width": H}, {"weight": "head"}))
+
+    register_architecture("ToySandwichLM", SandwichConfig, build, replace=True)
+
+
+SANDWICH = {"architectures": ["ToySandwichLM"], "vocab_size": 70, "hidden_size": 32, "layers": 2, "eps": 1e-5, "gain": 0.01,
+            "max_positions": 160}
+
+
+def plain_sandwich(w, toks, stream1):
+    import plain_qwen3 as P
+    d = SANDWICH
+    x = w["emb"][np.asarray(toks)]
+    T = len(toks)
+    for i in range(d["layers"]):
+        h = P.rms_norm(x, w[f"l{i}.pre_a"], d["eps"])
+        q = (h @ w[f"l{i}.q_proj"].T).reshape(T, 2, 16)
+        k = (h @ w[f"l{i}.k_proj"].T).reshape(T, 1, 16)
+        v = (h @ w[f"l{i}.v_proj"].T).reshape(T, 1, 16)
+        pos = np.arange(T) if i == 0 else np.asarray(stream1)
+        q, k = P.rope_neox(q, pos, 16, 50.0), P.rope_neox(k, pos, 16, 50.0)
+        y = P.attention_scores(q, k, v, 1).reshape(T, 32) @ w[f"l{i}.o_proj"].T
+        if i == 1:
+            y = y + d["gain"] * np.arange(1, T + 1)[:, None]
+        x = x + P.rms_norm(y, w[f"l{i}.post_a"], d["eps"])
+        h = P.rms_norm(x, w[f"l{i}.pre_f"], d["eps"])
+        y = (P.silu(h @ w[f"l{i}.gate_proj"].T) * (h @ w[f"l{i}.up_proj"].T)) @ w[f"l{i}.down_proj"].T
+        x = x + P.rms_norm(y, w[f"l{i}.post_f"], d["eps"])
+    return P.rms_norm(x, w["fn"], d["eps"]) @ w["head"].T
+
+
+def test_toy_block_with_four_norms_two_mixers_and_a_second_position_stream(tmp_path):
+    import plain_qwen3 as P
+    from rustingstrata_b200.config import EngineConfig, unregister_architecture
+    from rustingstrata_b200.engine import ModelRunner, StepEntry, StepError
+    from rustingstrata_b200.models import manifest_for
+    from rustingstrata_b200.parts import unregister_part
+    from rustingstrata_b200.weights import write_random_model
+    define_sandwich()
+    try:
+        d = str(tmp_path / "sandwich")
+        m = manifest_for(SANDWICH)
+        assert {"l0.pre_a", "l0.post_a", "l0.pre_f", "l0.post_f", "l1.q_proj"} <= set(m)
+        write_random_model(d, SANDWICH, m, seed=11, std=0.2, norm_std=0.1)
+        w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+        runner = ModelRunner.from_dir(d, EngineConfig(dtype="float32", page_size=4, num_pages=40, max_seqs=3,
+                                                      max_batch_tokens=128, max_logit_rows=128))
+        assert runner.model.n_position_streams == 2
+        assert sorted(runner.states) == [(1, "count")] and runner.states[(1, "count")].dtype == torch.int32
+        assert sorted(runner.model.calls[1].mixers) == ["attention", "count"]
+        toks = {r: random_tokens(70, n, 60 + i) for i, (r, n) in enumerate((("a", 45), ("b", 30)))}
+        # the second stream: positions that stall and jump (as an encoding of rows and columns would), not the count
+        stream1 = {"a": [(3 * t) % 41 + t // 7 for t in range(45)], "b": [100 - 2 * t for t in range(30)]}
+        ref = {r: plain_sandwich(w, toks[r], stream1[r]) for r in toks}
+        got = {r: {} for r in toks}
+
+        def step(entries):
+            logits = runner.step([StepEntry(r, toks[r][s:s + n], list(range(n)), [[p] for p in stream1[r][s:s + n]])
+                                  for r, s, n in entries]).cpu().numpy()
+            runner.check_status()
+            k = 0
+            for r, s, n in entries:
+                for i in range(n):
+                    got[r][s + i] = logits[k]
+                    k += 1
+        step([("a", 0, 19), ("b", 0, 2)])
+        step([("a", 19, 1), ("b", 2, 27)])
+        step([("b", 29, 1), ("a", 20, 25)])
+        for r in got:
+            rows = np.stack([got[r][i] for i in range(len(toks[r]))])
+            assert rel_err(rows, ref[r]) < 5e-6, r
+        with pytest.raises(StepError, match="stream_positions must be"):
+            runner.step([StepEntry("c", [1, 2], [], [[1, 2], [3, 4]])])
+        with pytest.raises(StepError, match="outside"):
+            runner.step([StepEntry("c", [1, 2], [], [[1], [160]])])
+        # without streams of its own a request's second stream is its token count: layer 1 then rotates like layer 0
+        plain_count = plain_sandwich(w, toks["b"], list(range(30)))
+        rows = runner.step([StepEntry("c", toks["b"], list(range(30)))]).cpu().numpy()
+        assert rel_err(rows, plain_count) < 5e-6
+        for r in ("a", "b", "c"):
+            runner.release(r)
+        runner.cache.check()
+        # a layer description that does not fit its block is refused with the block's roles
+        from rustingstrata_b200.parts import LayerSpec, PartSpec, Runtime
+        from rustingstrata_b200.models.causal_lm import CausalLM
+        arch_spec = runner.spec
+        import dataclasses
+        broken = dataclasses.replace(arch_spec, layers=(LayerSpec(PartSpec("toy_sandwich", {"hidden": 32}),
+                                                                   {"pre_a": PartSpec("rmsnorm", {"width": 32, "eps": 1e-5}, {"weight": "x"}),
+                                                                    "mixer": PartSpec("paged_attention", {})}),))
+        with pytest.raises(ValueError, match="unknown roles: .'mixer'.*missing roles"):
+            CausalLM(broken, Runtime(torch.float32, torch.device("cuda:0"), 8, 2, 2, 4, 160, 64))
+    finally:
+        unregister_architecture("ToySandwichLM")
+        unregister_part("block", "toy_sandwich")
+        unregister_part("mixer", "toy_token_count")
+        unregister_part("position", "toy_second_stream_rope")

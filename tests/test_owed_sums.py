@@ -71,7 +71,7 @@ class Rows(list):
 
 def run(b, ctx):
     b.runtime = SimpleNamespace(get_scratch=lambda name: Rows())
-    b.forward(object(), ctx, None)
+    b.forward(object(), ctx, SimpleNamespace(mixers={"mixer": None}))
 
 
 def test_a_sum_left_by_the_mixer_reaches_the_next_norm_and_nobody_else():
