@@ -2,14 +2,24 @@
 """Decode and prefill throughput of the engine at Qwen3-8B sizes with random weights, on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
+    python bench.py --workload 14b-mixed | 32b-long          (the two further measured workloads, one line each)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 (a "step" is one
 decode step of the whole batch, timed on the device with CUDA events); ``e2e`` is the
 same through the Python entry point with host token ids in and out every step;
 ``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode step's bytes
 (every weight it uses once plus the cache of the live requests) to the HBM peak;
-``points`` holds decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json beside
-this file when present, else from the fallback figures of this pool.
+``points`` holds decode at batch 1 and 64 (``points_roofline``: each point's time per step
+and fraction of the HBM peak).  Peaks come from MEASURED_PEAKS.json beside this file when
+present, else from the fallback figures of this pool.
+
+``--workload 14b-mixed``: Qwen3-14B layer sizes, 32 requests with prompts of 128 to 4,096
+random tokens, all present at the start, run by the engine's scheduler with portions of 512
+prompt tokens beside the decoding requests' tokens, 256 tokens each at temperature 0.7,
+context 8,192: total tokens per second, time to first token, and what the steps held.
+``--workload 32b-long``: Qwen3-32B layer sizes, 8 requests with 12,000-token prompts, then 256
+greedy tokens each, context 16,384: decode tokens per second, its fraction of the HBM peak,
+and the share of the step that is spent on the long cache (against the same step at 16 keys).
 
 The reference (a Rust crate) cannot be installed here: ``--impl reference`` says so.
 """
@@ -33,26 +43,10 @@ QWEN3_8B = {
     "intermediate_size": 12288, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 40960,
     "tie_word_embeddings": False, "use_sliding_window": False, "torch_dtype": "bfloat16",
 }
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
 CONTEXT = 4096          # tokens per request the cache is sized for
 PROMPT = 2048           # tokens each request holds before decoding is timed
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-
-
-def peaks():
-    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.isfile(p):
-        try:
-            with open(p) as f:
-                d = json.load(f)
-            out = dict(FALLBACK_PEAKS)
-            for k in out:
-                if isinstance(d.get(k), (int, float)) and d[k] > 0:
-                    out[k] = float(d[k])
-            out["source"] = "measured"
-            return out
-        except (OSError, ValueError):
-            pass
-    return dict(FALLBACK_PEAKS, source="fallback")
 
 
 class ClockSampler:
@@ -86,28 +80,6 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def weight_bytes(runner) -> int:
-    """Bytes of every weight one decode step reads once (the token table only through the rows it gathers)."""
-    seen, total = set(), 0
-    for part in runner.model.parts():
-        for v in vars(part).values():
-            if hasattr(v, "data_ptr") and hasattr(v, "element_size") and v.data_ptr() not in seen and v.dim() >= 1:
-                if part is runner.model.embedding and part.weight is not runner.model.head.weight:
-                    continue
-                seen.add(v.data_ptr())
-                total += v.numel() * v.element_size()
-    return total
-
-
-def step_flops(cfg, n_layers, tokens, kv_tokens_sum) -> float:
-    """Multiply-add flops of a step: projections of every token, causal attention, the head on one row."""
-    H, I = cfg["hidden_size"], cfg["intermediate_size"]
-    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
-    per_tok = 2 * (H * (q + 2 * kv) + q * H + 3 * H * I)
-    attn = 4 * q * kv_tokens_sum
-    return n_layers * (per_tok * tokens + attn) + 2 * H * cfg["vocab_size"]
-
-
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -117,6 +89,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run this many of the configuration's layers (0 = all)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long"])
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (no setup.py/pyproject.toml; "
@@ -127,14 +100,18 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "14b-mixed":
+        return mixed_workload(args)
+    if args.workload == "32b-long":
+        return long_context_workload(args)
 
     import numpy as np
     import torch
     from rustingstrata_b200 import Engine
-    from rustingstrata_b200.kernels import ops
+    from rustingstrata_b200.engine import roofline
     from rustingstrata_b200.sampling import SamplingParams
 
-    pk = peaks()
+    pk = roofline.peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
     cfg = dict(QWEN3_8B)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
@@ -146,7 +123,7 @@ def main() -> int:
     runner = eng.runner
     rng = np.random.default_rng(0)
     V = cfg["vocab_size"]
-    wbytes = weight_bytes(runner)
+    wbytes = roofline.weight_bytes(runner.model)
     clocks = ClockSampler()
 
     def prefill_requests(n):
@@ -207,17 +184,20 @@ def main() -> int:
     torch.cuda.synchronize()
     prefill_ms = ev0.elapsed_time(ev1)
     finish_all()
-    pf_flops = step_flops(cfg, n_layers, PROMPT, PROMPT * (PROMPT + 1) / 2)
+    pf_flops = roofline.step_flops(runner.model, [PROMPT], [PROMPT], 1)
     prefill = {"value": PROMPT / prefill_ms * 1000, "tokens": PROMPT, "ms": prefill_ms,
                "frac": pf_flops / (prefill_ms / 1000) / (pk["bf16_tflops"] * 1e12)}
 
     # ---- decode at the headline batch
     ms, e2e_ms, launches, kv_tokens = time_decode(args.batch, args.steps, args.warmup)
-    points = {}
+    points, points_roofline = {}, {}
     if not args.no_points:
         for b in (1, 64):
-            pms, _, _, _ = time_decode(b, max(8, args.steps // 2), args.warmup)
+            pms, _, _, pkv = time_decode(b, max(64, args.steps), args.warmup)
             points[f"decode_b{b}"] = b / pms * 1000
+            pr = roofline.decode_roofline(runner.model, runner.kv_bytes_per_token, pkv, pms, pk)
+            points_roofline[f"decode_b{b}"] = {"ms_per_step": pms, "steps": max(64, args.steps), "achieved": pr["achieved"],
+                                               "frac": pr["frac"]}
     clk = clocks.stop()
 
     step_bytes = wbytes + kv_tokens * runner.kv_bytes_per_token
@@ -241,8 +221,159 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,
+        "points_roofline": points_roofline,
         "clocks": clk,
     }
+    print(json.dumps(rec))
+    return 0
+
+
+def _flat_config(name, cfg, n_layers, full_layers, **more):
+    out = {"model": name, "layers": n_layers, "layers_of_config": full_layers, "hidden": cfg["hidden_size"],
+           "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+           "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": 16,
+           "parallelism": "single-gpu", "weights": "random N(0,0.02) bf16"}
+    out.update(more)
+    return out
+
+
+def mixed_workload(args) -> int:
+    """Qwen3-14B layer sizes: 32 requests, prompts U[128, 4096], portions of 512 beside decode tokens, 256 tokens each
+    at temperature 0.7, context 8,192, all through the engine's own scheduler and entry point."""
+    import numpy as np
+    import torch
+    from rustingstrata_b200 import Engine
+    from rustingstrata_b200.engine import roofline
+    from rustingstrata_b200.sampling import SamplingParams
+    cfg = dict(QWEN3_14B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    n_req, ctx, chunk, n_new = 32, 8192, 512, 256
+    pk = roofline.peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+    eng = Engine(cfg, dtype="bfloat16", random_seed=0, page_size=16, max_tokens=n_req * ctx, max_batch_tokens=chunk + n_req,
+                 max_seqs=n_req, prefill_chunk=chunk)
+    rng = np.random.default_rng(1)
+    V = cfg["vocab_size"]
+
+    def run(seed):
+        lens = rng.integers(128, 4097, size=n_req)
+        rids = [eng.add_request(rng.integers(0, V, size=int(n)).tolist(), n_new, SamplingParams(temp=0.7, seed=seed + i))
+                for i, n in enumerate(lens)]
+        first, steps = {}, []
+        launch = eng._launch
+
+        def spy(batch, prev):
+            steps.append((sum(len(s.tokens) for s in batch if len(s.tokens) > 1 or s.request.prefilling),
+                          sum(1 for s in batch if len(s.tokens) == 1 and not s.request.prefilling)))
+            return launch(batch, prev)
+        eng._launch = spy
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        generated = 0
+        while eng.has_work():
+            eng.step()
+            now = time.perf_counter()
+            for r in eng.scheduler.running:
+                if r.generated and r.rid not in first:
+                    first[r.rid] = now - t0
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        eng._launch = launch
+        eng.runner.check_status()
+        for rid in rids:
+            first.setdefault(rid, wall)
+        generated = n_req * n_new
+        return wall, generated, int(lens.sum()), sorted(first.values()), steps
+
+    run(100)                                   # warm-up: every kernel shape and graph of the workload has run once
+    clocks = ClockSampler()
+    clocks.start()
+    wall, generated, prompt_tokens, ttft, steps = run(200)
+    clk = clocks.stop()
+    pre = [p for p, d in steps]
+    dec = [d for p, d in steps]
+    mix = {"steps": len(steps), "steps_with_prompt_tokens": sum(1 for p in pre if p), "steps_decode_only": sum(1 for p in pre if not p),
+           "steps_mixed": sum(1 for p, d in steps if p and d), "prompt_tokens_per_step_mean": float(np.mean([p for p in pre if p] or [0])),
+           "decode_tokens_per_step_mean": float(np.mean(dec)), "decode_tokens_per_step_max": int(max(dec))}
+    rec = {"metric": "total generated tok/s, continuous batch of 32 (Qwen3-14B sizes, bf16, random weights)",
+           "value": generated / wall, "unit": "tok/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+           "data": "synthetic", "workload": "14b-mixed", "wall_s": wall, "generated_tokens": generated,
+           "prompt_tokens": prompt_tokens, "all_tokens_per_s": (generated + prompt_tokens) / wall,
+           "ttft_s": {"mean": float(np.mean(ttft)), "max": float(ttft[-1]), "min": float(ttft[0])},
+           "step_mix": mix, "preemptions": eng.scheduler.preemptions,
+           "config": _flat_config("qwen3-14b-sizes", cfg, cfg["num_hidden_layers"], full_layers, requests=n_req, seq_len=ctx,
+                                  prompt_len="U[128,4096]", chunk=chunk, new_tokens=n_new, temperature=0.7,
+                                  peaks=pk["source"]),
+           "clocks": clk}
+    print(json.dumps(rec))
+    return 0
+
+
+def long_context_workload(args) -> int:
+    """Qwen3-32B layer sizes: 8 requests with 12,000-token prompts, then 256 greedy tokens each, context 16,384."""
+    import numpy as np
+    import torch
+    from rustingstrata_b200 import Engine
+    from rustingstrata_b200.engine import roofline
+    from rustingstrata_b200.sampling import SamplingParams
+    cfg = dict(QWEN3_32B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    n_req, ctx, prompt, n_new = 8, 16384, 12000, 256
+    pk = roofline.peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+    eng = Engine(cfg, dtype="bfloat16", random_seed=0, page_size=16, max_tokens=n_req * ctx, max_batch_tokens=2048,
+                 max_seqs=n_req)
+    runner = eng.runner
+    rng = np.random.default_rng(2)
+    V = cfg["vocab_size"]
+
+    def prefill(n_tokens):
+        for _ in range(n_req):
+            eng.add_request(rng.integers(0, V, size=n_tokens).tolist(), ctx - n_tokens, SamplingParams())
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while eng.scheduler.waiting or any(r.prefilling for r in eng.scheduler.running):
+            eng.step()
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0
+
+    def finish_all():
+        eng.drain()
+        for r in list(eng.scheduler.running):
+            eng.scheduler.running.remove(r)
+            runner.release(r.rid)
+            eng._samplers.pop(r.rid, None)
+
+    # the same decode step with next to no cache: what is left of the step when attention has nothing to read
+    prefill(16)
+    short_ms = eng.decode_steps_device_timed(64, warmup=8)
+    finish_all()
+    clocks = ClockSampler()
+    clocks.start()
+    prefill_s = prefill(prompt)
+    for _ in range(args.warmup):
+        eng.step()
+    kv0 = sum(runner.length(r.rid) for r in eng.scheduler.running)
+    steps = n_new - args.warmup - 8
+    ms = eng.decode_steps_device_timed(steps, warmup=3)
+    kv1 = sum(runner.length(r.rid) for r in eng.scheduler.running)
+    clk = clocks.stop()
+    runner.check_status()
+    roof = roofline.decode_roofline(runner.model, runner.kv_bytes_per_token, (kv0 + kv1) / 2.0, ms, pk)
+    kv_bytes = (kv0 + kv1) / 2.0 * runner.kv_bytes_per_token
+    rec = {"metric": "decode tok/s at batch 8 after 12,000-token prompts (Qwen3-32B sizes, bf16, random weights)",
+           "value": n_req / ms * 1000, "unit": "tok/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+           "data": "synthetic", "workload": "32b-long", "steps": steps, "ms_per_step": ms,
+           "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")},
+           "kv_share_of_bytes": kv_bytes / roof["bytes_per_step"],
+           "ms_per_step_at_16_keys": short_ms, "long_cache_share_of_step": (ms - short_ms) / ms,
+           "long_cache_gbs": kv_bytes / ((ms - short_ms) / 1000) / 1e9 if ms > short_ms else None,
+           "prefill": {"tokens": n_req * prompt, "s": prefill_s, "value": n_req * prompt / prefill_s},
+           "config": _flat_config("qwen3-32b-sizes", cfg, cfg["num_hidden_layers"], full_layers, global_batch=n_req,
+                                  seq_len=ctx, prompt_len=prompt, new_tokens=n_new, peaks=pk["source"]),
+           "clocks": clk}
     print(json.dumps(rec))
     return 0
 

@@ -24,6 +24,8 @@ def _engine_flags(ap):
                     help="no model folder: draw the weights on the device from --config and --weights-seed")
     ap.add_argument("--config", default=None, help="config.json of the architecture (with --random-weights)")
     ap.add_argument("--weights-seed", type=int, default=0)
+    ap.add_argument("--weights-std", type=float, default=0.02, help="spread of the drawn matrices (with --random-weights)")
+    ap.add_argument("--weights-norm-std", type=float, default=0.0, help="spread of the drawn norm scales around 1")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     ap.add_argument("--ctx", type=int, default=4096, help="cache size in tokens")
     ap.add_argument("--chunk", type=int, default=None, help="prefill portion in tokens [default: the token budget]")
@@ -55,14 +57,16 @@ def _sampling(args):
 def _make_engine(args, ctx=None, max_seqs=None):
     from .engine import Engine
     ctx = ctx or args.ctx
-    dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(args.dtype, args.dtype)
+    from .dtypes import engine_dtype_name
+    dtype = engine_dtype_name(args.dtype)
     kw = dict(dtype=dtype, page_size=args.page_size, max_tokens=ctx, max_batch_tokens=min(max(ctx, 64), 8192),
               max_seqs=max_seqs or args.parallel, prefill_chunk=args.chunk)
     if args.random_weights:
         if not args.config:
             raise SystemExit("--random-weights needs --config config.json")
         with open(args.config) as f:
-            return Engine(json.load(f), random_seed=args.weights_seed, **kw)
+            return Engine(json.load(f), random_seed=args.weights_seed, random_std=args.weights_std,
+                          random_norm_std=args.weights_norm_std, **kw)
     if not args.model:
         raise SystemExit("give --model DIR, or --random-weights --config config.json")
     return Engine(args.model, **kw)
@@ -119,6 +123,9 @@ def cmd_bench(args):
     for n in pps:
         rec = eng.bench([n], args.tg, args.reps, args.batch)[0]
         print(f"pp {n:6d}: prefill {_stat(rec['prefill_tok_s'])} tok/s | tg {args.tg}: decode {_stat(rec['decode_tok_s'])} tok/s")
+        rf = rec["roofline"]
+        print(f"          prefill {rf['prefill']['achieved']:.1f} TFLOP/s = {rf['prefill']['frac']:.3f} of the tensor peak | decode "
+              f"{rf['decode']['achieved']:.0f} GB/s = {rf['decode']['frac']:.3f} of the HBM peak ({rf['decode']['peaks']} peaks)")
         results.append(rec)
     if args.json_out:
         rec = {"schema": "rustingstrata_b200.bench.v1", "model": args.model or args.config, "dtype": args.dtype, "ctx": ctx, "tg": args.tg,
@@ -167,6 +174,10 @@ def cmd_init_random(args):
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":          # everything behind the word belongs to trace replay's own parser
+        from .replay import main as replay_main
+        return replay_main(argv[1:])
     ap = argparse.ArgumentParser(prog="rustingstrata_b200", description="B200 inference engine for the Qwen3 dense decoder")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate", help="generation (greedy unless --temp)")
@@ -190,9 +201,7 @@ def main(argv=None) -> int:
     _engine_flags(s)
     s.add_argument("--input", default="-")
     s.set_defaults(fn=cmd_score)
-    r = sub.add_parser("replay", help="trace replay (same as bin/trace_run)")
-    r.add_argument("rest", nargs=argparse.REMAINDER)
-    r.set_defaults(fn=lambda a: __import__("rustingstrata_b200.replay", fromlist=["main"]).main(a.rest))
+    sub.add_parser("replay", help="trace replay (same as bin/trace_run; its options follow the word)")
     i = sub.add_parser("init-random", help="write a model folder with random weights from a config.json and a seed")
     i.add_argument("--config", required=True)
     i.add_argument("--out", required=True)

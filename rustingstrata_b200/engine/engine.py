@@ -252,10 +252,14 @@ class Engine:
         times: ``batch`` prompts of seeded random ids are run to the end of their prompts (timed: prefill tok/s), then
         ``tg`` tokens each are decoded greedily (timed: decode tok/s over all requests).  Wall-clock times around
         ``step`` with a device synchronisation on both sides.  Returns one record per prompt length with mean, min
-        and max of both rates."""
+        and max of both rates, and ``roofline``: the decode step's bytes (weights once, the live cache) over the HBM
+        peak and the prompts' multiply-adds over the tensor peak, both at the mean rate."""
         import time
+        from . import roofline
         rng = np.random.default_rng(seed)
         out = []
+        pk = roofline.peaks()
+        model = self.runner.model
         for n in pp:
             pre, dec = [], []
             for _ in range(reps):
@@ -279,7 +283,15 @@ class Engine:
                 pre.append(n * batch / (t1 - t0))
                 dec.append(batch * steps / (t2 - t1))
             stat = lambda xs: {"mean": sum(xs) / len(xs), "min": min(xs), "max": max(xs)}  # noqa: E731
-            out.append({"pp": int(n), "tg": int(tg), "batch": int(batch), "prefill_tok_s": stat(pre), "decode_tok_s": stat(dec)})
+            rec = {"pp": int(n), "tg": int(tg), "batch": int(batch), "prefill_tok_s": stat(pre), "decode_tok_s": stat(dec)}
+            pre_ms = n * batch / rec["prefill_tok_s"]["mean"] * 1000
+            dec_ms = batch / rec["decode_tok_s"]["mean"] * 1000 if rec["decode_tok_s"]["mean"] > 0 else float("inf")
+            rec["roofline"] = {
+                "prefill": roofline.prefill_roofline(model, [n] * batch, [n] * batch, batch, pre_ms, pk, self.config.dtype),
+                # the cache a decode step reads grows from n to n + tg tokens per request: the middle stands for all
+                "decode": roofline.decode_roofline(model, self.runner.kv_bytes_per_token, batch * (n + tg / 2.0), dec_ms, pk),
+            }
+            out.append(rec)
         return out
 
     # ------------------------------------------------------------------ device-resident greedy decode

@@ -106,6 +106,16 @@ class PagedAttention(Mixer):
     def cache_need(self):
         return CacheNeed(self.n_kv, self.hd, self.window or None)
 
+    def mixing_flops(self, q_lens, kv_lens) -> float:
+        """Flops of scores and weighted sums for sequences that add q_lens[i] queries and then hold kv_lens[i] keys:
+        4 * heads * head size per (query, visible key) pair."""
+        pairs = 0.0
+        for q, kv in zip(np.asarray(q_lens, dtype=np.int64), np.asarray(kv_lens, dtype=np.int64)):
+            pos = np.arange(kv - q, kv, dtype=np.float64)                  # query positions; each sees pos + 1 keys
+            seen = pos + 1 if not self.window else np.minimum(pos + 1, self.window)
+            pairs += float(seen.sum())
+        return 4.0 * self.n_heads * self.hd * pairs
+
     # ---------------------------------------------------------------- planning
     def plan_key(self):
         if self.q_per_cta is None:
