@@ -9,7 +9,11 @@
 #include <unordered_map>
 #include <vector>
 
-constexpr unsigned long long RS_WAIT_LIMIT_NS = 2000000000ull;
+// the limit of every bounded wait; a build may set another (the wait-probe library of the tests uses 2 ms)
+#ifndef RS_WAIT_LIMIT_NS_VALUE
+#define RS_WAIT_LIMIT_NS_VALUE 2000000000ull
+#endif
+constexpr unsigned long long RS_WAIT_LIMIT_NS = RS_WAIT_LIMIT_NS_VALUE;
 constexpr int RS_TMA_BOX_K = 64;          // 64 bf16 = 128 bytes = one swizzle row
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

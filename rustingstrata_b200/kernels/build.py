@@ -33,6 +33,9 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "core": {"sources": ["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "sampling.cu"], "link": []},
     # tensor-core paths of the bfloat16 engine; the 32-bit engine never loads this library
+    # not loaded by the engine: one kernel whose wait is never satisfied, built with a 2 ms limit, so that a test can
+    # see the bounded-wait path end in a status bit and leave the context usable
+    "probe": {"sources": ["wait_probe.cu"], "link": [], "flags": ["-DRS_WAIT_LIMIT_NS_VALUE=2000000ull"]},
     "bf16": {"sources": ["gemm_tcgen05.cu", "skinny_gemm_tma.cu", "mid_gemm_tcgen05.cu", "attention_decode_mma.cu", "attention_prefill_mma.cu", "attention_prefill_tc.cu"], "link": []},
 }
 

@@ -678,6 +678,20 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
         _stream()), "attention_decode_bf16", 2)
 
 
+# ----------------------------------------------------------------------------- the bounded-wait probe
+def wait_probe(status: torch.Tensor) -> dict:
+    """Runs the probe kernel of csrc/wait_probe.cu (a wait nobody satisfies, limit 2 ms) with ``status`` as its status
+    word and returns {"satisfied": bool, "waited_us": int, "limit_us": int} once it has ended.  For tests."""
+    lib = load_library("probe")
+    lib.rs_wait_probe.argtypes = [c_void_p, c_void_p, c_void_p]
+    lib.rs_wait_probe_limit_ns.restype = ctypes.c_ulonglong
+    _cuda(status)
+    outcome = torch.full((2,), -1, dtype=torch.int32, device=status.device)
+    _check(lib.rs_wait_probe(_ptr(status), _ptr(outcome), _stream()), "wait_probe")
+    got = outcome.cpu().tolist()
+    return {"satisfied": got[0] == 1, "waited_us": got[1], "limit_us": int(lib.rs_wait_probe_limit_ns() // 1000)}
+
+
 # ----------------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, n_rows: int, out: torch.Tensor, status: torch.Tensor,
            temps: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None) -> None:

@@ -237,6 +237,29 @@ def test_one_long_request_beside_short_ones_in_decode_steps(tiny_models, dtype):
     print(f"{dtype}: worst {worst:.3e}")
 
 
+def test_a_wait_that_runs_out_becomes_a_step_error_and_the_engine_goes_on(tiny_models):
+    """Every wait inside the tensor-core kernels is bounded.  A probe kernel built with a 2 ms limit waits on a barrier
+    nobody arrives at, with the runner's status word: the wait gives up, the kernel ends, the status bit turns into a
+    StepError at the next check, and the very next step on the same context runs and is right."""
+    from rustingstrata_b200.engine import StepEntry, StepError
+    from rustingstrata_b200.kernels import ops
+    cfg, w = P.read_model(tiny_models["D"])
+    eng = engine(tiny_models, "D", "bfloat16")
+    toks = random_tokens(cfg["vocab_size"], 40, 8)
+    ref = P.forward_logits(cfg, w, toks)
+    eng.step_raw([StepEntry("x", toks[:30], [])])
+    eng.runner.check_status()
+    res = ops.wait_probe(eng.runner.status)
+    assert not res["satisfied"] and res["limit_us"] == 2000 and 2000 <= res["waited_us"] < 200_000, res
+    with pytest.raises(StepError, match="bounded wait"):
+        eng.runner.check_status()
+    eng.runner.check_status()                                  # the word was cleared: one report per event
+    rows = eng.step_raw([StepEntry("x", toks[30:], list(range(10)))]).cpu().numpy()
+    eng.runner.check_status()
+    assert rel_err(rows, ref[30:]) <= TOL["bfloat16"]
+    eng.release("x")
+
+
 def test_step_errors_leave_the_cache_untouched(tiny_models):
     from rustingstrata_b200.cache import OutOfPages
     from rustingstrata_b200.engine import StepEntry, StepError

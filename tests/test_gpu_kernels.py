@@ -347,6 +347,44 @@ def test_attention_finds_a_far_key_among_hundreds(dtype, far):
     assert (got[0].double().cpu() - want[0]).abs().max() < 0.05
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window", [116, 128, 100, 77])
+@pytest.mark.parametrize("inside", [True, False])
+def test_window_edge_in_the_tensor_core_kernels(hd, window, inside):
+    """The tcgen05 portion kernel and the TMA-fed single-query kernel (head 64/128, pages of 16, bfloat16) with one key
+    that answers every query, placed on the oldest position a window still shows (it must carry the result) or one
+    before it (it must not be seen at all).  The lengths put that edge on a boundary between 128-key splits and between
+    pages (500 keys, window 116: key 384), on a page boundary only (window 100: key 400), and inside a page."""
+    o = ops()
+    n_q, n_kv, page = 8, 2, 16
+    assert o.attention_prefill_kernel(torch.bfloat16, n_q, n_kv, hd, page) == "tc"
+    assert o.attention_decode_fast_ok(torch.bfloat16, n_q, n_kv, hd, page)
+    # (keys, queries): single queries at three lengths, and a portion whose queries straddle the marked key's edge
+    seqs = [(500, 1), (1024 + window, 1), (window + 7, 1), (700, 64), (300, 150)]
+    edge = [kv - ql - window + 1 if ql > 1 else kv - window for kv, ql in seqs]       # oldest key the first query sees
+    marked = [e + (20 if ql > 1 else 0) - (0 if inside else 1) for e, (kv, ql) in zip(edge, seqs)]
+
+    def boost(s, t):
+        if s is None:
+            t[:, :, 0] = 6.0
+        else:
+            t[:, :, 0] = 0.0
+            t[marked[s], :, 0] = 40.0
+    got, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, boost=boost)
+    close(got, want, 1.5e-2)
+    # the construction bites: for the single queries the marked key either is the answer or is not there
+    starts = np.cumsum([0] + [ql for _, ql in seqs])
+    for s, (kv, ql) in enumerate(seqs[:3]):
+        w = want[starts[s]]
+        assert (got[starts[s]].double().cpu() - w).abs().max() < 0.05
+    # in a portion, the marked key is seen by the first queries and has left the window of the later ones
+    for s in (3, 4):
+        kv, ql = seqs[s]
+        first_pos = kv - ql
+        sees = [marked[s] > first_pos + i - window and marked[s] <= first_pos + i for i in range(ql)]
+        assert any(sees) and not all(sees)
+
+
 @pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (32, 8, 128, 16), (16, 1, 64, 8), (9, 1, 64, 16), (3, 3, 128, 32),
                                               (4, 1, 64, 128), (12, 4, 64, 64), (16, 1, 128, 8)])
 @pytest.mark.parametrize("window", [0, 100])
