@@ -26,75 +26,10 @@
 //
 // Reference counterpart: gemv_bf16 / gemvn_bf16 (src/cuda/kernels.cu:307-329,826-853): one warp per row on CUDA
 // cores, each weight read once for up to 4 inputs.
-#include "tma_helpers.cuh"
-#include "mma_helpers.cuh"
-#include "stream_k_partials.cuh"
+#include "skinny_tile.cuh"
 
 namespace {
-using rs_streamk::first_unit;
-using rs_streamk::cta_of_unit;
-constexpr int TILE_N = 64;                 // rows of W per unit
-constexpr int BOX_K = 64;                  // k per TMA box (one 128-byte swizzle row)
-constexpr int BOXES = 2;                   // boxes per unit
-constexpr int TILE_K = BOX_K * BOXES;      // k per unit
-constexpr int W_BOX_BYTES = TILE_N * BOX_K * 2;
-constexpr int W_BYTES = W_BOX_BYTES * BOXES;
-constexpr int CONSUMER_WARPS = 4;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int SMEM_BUDGET = 200 * 1024;
-
-enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
-
-struct SkinnyParams {
-    void* C; long ldc;
-    int M, N, K;
-    int stages;
-    float* workspace;          // [grid][2][8 NT activation rows][TILE_N] float32 partials
-    int* status;
-};
-
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-
-template <int NT, int EPI>
-__device__ __forceinline__ void store_tile(const SkinnyParams& p, const float (&acc)[NT][4], int tile, int warp, int g, int t) {
-    const int na = tile * TILE_N + 16 * warp + g, nb = na + 8;
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        const int m0 = 8 * j + 2 * t;
-        if (EPI == EPI_SWIGLU_BF16) {
-            // rows of W alternate gate, up: lanes g and g ^ 1 hold a pair; the even one writes
-            float partner[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) partner[i] = __shfl_xor_sync(0xffffffffu, acc[j][i], 4);
-            if ((g & 1) == 0) {
-                __nv_bfloat16* out = (__nv_bfloat16*)p.C;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int m = m0 + (i & 1), n = (i >> 1) ? nb : na;
-                    if (m < p.M && n + 1 < p.N) {
-                        const float gate = acc[j][i], up = partner[i];
-                        out[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
-                    }
-                }
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int m = m0 + (i & 1), n = (i >> 1) ? nb : na;
-                if (m < p.M && n < p.N) {
-                    const size_t o = (size_t)m * p.ldc + n;
-                    if (EPI == EPI_STORE_BF16) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(acc[j][i]);
-                    else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = acc[j][i];
-                    else ((float*)p.C)[o] += acc[j][i];
-                }
-            }
-        }
-    }
-}
+using namespace rs_skinny;
 
 template <int NT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -186,26 +121,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (ok) ok = mbar_wait(full_bar(s), phase, abort_flag, p.status);
             const uint32_t wst = base + s * STAGE_BYTES, xst = wst + W_BYTES;
             if (ok) {
-#pragma unroll
-            for (int b = 0; b < BOXES; ++b) {
-                const uint32_t row_a = wst + b * W_BOX_BYTES + (16 * warp + g) * 128, row_b = row_a + 8 * 128;
-                const uint32_t xb = xst + b * X_BOX_BYTES;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    // lane t takes the 16-byte chunks 2t and 2t+1 of the row (the same for W and A, whatever g is:
-                    // the k slots of the MMA pair lane (g, t) of one operand with lane (g', t) of the other);
-                    // with the swizzle the 8 lanes of a quarter-warp then fall into 8 different bank groups
-                    const uint32_t chunk = (uint32_t)(((2 * t + half) ^ g) << 4);
-                    const uint4 wa = lds128(row_a + chunk), wb = lds128(row_b + chunk);
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        const uint4 x = lds128(xb + (8 * j + g) * 128 + chunk);
-                        const uint32_t a0[4] = {wa.x, wb.x, wa.y, wb.y}, a1[4] = {wa.z, wb.z, wa.w, wb.w};
-                        if (b == 0) { mma16816(acc[j], a0, x.x, x.y); mma16816(acc[j], a1, x.z, x.w); }
-                        else { mma16816(acc2[j], a0, x.x, x.y); mma16816(acc2[j], a1, x.z, x.w); }
-                    }
-                }
-            }
+                consume_unit<NT>(wst, xst, warp, g, t, acc, acc2);
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(s));
             }
@@ -224,11 +140,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 } else {
                     // shared with other CTAs: my float32 partial goes to the workspace; skinny_reduce_kernel adds them up
                     const int slot = (u0 >= tile_first) ? 0 : 1;            // 0: the tile my range starts in
-                    float* mine = p.workspace + ((size_t)blockIdx.x * 2 + slot) * (8 * NT * TILE_N) + 16 * warp + g;
-#pragma unroll
-                    for (int j = 0; j < NT; ++j)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) __stcg(mine + (8 * j + 2 * t + (i & 1)) * TILE_N + 8 * (i >> 1), acc[j][i]);
+                    store_partial<NT>(p.workspace, blockIdx.x, slot, warp, g, t, acc);
                 }
 #pragma unroll
                 for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
@@ -254,42 +166,10 @@ __global__ void __launch_bounds__(CONSUMER_WARPS * 32) skinny_reduce_kernel(cons
     // who shares which tile follows from the shape alone: worked out while the product is still running
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int KB = (p.K + TILE_K - 1) / TILE_K;
-    const int U = ((p.N + TILE_N - 1) / TILE_N) * KB;
-    const int b = blockIdx.x + 1;                              // boundary between CTA b - 1 and CTA b
-    const int ub = first_unit(b, U, G);
-    const int tile = ub / KB, tile_first = tile * KB;
-    // on a tile's edge nobody shares because of this boundary; if an earlier boundary lies in the tile, its CTA acts
-    const bool acts = ub % KB != 0 && first_unit(b - 1, U, G) <= tile_first;
-    const int c_first = b - 1, c_last = acts ? cta_of_unit(tile_first + KB - 1, U, G) : b - 1;
+    const SharedTile st = shared_tile_of_boundary(blockIdx.x + 1, p.N, p.K, G);
     pdl_wait();                                                // every CTA waits, so that this grid never ends before the product
-    if (!acts) return;
-    float acc[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-    constexpr int CH = NT == 1 ? 4 : (NT == 2 ? 2 : 1);       // contributors whose loads are in flight together
-    for (int c0 = c_first; c0 <= c_last; c0 += CH) {
-        float v[CH][NT][4];
-#pragma unroll
-        for (int cc = 0; cc < CH; ++cc) {
-            const int c = min(c0 + cc, c_last);
-            const int cslot = (first_unit(c, U, G) >= tile_first) ? 0 : 1;
-            const float* src = p.workspace + ((size_t)c * 2 + cslot) * (8 * NT * TILE_N) + 16 * warp + g;
-#pragma unroll
-            for (int j = 0; j < NT; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) v[cc][j][i] = ld_dep(src + (8 * j + 2 * t + (i & 1)) * TILE_N + 8 * (i >> 1));
-        }
-#pragma unroll
-        for (int cc = 0; cc < CH; ++cc)
-            if (c0 + cc <= c_last) {
-#pragma unroll
-                for (int j = 0; j < NT; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[j][i] += v[cc][j][i];
-            }
-    }
-    store_tile<NT, EPI>(p, acc, tile, warp, g, t);
+    if (!st.acts) return;
+    finish_shared_tile<NT, EPI>(p, st, G, warp, g, t);
 }
 
 template <int NT> constexpr int stage_bytes() { return W_BYTES + 8 * NT * TILE_K * 2; }

@@ -93,6 +93,7 @@ class ModelRunner:
         self._graphs: Dict = {}
         self.graph_replays = 0
         self.kernels_replayed = 0           # kernels this runner launched through graph replays
+        self.chain_kernels = 0              # chained-product kernels launched outside graph replays
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -245,10 +246,21 @@ class ModelRunner:
         try:
             ctx, layout = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R, graphable)
 
+            chain = (ops.CHAIN_DECODE and self.dtype == torch.bfloat16 and T <= ops.chain_max_rows()
+                     and self.model.chain_safe)
+
             def run():
                 if device_tokens is not None:
                     ctx.token_ids[:T].copy_(device_tokens[:T], non_blocking=True)
-                out = self.model.forward(ctx)
+                if chain:
+                    # a small decode step: the products between two attention calls leave as one persistent kernel
+                    ops.begin_chain(self.status)
+                    try:
+                        out = self.model.forward(ctx)
+                    finally:
+                        self.chain_kernels += ops.end_chain()
+                else:
+                    out = self.model.forward(ctx)
                 if post is not None:
                     post(out, R)
                 return out
@@ -367,6 +379,8 @@ class ModelRunner:
         code = int(self._status_host[0])
         if code:
             self.status.zero_()
+            if code & ops.STATUS_WAIT_EXPIRED:
+                ops.reset_chain_barrier()
             what = [n for b, n in ((ops.STATUS_BAD_TOKEN, "token id outside the vocabulary"),
                                    (ops.STATUS_BAD_PAGE, "block table entry outside the page pool"),
                                    (ops.STATUS_WAIT_EXPIRED, "a bounded wait inside a kernel gave up"),

@@ -36,7 +36,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     # not loaded by the engine: one kernel whose wait is never satisfied, built with a 2 ms limit, so that a test can
     # see the bounded-wait path end in a status bit and leave the context usable
     "probe": {"sources": ["wait_probe.cu"], "link": [], "flags": ["-DRS_WAIT_LIMIT_NS_VALUE=2000000ull"]},
-    "bf16": {"sources": ["gemm_tcgen05.cu", "skinny_gemm_tma.cu", "mid_gemm_tcgen05.cu", "attention_decode_mma.cu", "attention_prefill_mma.cu", "attention_prefill_tc.cu"], "link": []},
+    "bf16": {"sources": ["gemm_tcgen05.cu", "skinny_gemm_tma.cu", "decode_chain.cu", "mid_gemm_tcgen05.cu", "attention_decode_mma.cu", "attention_prefill_mma.cu", "attention_prefill_tc.cu"], "link": []},
 }
 
 

@@ -40,6 +40,9 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
 
 
 def _stream() -> c_void_p:
+    """The stream to launch on.  Every launcher asks for it right before its launch, so this is also where a recorded
+    chain of decode products (see :func:`begin_chain`) is sent off before any other kernel can overtake it."""
+    flush_chain()
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -136,6 +139,17 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     ``pending``: a :class:`PendingSum` still owed to ``x``.  If it covers exactly the rows that are normed, one kernel
     adds the partial sums and norms the rows (the same bits as the two kernels in turn); else it is finished first."""
     _cuda(x, weight, out, rows)
+    if _ACTIVE_CHAIN is not None and _ACTIVE_CHAIN.ops and pending is None and rows is None:
+        nr = n_rows if n_rows is not None else x.shape[0]
+        lib = bf16lib()
+        if (nr <= lib.rs_decode_chain_max_rows() and x.dtype == torch.float32 and out.dtype == torch.bfloat16
+                and x.dim() == 2 and out.dim() == 2 and x.stride(1) == 1 and out.stride(1) == 1
+                and x.shape[1] == weight.numel() == out.shape[1] and x.shape[1] % 4 == 0
+                and x.shape[1] <= lib.rs_decode_chain_max_norm_width() and x.stride(0) % 4 == 0 and out.stride(0) % 4 == 0
+                and x.data_ptr() % 16 == 0 and out.data_ptr() % 8 == 0 and weight.data_ptr() % 16 == 0
+                and weight.is_contiguous() and weight.dtype in (torch.float32, torch.bfloat16) and nr <= out.shape[0]):
+            _ACTIVE_CHAIN.add_rmsnorm(x, weight, eps, out, nr)
+            return
     if pending is not None and not pending.done:
         nr = n_rows if n_rows is not None else (out.shape[0] if rows is not None else x.shape[0])
         lib = bf16lib()
@@ -283,6 +297,7 @@ def bf16lib():
         lib.rs_skinny_finish_rmsnorm_supported.argtypes = [c_void_p, c_long, c_int, c_void_p, c_void_p, c_long]
         lib.rs_skinny_finish_rmsnorm.argtypes = [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
                                                  c_float, c_void_p, c_long, c_void_p]
+        lib.rs_decode_chain.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         lib.rs_mid_gemm_bf16.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                          c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.rs_mid_finish.argtypes = lib.rs_skinny_finish.argtypes
@@ -479,6 +494,145 @@ def _default_status(device) -> torch.Tensor:
     return t
 
 
+# ----------------------------------------------------------------------------- a chain of decode products in one kernel
+class RsChainOp(ctypes.Structure):
+    """One operation of a chain, as csrc/decode_chain.cu takes it."""
+    _fields_ = [("type", c_int), ("M", c_int), ("N", c_int), ("K", c_int), ("epi", c_int), ("owed", c_int), ("w_dt", c_int),
+                ("reserved", c_int), ("lda", c_long), ("a_rows", c_long), ("ldw", c_long), ("ldc", c_long), ("out_stride", c_long),
+                ("A", c_void_p), ("W", c_void_p), ("C", c_void_p), ("w", c_void_p), ("out", c_void_p), ("eps", c_float),
+                ("reserved2", c_int)]
+
+
+CHAIN_GEMV, CHAIN_REDUCE, CHAIN_ROWNORM = 0, 1, 2
+CHAIN_DECODE = False     # whether the engine chains the products of a decode step of up to 8 tokens (begin_chain); measured
+                         # slower than the separate kernels under programmatic dependent launch, so it is off
+_CHAIN_BUFFERS = {}
+
+
+class _Chain:
+    """The products of up to 8 rows, and the row norms between them, that have been asked for since the last kernel of
+    another kind: they wait here and leave as ONE persistent kernel (csrc/decode_chain.cu) when anything else is about
+    to be launched, so that the weights of a whole run of dependent products stream without a kernel boundary."""
+
+    def __init__(self, status: torch.Tensor):
+        self.status = status
+        self.ops = []            # RsChainOp
+        self.keep = []           # the tensors the operations point into
+        self.n_products = 0
+        self.open_product = None   # the last op, if it is a product whose shared tiles nobody has been told to finish
+        self.launches = 0
+
+    def _room(self, n_ops: int, n_products: int = 0) -> None:
+        lib = bf16lib()
+        if (len(self.ops) + n_ops > lib.rs_decode_chain_max_ops()
+                or self.n_products + n_products > lib.rs_decode_chain_max_products()):
+            self.flush()
+
+    def _close_product(self) -> None:
+        """The product recorded last leaves its shared tiles to a REDUCE operation (nobody else took them)."""
+        g = self.open_product
+        if g is not None:
+            self.open_product = None
+            r = RsChainOp.from_buffer_copy(g)
+            r.type = CHAIN_REDUCE
+            self.ops.append(r)
+
+    def add_product(self, a, weight, out, n_rows, epi) -> None:
+        self._close_product()
+        self._room(2, 1)
+        N, K = weight.shape
+        op = RsChainOp(type=CHAIN_GEMV, M=n_rows, N=N, K=K, epi=epi, lda=a.stride(0), a_rows=a.shape[0], ldw=weight.stride(0),
+                       ldc=out.stride(0), A=a.data_ptr(), W=weight.data_ptr(), C=out.data_ptr())
+        self.ops.append(op)
+        self.keep += [a, weight, out]
+        self.n_products += 1
+        self.open_product = op
+
+    def add_rmsnorm(self, x, weight, eps, out, n_rows) -> None:
+        g = self.open_product
+        owed = (g is not None and g.epi == EPI_ADD_F32 and g.C == x.data_ptr() and g.ldc == x.stride(0) and g.M == n_rows
+                and g.N == x.shape[1])
+        if owed:
+            self.open_product = None                 # the norm adds the product's partial sums while it reads the rows
+        else:
+            self._close_product()
+        self._room(1)
+        self.ops.append(RsChainOp(type=CHAIN_ROWNORM, M=n_rows, N=x.shape[1], K=g.K if owed else 1, owed=1 if owed else 0,
+                                  w_dt=dtype_code(weight), ldc=x.stride(0), out_stride=out.stride(0), C=x.data_ptr(),
+                                  w=weight.data_ptr(), out=out.data_ptr(), eps=float(eps)))
+        self.keep += [x, weight, out]
+
+    def flush(self) -> None:
+        if not self.ops:
+            return
+        self._close_product()
+        ops, self.ops, keep, self.keep = self.ops, [], self.keep, []
+        self.n_products = 0
+        arr = (RsChainOp * len(ops))(*ops)
+        dev = self.status.device
+        bufs = _CHAIN_BUFFERS.get(dev)
+        if bufs is None:
+            bufs = _CHAIN_BUFFERS[dev] = torch.zeros(2, dtype=torch.int32, device=dev)
+        ws = _skinny_scratch(dev)
+        global _FLUSHING
+        _FLUSHING = True
+        try:
+            stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+            _check(bf16lib().rs_decode_chain(ctypes.cast(arr, c_void_p), len(ops), _ptr(ws), _ptr(bufs), _ptr(self.status), stream),
+                   "decode_chain")
+        finally:
+            _FLUSHING = False
+        self.launches += 1
+        del keep
+
+
+_ACTIVE_CHAIN: Optional[_Chain] = None
+_FLUSHING = False
+
+
+def chain_max_rows() -> int:
+    return int(bf16lib().rs_decode_chain_max_rows())
+
+
+def begin_chain(status: torch.Tensor) -> None:
+    """From here to :func:`end_chain`, products of up to 8 bfloat16 rows (``linear``, ``linear_swiglu``) and the row
+    norms between them are recorded instead of launched, and leave as one kernel when any other kernel of this module is
+    asked for or the chain is ended.  Only for callers that touch the tensors involved through this module alone in
+    between (torch operations on them would not see the recorded work)."""
+    global _ACTIVE_CHAIN
+    if _ACTIVE_CHAIN is not None:
+        raise KernelError("a chain of decode products is already being recorded")
+    _ACTIVE_CHAIN = _Chain(status)
+
+
+def end_chain() -> int:
+    """Launches what is recorded and stops recording; returns the number of chain kernels launched since begin_chain."""
+    global _ACTIVE_CHAIN
+    ch, _ACTIVE_CHAIN = _ACTIVE_CHAIN, None
+    if ch is None:
+        return 0
+    ch.flush()
+    return ch.launches
+
+
+def flush_chain() -> None:
+    if _ACTIVE_CHAIN is not None and not _FLUSHING:
+        _ACTIVE_CHAIN.flush()
+
+
+def reset_chain_barrier() -> None:
+    """After a chain kernel gave up on a wait its arrival counter may be left mid-count: set it back."""
+    for t in _CHAIN_BUFFERS.values():
+        t.zero_()
+
+
+def _chain_takes_product(a, weight, out, n_rows, swiglu: bool) -> bool:
+    lib = bf16lib()
+    return (_ACTIVE_CHAIN is not None and n_rows <= lib.rs_decode_chain_max_rows() and tensor_core_shape_ok(a, weight)
+            and weight.numel() < SKINNY_MAX_WEIGHT and out.dtype in (torch.bfloat16, torch.float32)
+            and a.is_cuda and weight.is_cuda and out.is_cuda)
+
+
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, accumulate: bool = False,
            status: Optional[torch.Tensor] = None, may_defer: bool = False) -> Optional[PendingSum]:
     """The engine's matrix product: the tensor-core kernels for bfloat16 operands whose rows are 16-byte
@@ -486,6 +640,10 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int
     CUDA-core kernel for everything else
     (the 32-bit engine, float32-stored weights, odd widths).  ``may_defer``: the caller hands a :class:`PendingSum`
     on to the next reader of ``out`` if the kernel that runs can leave one (else None comes back and ``out`` is whole)."""
+    if _chain_takes_product(a, weight, out, n_rows, False):
+        _check_product(a, weight, out, n_rows, False)
+        _ACTIVE_CHAIN.add_product(a, weight, out, n_rows, _epilogue_code(out, accumulate, False))
+        return None
     if tensor_core_shape_ok(a, weight) and out.dtype in (torch.bfloat16, torch.float32):
         if n_rows <= SKINNY_ROWS and weight.numel() < SKINNY_MAX_WEIGHT:
             defer = may_defer and DEFER_SUMS and accumulate and out.dtype == torch.float32 and n_rows <= SKINNY_DEFER_ROWS
@@ -502,6 +660,10 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int
 def linear_swiglu(a: torch.Tensor, weight_interleaved: torch.Tensor, out: torch.Tensor, n_rows: int,
                   status: Optional[torch.Tensor] = None) -> None:
     """out[:, j] = silu(a @ w[2j]) * (a @ w[2j+1]) in one kernel; only for shapes ``tensor_core_shape_ok`` takes."""
+    if _chain_takes_product(a, weight_interleaved, out, n_rows, True):
+        _check_product(a, weight_interleaved, out, n_rows, True)
+        _ACTIVE_CHAIN.add_product(a, weight_interleaved, out, n_rows, _epilogue_code(out, False, True))
+        return
     if n_rows <= SKINNY_ROWS:
         skinny_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
     elif n_rows <= MID_MAX_ROWS:

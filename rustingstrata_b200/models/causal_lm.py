@@ -124,6 +124,11 @@ class CausalLM:
         """Whether a step of this model may be replayed from a CUDA graph (every part allows it)."""
         return all(p.capturable for p in self.parts())
 
+    @property
+    def chain_safe(self) -> bool:
+        """Whether the launchers may chain the products of a small decode step (every part goes through them alone)."""
+        return all(p.chain_safe for p in self.parts())
+
     def tensor_needs(self) -> Dict[str, TensorNeed]:
         needs: Dict[str, TensorNeed] = {}
         for p in self.parts():

@@ -40,6 +40,7 @@ class PagedAttention(Mixer):
     """params: hidden, n_heads, n_kv_heads, head_dim, qk_norm (bool), eps, window (int or None),
     scale (float or None = 1/sqrt(head_dim)), kv_projection (bool, default True).
     tensors: q_proj, k_proj, v_proj, o_proj, and q_norm, k_norm when qk_norm."""
+    chain_safe = True
 
     def __init__(self, spec, runtime, position=None):
         super().__init__(spec, runtime)

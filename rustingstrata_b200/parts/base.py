@@ -146,6 +146,10 @@ class Part:
     # device results on the host, no host loop over the batch's contents).  A step is captured into a CUDA graph
     # only if every part of the model says so; a part that needs the host says False and its model runs eagerly.
     capturable = True
+    # Whether the part touches the step's tensors through the kernel launchers of ``kernels.ops`` only (no torch
+    # arithmetic on them).  Only then may the engine let those launchers hold back the products of a small decode step and
+    # send them off as one chained kernel: work done behind the launchers' back would not see what they still hold.
+    chain_safe = False
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         self.spec = spec

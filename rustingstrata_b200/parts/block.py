@@ -13,6 +13,7 @@ from .registry import register_part
 class PreNormBlock(Block):
     """params: hidden.  Made of: mixer_norm, mixer, feed_forward_norm, feed_forward (and a position encoding for
     the mixer, if the layer lists one)."""
+    chain_safe = True
     roles = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
     def __init__(self, spec, runtime, parts):

@@ -12,6 +12,7 @@ from .spec import TensorNeed
 @register_part("embedding", "token_table")
 class TokenEmbedding(Part):
     """params: vocab, width.  tensors: weight."""
+    chain_safe = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -33,6 +34,7 @@ class TokenEmbedding(Part):
 class LinearHead(Part):
     """params: vocab, width.  tensors: weight (names the token table when the head is tied, in
     which case both parts hold the same device tensor)."""
+    chain_safe = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

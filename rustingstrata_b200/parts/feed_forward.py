@@ -18,6 +18,7 @@ from .spec import TensorNeed
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(FeedForward):
     """params: hidden, intermediate, activation ("silu").  tensors: gate_proj, up_proj, down_proj."""
+    chain_safe = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

@@ -13,6 +13,7 @@ from .spec import TensorNeed
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     """params: width, eps.  tensors: weight."""
+    chain_safe = True
     takes_owed = True
 
     def __init__(self, spec, runtime):

@@ -17,6 +17,7 @@ from .registry import register_part
 @register_part("position", "rope_neox")
 class RotaryNeox(PositionEncoding):
     """params: n_rot (rotated dims of a head), base."""
+    chain_safe = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -43,5 +44,6 @@ class RotaryNeox(PositionEncoding):
 
 @register_part("position", "none")
 class NoPosition(PositionEncoding):
+    chain_safe = True
     n_rot = 0
     cos_sin = None
