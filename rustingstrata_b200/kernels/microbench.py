@@ -2,7 +2,10 @@
 
     python -m rustingstrata_b200.kernels.microbench KERNEL [--m M] [--n N] [--k K] [--batch B] [--ctx S] ...
 
-KERNEL: skinny | mid | gemm | decode_attention | prefill_attention | rmsnorm | qk_norm_rope | sample.
+KERNEL: skinny | mid | gemm | chain | decode_attention | prefill_attention | rmsnorm | qk_norm_rope | sample.
+``chain``: the run of few-rows products between two attention calls of a decode step (output projection, norm, gate/up,
+down projection, norm, next QKV; --k = hidden size, --n = feed-forward size, heads from --heads/--kv-heads/--head-dim)
+as separate kernels and as one chained kernel.
 The launches are captured in a CUDA graph and the replay is timed with CUDA events, so the figure is
 device time per launch without host overhead; weights (or caches) rotate over buffers larger than the
 L2 cache so every launch reads from HBM.  With ``--once`` it launches the kernel a few times without a
@@ -119,9 +122,45 @@ def bench_prefill_attention(S, n_q, n_kv, hd, page, iters, once, force=""):
           f"TFLOP/s (causal half counted)")
 
 
+def bench_chain(M: int, hidden: int, inter: int, n_q: int, n_kv: int, hd: int, iters: int):
+    """One layer's products at M rows: the kernels one by one against the chained kernel, each timed as a graph of
+    `iters` runs; the layer's weights (larger than L2 at real sizes) are read from HBM every time."""
+    g = torch.Generator(device=DEV).manual_seed(0)
+    r = lambda *s: torch.randn(*s, device=DEV, generator=g)  # noqa: E731
+    Q, KV = n_q * hd, n_kv * hd
+    t = dict(attn=r(8, Q).to(torch.bfloat16), wo=(r(hidden, Q) * 0.03).to(torch.bfloat16), res=r(8, hidden),
+             n1=torch.ones(hidden, device=DEV, dtype=torch.bfloat16), wgu=(r(2 * inter, hidden) * 0.03).to(torch.bfloat16),
+             wd=(r(hidden, inter) * 0.03).to(torch.bfloat16), n2=torch.ones(hidden, device=DEV, dtype=torch.bfloat16),
+             wqkv=(r(Q + 2 * KV, hidden) * 0.03).to(torch.bfloat16),
+             h=torch.zeros(8, hidden, device=DEV, dtype=torch.bfloat16), act=torch.zeros(8, inter, device=DEV, dtype=torch.bfloat16),
+             h2=torch.zeros(8, hidden, device=DEV, dtype=torch.bfloat16), qkv=torch.zeros(8, Q + 2 * KV, device=DEV, dtype=torch.bfloat16))
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def run(chained: bool, norms: bool):
+        if chained:
+            ops.begin_chain(st)
+        owed = ops.linear(t["attn"], t["wo"], t["res"], M, accumulate=True, status=st, may_defer=norms)
+        if norms:
+            ops.rmsnorm(t["res"], t["n1"], 1e-6, t["h"], n_rows=M, pending=owed)
+        ops.linear_swiglu(t["h"], t["wgu"], t["act"], M, status=st)
+        owed = ops.linear(t["act"], t["wd"], t["res"], M, accumulate=True, status=st, may_defer=norms)
+        if norms:
+            ops.rmsnorm(t["res"], t["n2"], 1e-6, t["h2"], n_rows=M, pending=owed)
+        ops.linear(t["h2"], t["wqkv"], t["qkv"], M, status=st)
+        if chained:
+            ops.end_chain()
+    mb = sum(t[k].numel() * 2 for k in ("wo", "wgu", "wd", "wqkv")) / 1e6
+    for name, norms in (("four products", False), ("products and the two norms between them", True)):
+        a = timed(lambda i: run(False, norms), 1, iters, False)
+        b = timed(lambda i: run(True, norms), 1, iters, False)
+        print(f"chain M={M} hidden={hidden} ffn={inter} ({mb:.0f} MB of weights): {name}: separate kernels {a:.1f} us "
+              f"({mb / a / 1e6 * 1e6:.2f} TB/s), chained {b:.1f} us ({mb / b / 1e6 * 1e6:.2f} TB/s)")
+    assert st.item() == 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("kernel", choices=["skinny", "mid", "gemm", "decode_attention", "prefill_attention", "rmsnorm", "qk_norm_rope",
+    ap.add_argument("kernel", choices=["skinny", "mid", "gemm", "chain", "decode_attention", "prefill_attention", "rmsnorm", "qk_norm_rope",
                                        "sample"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
@@ -143,6 +182,8 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     if a.kernel in ("skinny", "mid", "gemm"):
         bench_linear(a.kernel, a.m, a.n, a.k, a.epilogue, a.bn, a.iters, a.once, a.then_norm)
+    elif a.kernel == "chain":
+        bench_chain(a.m, a.k, a.n, a.heads, a.kv_heads, a.head_dim, min(a.iters, 20))
     elif a.kernel == "decode_attention":
         bench_decode_attention(a.batch, a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size, a.iters, a.once)
     elif a.kernel == "prefill_attention":
