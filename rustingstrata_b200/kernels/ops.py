@@ -627,8 +627,10 @@ def reset_chain_barrier() -> None:
 
 
 def _chain_takes_product(a, weight, out, n_rows, swiglu: bool) -> bool:
+    if _ACTIVE_CHAIN is None:            # asked first: the 32-bit engine must not load (or compile) the bfloat16 library
+        return False
     lib = bf16lib()
-    return (_ACTIVE_CHAIN is not None and n_rows <= lib.rs_decode_chain_max_rows() and tensor_core_shape_ok(a, weight)
+    return (n_rows <= lib.rs_decode_chain_max_rows() and tensor_core_shape_ok(a, weight)
             and weight.numel() < SKINNY_MAX_WEIGHT and out.dtype in (torch.bfloat16, torch.float32)
             and a.is_cuda and weight.is_cuda and out.is_cuda)
 

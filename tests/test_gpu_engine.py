@@ -355,3 +355,20 @@ def test_bench_method_of_the_entry_point(tiny_models):
             assert 0 < r[k]["min"] <= r[k]["mean"] <= r[k]["max"]
     assert not eng.has_work()
     eng.runner.cache.check()
+
+
+def test_the_32_bit_engine_loads_only_the_library_it_needs(tiny_models):
+    """A float32 engine in a fresh process generates without loading (so, in a fresh checkout, without compiling) the
+    library of bfloat16 tensor-core kernels."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    code = (f"import sys; sys.path.insert(0, {ROOT!r})\n"
+            "from rustingstrata_b200 import Engine\n"
+            "from rustingstrata_b200.kernels import build\n"
+            f"eng = Engine({tiny_models['A']!r}, dtype='float32', page_size=4, max_tokens=128, max_batch_tokens=32, max_seqs=2)\n"
+            "print(eng.generate([1, 2, 3], max_new_tokens=4))\n"
+            "print('LOADED', sorted(build._LOADED))\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "LOADED ['core']" in r.stdout, r.stdout
