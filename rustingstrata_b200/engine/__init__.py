@@ -1,3 +1,3 @@
 from .runner import ModelRunner, StepEntry, StepError
-from .scheduler import Scheduler, Request, Scheduled, RequestRejected
+from .scheduler import Scheduler, Request, Scheduled, RequestRejected, SchedulerStuck
 from .engine import Engine
