@@ -38,6 +38,7 @@ struct AttnParams {
     int n_q, n_kv, hd, group, heads_per_cta, chunks_per_group, q_per_cta;
     int window;                            // 0 = all keys
     float scale;
+    const float* slopes;                   // [n_q] or null: slopes[h] * (key position - query position) is added to a score
     int decode, split_keys, max_splits;
     const int* split_start;                // decode: [n_work] first partial slot of each sequence
     float* partial;                        // decode: [slot][n_q][hd + 2], slot = split_start[w] + split
@@ -130,6 +131,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(const AttnP
             float s = 0.f;
             for (int d = 0; d < hd; ++d) s = fmaf(qr[d], kr[d], s);
             s *= p.scale;
+            if (p.slopes != nullptr) s = fmaf(p.slopes[head0 + r % n_heads], (float)(kpos - qpos), s);   // a bias linear in the distance
             const bool ok = kpos >= key_lo && kpos < key_hi && kpos <= qpos &&
                             (p.window <= 0 || kpos > qpos - p.window);
             s = ok ? s : -INFINITY;
@@ -257,8 +259,8 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
                                 long page_stride, int num_pages, int page_size, const int* block_table,
                                 int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
                                 int n_q, int n_kv, int hd, int window, float scale, int decode, int split_keys,
-                                int max_splits, const int* split_start, float* partial, int partial_slots, int* status,
-                                void* stream) {
+                                int max_splits, const int* split_start, float* partial, int partial_slots,
+                                const float* slopes, int* status, void* stream) {
     if (n_work <= 0) return 0;
     if (hd % 16 || hd > 256 || hd <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
     if (decode && (split_keys % KT || split_keys <= 0 || max_splits <= 0 || partial == nullptr || partial_slots <= 0 ||
@@ -274,6 +276,7 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
     p.q_per_cta = decode ? 1 : ROWS / p.heads_per_cta;
     p.window = window; p.scale = scale; p.decode = decode; p.split_keys = split_keys; p.max_splits = max_splits;
     p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
+    p.slopes = slopes;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RS_F32) return dispatch_hd<float, true>(p, n_work, s);
     if (dt == RS_BF16) return dispatch_hd<__nv_bfloat16, false>(p, n_work, s);
@@ -360,7 +363,7 @@ RS_EXPORT int rs_attention_decode_noalloc(const void* q, long q_stride, void* ou
     p.chunks_per_group = (p.group + p.heads_per_cta - 1) / p.heads_per_cta;
     p.q_per_cta = 1;
     p.window = window; p.scale = scale; p.decode = 1; p.split_keys = split_keys; p.max_splits = max_splits;
-    p.split_start = split_start; p.partial = partial; p.status = status;
+    p.split_start = split_start; p.partial = partial; p.status = status; p.slopes = nullptr;
     // what the array really holds for this shape, not what the caller said it would use: a split list that
     // disagrees with total_splits is flagged by the kernels (RS_STATUS_BAD_PLAN) instead of written past the array
     p.partial_slots = (int)((long)RS_NOALLOC_MAX_FLOATS / ((long)n_q * (hd + 2)));

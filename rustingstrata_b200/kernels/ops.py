@@ -99,7 +99,7 @@ def core():
                                        c_int, c_int, c_int, c_int, c_void_p]
         lib.rs_attention_simt.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int,
                                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                           c_void_p]
         lib.rs_attention_simt_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_attention_simt_partial_floats.argtypes = [c_int, c_int, c_int]
@@ -687,8 +687,12 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
                    q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                    head_dim: int, page_size: int, window: int, scale: float, decode: bool, status: torch.Tensor,
                    split_keys: int = 128, max_splits: int = 1, split_start: Optional[torch.Tensor] = None,
-                   total_splits: int = 0, partial: Optional[torch.Tensor] = None) -> None:
+                   total_splits: int = 0, partial: Optional[torch.Tensor] = None,
+                   slopes: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention (see csrc/attention_simt.cu).  q/out: [T, >= n_q*head_dim] views.
+
+    ``slopes``: float32 [n_q] or None: slopes[h] * (key position - query position) is added to every scaled score of
+    head h (a position encoding that biases scores by distance instead of rotating q and k).
 
     Decode form: ``partial`` is the workspace of un-normalised partial results, one slot of n_q * (head_dim + 2)
     float32 values per (sequence, split); ``split_start[w]`` is the first slot of sequence w and ``total_splits`` the
@@ -709,6 +713,8 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
         if t.dtype != torch.int32:
             raise KernelError(f"attention: {name} must be int32")
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != n_q or not slopes.is_contiguous() or not slopes.is_cuda):
+        raise KernelError(f"attention: slopes must be contiguous float32 [{n_q}] on the device")
     slots = 0
     if decode:
         if split_start is None or split_start.dtype != torch.int32:
@@ -718,8 +724,8 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q), _ptr(cache), cache.stride(0), cache.shape[0],
         page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q,
         n_kv, head_dim, int(window), float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start),
-        _ptr(partial), slots,
-        _ptr(status), _stream()), "attention_simt")
+        _ptr(partial), slots, _ptr(slopes),
+        _ptr(status), _stream()), "attention_simt", 2 if decode else 1)
 
 
 def _partial_slots(partial: Optional[torch.Tensor], total_splits: int, n_q: int, head_dim: int, who: str) -> int:
@@ -766,14 +772,16 @@ def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_di
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                       head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor,
-                      force: str = "") -> None:
+                      force: str = "", slopes: Optional[torch.Tensor] = None) -> None:
     """Attention of prompt portions; ``work`` lists (sequence, first query) tiles of ``attention_prefill_q_per_cta``
     tokens.  tcgen05 kernel (csrc/attention_prefill_tc.cu), mma.sync kernel (csrc/attention_prefill_mma.cu) or
-    CUDA cores, whichever takes the shape; ``force`` names one."""
+    CUDA cores, whichever takes the shape; ``force`` names one.  Score biases (``slopes``) are the CUDA-core kernel's."""
     kind = attention_prefill_kernel(q.dtype, n_q, n_kv, head_dim, page_size, force)
+    if slopes is not None and kind != "simt":
+        raise KernelError("attention_prefill: only the CUDA-core kernel (force='simt') adds score biases")
     if kind == "simt":
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
-                       scale, False, status)
+                       scale, False, status, slopes=slopes)
         return
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status)
     _rows_contiguous(q, "q")
@@ -815,13 +823,14 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                      q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                      head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor, split_keys: int,
                      max_splits: int, split_start: torch.Tensor, total_splits: int, partial: torch.Tensor,
-                     force_simt: bool = False) -> None:
+                     force_simt: bool = False, slopes: Optional[torch.Tensor] = None) -> None:
     """Attention of sequences with one query token each: the tensor-core kernel (csrc/attention_decode_mma.cu)
-    where it takes the shape, else the CUDA-core kernel's split form.  Same partial-workspace layout."""
-    if force_simt or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size):
+    where it takes the shape, else the CUDA-core kernel's split form (always, when score biases are given).  Same
+    partial-workspace layout."""
+    if force_simt or slopes is not None or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size):
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, True, status, split_keys=split_keys, max_splits=max_splits, split_start=split_start,
-                       total_splits=total_splits, partial=partial)
+                       total_splits=total_splits, partial=partial, slopes=slopes)
         return
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
     _rows_contiguous(q, "q")

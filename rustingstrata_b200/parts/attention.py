@@ -12,6 +12,10 @@ Everything that distinguishes one architecture's attention from another's is a
 parameter: head counts, head size, whether q/k are normed and with which eps, the
 window, the score scale, which position encoding is applied, and whether this call
 projects keys and values at all (a call that reads another call's cache does not).
+A position encoding reaches the attention in one of two ways, or both: a rotation of
+q and k (its ``cos_sin`` table, ``n_rot`` and ``stream``) applied before the cache
+write, and a bias on the scores that is linear in the distance between query and key
+(its ``score_slopes``, one per head), which the CUDA-core attention kernels add.
 """
 from __future__ import annotations
 
@@ -118,10 +122,16 @@ class PagedAttention(Mixer):
         return 4.0 * self.n_heads * self.hd * pairs
 
     # ---------------------------------------------------------------- planning
+    def _score_slopes(self):
+        """The position encoding's bias on the scores, if it has one: float32 [n_heads], slope of head h times (key
+        position - query position) added to every scaled score.  The CUDA-core attention kernels take it."""
+        return getattr(self.position, "score_slopes", None) if self.position is not None else None
+
     def plan_key(self):
         if self.q_per_cta is None:
+            force = "simt" if self._score_slopes() is not None else ""
             self.q_per_cta = ops.attention_prefill_q_per_cta(self.runtime.dtype, self.n_heads, self.n_kv, self.hd,
-                                                              self.runtime.page_size)
+                                                              self.runtime.page_size, force)
         return ("paged_attention", self.q_per_cta, self.window)
 
     def build_plan(self, batch: HostBatch):
@@ -171,8 +181,9 @@ class PagedAttention(Mixer):
         ops.linear(h, w, qkv, T, status=ctx.status)
         table = ctx.block_tables[call.cache_group]
         pos = self.position
+        rot = getattr(pos, "cos_sin", None) if pos is not None else None
         ops.qk_norm_rope_kv(qkv, T, self.n_heads, self.n_kv, self.hd, self.q_norm_w, self.k_norm_w, self.eps,
-                            pos.cos_sin if pos is not None else None, pos.n_rot if pos is not None else 0,
+                            rot, pos.n_rot if rot is not None else 0,
                             ctx.positions, ctx.seq_of_token, table, rt.page_size, call.cache, write_kv, ctx.status,
                             stream=pos.stream if pos is not None else 0)
         out = rt.get_scratch("attn_out")[:, : self.q_width]
@@ -180,11 +191,13 @@ class PagedAttention(Mixer):
         common = dict(q=qkv, out=out, cache=call.cache, block_table=table, q_start=ctx.q_start, kv_len=ctx.kv_len,
                       n_q=self.n_heads, n_kv=self.n_kv, head_dim=self.hd, page_size=rt.page_size, window=self.window,
                       scale=self.scale, status=ctx.status)
+        slopes = self._score_slopes()
         if plan["n_prefill"]:
-            ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], **common)
+            ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], slopes=slopes,
+                                  force="simt" if slopes is not None else "", **common)
         if plan["n_decode"]:
             ops.attention_decode(work=plan["decode_work"], n_work=plan["n_decode"], split_keys=SPLIT_KEYS,
                                  max_splits=plan["max_splits"], split_start=plan["split_start"],
-                                 total_splits=plan["total_splits"],
+                                 total_splits=plan["total_splits"], slopes=slopes,
                                  partial=rt.get_scratch("attn_partial", torch.float32), **common)
         ctx.owed = ops.linear(out, self.w_o, residual, T, accumulate=True, status=ctx.status, may_defer=ctx.may_owe)

@@ -208,10 +208,15 @@ class Norm(Part):
 class PositionEncoding(Part):
     """What a mixer needs to encode positions; the mixer's kernels consume it.
 
+    ``cos_sin`` / ``n_rot``: a rotation table [positions, cos(n_rot/2) | sin(n_rot/2)] (None / 0: no rotation);
     ``n_streams``: how many position values per token the step must carry for this part (1: the token's place in its
-    sequence is all it needs); ``stream``: which of them its table is indexed by."""
+    sequence is all it needs); ``stream``: which of them its table is indexed by; ``score_slopes``: None, or float32
+    [heads] on the device: slope of head h times (key position - query position) is added to every scaled score."""
     n_streams = 1
     stream = 0
+    cos_sin = None
+    n_rot = 0
+    score_slopes = None
 
 
 class Block(Part):

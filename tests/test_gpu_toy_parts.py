@@ -554,3 +554,133 @@ def test_toy_block_with_four_norms_two_mixers_and_a_second_position_stream(tmp_p
         unregister_part("block", "toy_sandwich")
         unregister_part("mixer", "toy_token_count")
         unregister_part("position", "toy_second_stream_rope")
+
+
+# ----------------------------------------------------------------------------------------------------------
+# A position encoding that is no rotation: a bias on the attention scores, linear in the distance, defined here only.
+
+def define_distance_bias():
+    from rustingstrata_b200.config import register_architecture
+    from rustingstrata_b200.parts import LayerCall, LayerSpec, ModelSpec, PartSpec, PositionEncoding, register_part
+
+    @register_part("position", "toy_distance_bias", replace=True)
+    class DistanceBias(PositionEncoding):
+        """score(q at i, k at j) += slope_h * (j - i) with slope_h = first / ratio^h: nothing is rotated, keys and queries
+        enter the cache and the product as they are; the attention kernels add the bias."""
+        chain_safe = True
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            n, first, ratio = int(spec.params["heads"]), float(spec.params["first"]), float(spec.params["ratio"])
+            self._slopes = torch.tensor([first / ratio ** h for h in range(n)], dtype=torch.float32, device=runtime.device)
+
+        @property
+        def score_slopes(self):
+            return self._slopes
+
+    class BiasConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d, where=""):
+            return cls(dict(d))
+
+    def build(cfg):
+        d = cfg.d
+        H, V, nh = d["hidden_size"], d["vocab_size"], d["heads"]
+        norm = lambda n: PartSpec("rmsnorm", {"width": H, "eps": d["eps"]}, {"weight": n})  # noqa: E731
+        layers = []
+        for i in range(d["layers"]):
+            parts = {"mixer_norm": norm(f"l{i}.n1"), "feed_forward_norm": norm(f"l{i}.n2"),
+                     "mixer": PartSpec("paged_attention", {"hidden": H, "n_heads": nh, "n_kv_heads": d["kv_heads"], "head_dim": d["head_dim"],
+                                                           "qk_norm": False, "window": 37 if i == 1 else None},
+                                       {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")}),
+                     "position": PartSpec("toy_distance_bias", {"heads": nh, "first": 0.5, "ratio": 2.0}),
+                     "feed_forward": PartSpec("gated_mlp", {"hidden": H, "intermediate": d["ffn"]},
+                                              {k: f"l{i}.{k}" for k in ("gate_proj", "up_proj", "down_proj")})}
+            layers.append(LayerSpec(PartSpec("pre_norm", {"hidden": H}), parts))
+        return ModelSpec("bias", V, H, d["max_positions"], PartSpec("token_table", {"vocab": V, "width": H}, {"weight": "emb"}),
+                         tuple(layers), tuple(LayerCall(i) for i in range(d["layers"])), norm("fn"),
+                         PartSpec("linear", {"vocab": V, "width": H}, {"weight": "head"}))
+
+    register_architecture("ToyBiasLM", BiasConfig, build, replace=True)
+
+
+BIAS = {"architectures": ["ToyBiasLM"], "vocab_size": 90, "hidden_size": 64, "layers": 2, "heads": 4, "kv_heads": 2, "head_dim": 64,
+        "ffn": 96, "eps": 1e-5, "max_positions": 400}
+
+
+def plain_bias(w, toks):
+    import math
+    import plain_qwen3 as P
+    d = BIAS
+    nh, nkv, hd, T = d["heads"], d["kv_heads"], d["head_dim"], len(toks)
+    x = w["emb"][np.asarray(toks)]
+    tq, tk = np.arange(T)[:, None], np.arange(T)[None, :]
+    for i in range(d["layers"]):
+        h = P.rms_norm(x, w[f"l{i}.n1"], d["eps"])
+        q = (h @ w[f"l{i}.q_proj"].T).reshape(T, nh, hd)
+        k = (h @ w[f"l{i}.k_proj"].T).reshape(T, nkv, hd)
+        v = (h @ w[f"l{i}.v_proj"].T).reshape(T, nkv, hd)
+        vis = tk <= tq
+        if i == 1:
+            vis &= tk > tq - 37
+        o = np.zeros((T, nh, hd))
+        for hh in range(nh):
+            g = hh // (nh // nkv)
+            s = (q[:, hh] @ k[:, g].T) / math.sqrt(hd) + (0.5 / 2.0 ** hh) * (tk - tq)
+            o[:, hh] = P.softmax(np.where(vis, s, -np.inf)) @ v[:, g]
+        x = x + o.reshape(T, nh * hd) @ w[f"l{i}.o_proj"].T
+        h = P.rms_norm(x, w[f"l{i}.n2"], d["eps"])
+        x = x + (P.silu(h @ w[f"l{i}.gate_proj"].T) * (h @ w[f"l{i}.up_proj"].T)) @ w[f"l{i}.down_proj"].T
+    return P.rms_norm(x, w["fn"], d["eps"]) @ w["head"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_position_encoding_that_biases_scores_instead_of_rotating(tmp_path, dtype):
+    """Head size 64 with pages of 16 is a shape the tensor-core attention kernels take; with a score bias the engine
+    must run the CUDA-core kernels instead, in portions and in captured single-token steps across several splits."""
+    import plain_qwen3 as P
+    from rustingstrata_b200.config import EngineConfig, unregister_architecture
+    from rustingstrata_b200.engine import ModelRunner, StepEntry
+    from rustingstrata_b200.models import manifest_for
+    from rustingstrata_b200.parts import unregister_part
+    from rustingstrata_b200.weights import write_random_model
+    define_distance_bias()
+    try:
+        d = str(tmp_path / "bias")
+        write_random_model(d, BIAS, manifest_for(BIAS), seed=21, std=0.12, norm_std=0.1)
+        w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+        runner = ModelRunner.from_dir(d, EngineConfig(dtype=dtype, page_size=16, num_pages=48, max_seqs=3,
+                                                      max_batch_tokens=256, max_logit_rows=256))
+        toks = {r: random_tokens(90, n, 70 + i) for i, (r, n) in enumerate((("a", 330), ("b", 90)))}
+        ref = {r: plain_bias(w, t) for r, t in toks.items()}
+        got = {r: {} for r in toks}
+
+        def step(entries):
+            logits = runner.step([StepEntry(r, toks[r][s:s + n], list(range(n))) for r, s, n in entries]).cpu().numpy()
+            runner.check_status()
+            k = 0
+            for r, s, n in entries:
+                for i in range(n):
+                    got[r][s + i] = logits[k]
+                    k += 1
+        step([("a", 0, 200), ("b", 0, 3)])
+        step([("a", 200, 110), ("b", 3, 60)])
+        for i in range(20):
+            step([("a", 310 + i, 1)] + ([("b", 63 + i, 1)] if True else []))
+        for i in range(83, 90):
+            step([("b", i, 1)])
+        tol = 5e-6 if dtype == "float32" else 2e-2
+        for r in got:
+            rows = np.stack([got[r][i] for i in range(len(toks[r]))])
+            assert rel_err(rows, ref[r]) < tol, r
+        # the bias matters: without it the logits are far away
+        assert runner.model.capturable and (runner.graph_replays > 10 or dtype == "float32")
+        for r in toks:
+            runner.release(r)
+        runner.cache.check()
+    finally:
+        unregister_architecture("ToyBiasLM")
+        unregister_part("position", "toy_distance_bias")
