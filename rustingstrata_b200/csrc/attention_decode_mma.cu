@@ -55,7 +55,7 @@ struct DecodeParams {
     float* partial;                    // [slot][n_q][hd + 2]: acc, max (log2 units), sum
     int partial_slots;                 // slots `partial` holds; a slot beyond it is flagged and not written
     int* status;
-    int n_work, max_splits, total;     // total = n_work * n_kv * max_splits items, dead ones included
+    int n_work, max_splits, total;     // total: items = (partial slot, kv head) pairs; the kernel reads it from split_start[n_work]
     int groups, depth;                 // consumer groups and stages per group
     int one_load_per_page;             // the 5-d map is in use
 };
@@ -63,12 +63,21 @@ struct DecodeParams {
 struct Item { int w, kvh, split_local, seq, key_lo, key_hi, k_base, kv_len; bool live; };
 
 // The metadata arrays are uploaded before the step's first kernel, so the read-only path is safe for them.
+// Item id = (partial slot, kv head), the kv head fastest.  The slots are the live (sequence, split) pairs in order:
+// split_start[w] is the first slot of sequence w, so the sequence of a slot is found by bisection.  Every id below
+// split_start[n_work] * n_kv is a split that holds keys, whatever the launch shape was rounded up to: the CTAs, which
+// take ids round robin, get the same number of items to within one.
 __device__ __forceinline__ Item decode_item(const DecodeParams& p, int id) {
     Item it;
-    it.split_local = id % p.max_splits;
-    const int r = id / p.max_splits;
-    it.kvh = r % p.n_kv;
-    it.w = r / p.n_kv;
+    it.kvh = id % p.n_kv;
+    const int slot = id / p.n_kv;
+    int a = 0, b = p.n_work;                       // split_start[a] <= slot < split_start[b]
+    while (b - a > 1) {
+        const int mid = (a + b) >> 1;
+        if (__ldg(p.split_start + mid) <= slot) a = mid; else b = mid;
+    }
+    it.w = a;
+    it.split_local = slot - __ldg(p.split_start + a);
     it.seq = __ldg(p.work + it.w);
     const int kv_len = __ldg(p.kv_len + it.seq);
     it.kv_len = kv_len;
@@ -91,7 +100,10 @@ __device__ __forceinline__ int next_live(const DecodeParams& p, int id, Item& it
 }
 
 template <int HD>
-__global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const __grid_constant__ CUtensorMap map_kv, const DecodeParams p) {
+__global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const __grid_constant__ CUtensorMap map_kv, const DecodeParams p_launch) {
+    // the step's metadata is in place before its first kernel: the number of live items is read, not launched with
+    DecodeParams p = p_launch;
+    p.total = __ldg(p.split_start + p.n_work) * p.n_kv;
     // A stage holds the item's pages one after the other; a page's block is [K | V][half of the head][token][64 dims],
     // every (K|V, half) piece a multiple of 1 KiB, so a token's swizzle phase is its index mod 8.
     constexpr int HALVES = HD / 64;                  // 64-wide (128-byte) column blocks of a head
@@ -622,7 +634,7 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
     p.n_work = n_work; p.max_splits = max_splits;
-    p.total = n_work * n_kv * max_splits;
+    p.total = n_work * n_kv * max_splits;          // an upper bound, for the size of the grid
     p.groups = p.depth = 0;
     CUtensorMap mkv;
     p.one_load_per_page = cached_page_map(cache, num_pages, n_kv, page_size, hd, &mkv) == 0;
