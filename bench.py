@@ -13,6 +13,11 @@ same through the Python entry point with host token ids in and out every step;
 and fraction of the HBM peak).  Peaks come from MEASURED_PEAKS.json beside this file when
 present, else from the fallback figures of this pool.
 
+``--marginal``: instead of the benchmark line, what each kernel family costs INSIDE the captured decode step (batch
+``--batch``, prompts of ``--prompt-len`` tokens): the step is timed whole and again with that family's launches left out
+(the results are then wrong, only the clock is read).  The difference is what the family adds to the step with all the
+overlap between neighbouring kernels that programmatic dependent launch gives, which a kernel timed alone cannot show.
+
 ``--workload 14b-mixed``: Qwen3-14B layer sizes, 32 requests with prompts of 128 to 4,096
 random tokens, all present at the start, run by the engine's scheduler with portions of 512
 prompt tokens beside the decoding requests' tokens, 256 tokens each at temperature 0.7,
@@ -90,6 +95,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long"])
+    ap.add_argument("--marginal", action="store_true", help="marginal cost of each kernel family inside the decode step")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT, help="with --marginal: tokens each request holds")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (no setup.py/pyproject.toml; "
@@ -100,6 +107,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.marginal:
+        return marginal_costs(args)
     if args.workload == "14b-mixed":
         return mixed_workload(args)
     if args.workload == "32b-long":
@@ -225,6 +234,57 @@ def main() -> int:
         "clocks": clk,
     }
     print(json.dumps(rec))
+    return 0
+
+
+def marginal_costs(args) -> int:
+    """Times the captured decode step whole, then with one kernel family's launches left out at a time."""
+    import numpy as np
+    from rustingstrata_b200 import Engine
+    from rustingstrata_b200.kernels import ops
+    from rustingstrata_b200.sampling import SamplingParams
+    cfg = dict(QWEN3_8B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    L, B, S = cfg["num_hidden_layers"], args.batch, args.prompt_len
+    eng = Engine(cfg, dtype="bfloat16", random_seed=0, page_size=16, max_tokens=B * CONTEXT, max_batch_tokens=PROMPT, max_seqs=B)
+    rng = np.random.default_rng(0)
+    for _ in range(B):
+        eng.add_request(rng.integers(0, cfg["vocab_size"], size=S).tolist(), CONTEXT - S, SamplingParams())
+    while eng.scheduler.waiting or any(r.prefilling for r in eng.scheduler.running):
+        eng.step()
+
+    def timed():
+        eng.runner._graphs.clear()                       # the step is captured anew, without the launches that are off
+        return eng.decode_steps_device_timed(max(args.steps, 32), warmup=4)
+    for _ in range(3):
+        timed()                                          # until the clocks have settled under the power cap
+    whole = timed()
+    out = {"batch": B, "prompt_len": S, "layers": L, "ms_per_step": whole, "us_per_layer": whole / L * 1000, "marginal_us_per_layer": {},
+           "marginal_us_per_step": {}}
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    families = [("attention_decode (+ merge)", "attention_decode", None), ("qk_norm_rope_kv", "qk_norm_rope_kv", None),
+                ("gate/up product", "linear_swiglu", None), ("row norms (+ owed sums)", "rmsnorm", None),
+                ("qkv product", "linear", (qkv, H)), ("output product", "linear", (H, cfg["num_attention_heads"] * cfg["head_dim"])),
+                ("down product", "linear", (H, I)), ("output head", "linear", (cfg["vocab_size"], H))]
+    for label, fn_name, shape in families:
+        real = getattr(ops, fn_name)
+        if shape is None:
+            setattr(ops, fn_name, lambda *a, **k: None)
+        else:
+            setattr(ops, fn_name, lambda a, w, *r, _real=real, _shape=shape, **k: None if tuple(w.shape) == _shape else _real(a, w, *r, **k))
+        try:
+            t = timed()
+        finally:
+            setattr(ops, fn_name, real)
+        again = timed()                                  # the whole step once more: clocks drift under a long load
+        per_step = ((whole + again) / 2 - t) * 1000
+        whole = again
+        key = "marginal_us_per_step" if label == "output head" else "marginal_us_per_layer"
+        out[key][label] = per_step if label == "output head" else per_step / L
+    out["ms_per_step_at_the_end"] = whole
+    print(json.dumps(out))
     return 0
 
 

@@ -52,6 +52,7 @@ struct DecodeParams {
     int window;
     float scale_log2;                  // scale * log2(e)
     const int* split_start;
+    const int* items;                  // [split_start[n_work] * n_kv] live items, packed by pack_item
     float* partial;                    // [slot][n_q][hd + 2]: acc, max (log2 units), sum
     int partial_slots;                 // slots `partial` holds; a slot beyond it is flagged and not written
     int* status;
@@ -60,24 +61,27 @@ struct DecodeParams {
     int one_load_per_page;             // the 5-d map is in use
 };
 
-struct Item { int w, kvh, split_local, seq, key_lo, key_hi, k_base, kv_len; bool live; };
+struct Item { int w, kvh, split_local, seq, key_lo, key_hi, k_base, kv_len; };
 
-// The metadata arrays are uploaded before the step's first kernel, so the read-only path is safe for them.
-// Item id = (partial slot, kv head), the kv head fastest.  The slots are the live (sequence, split) pairs in order:
-// split_start[w] is the first slot of sequence w, so the sequence of a slot is found by bisection.  Every id below
-// split_start[n_work] * n_kv is a split that holds keys, whatever the launch shape was rounded up to: the CTAs, which
-// take ids round robin, get the same number of items to within one.
+// The metadata arrays are uploaded before the step's first kernel, and the list of items is written by a kernel that
+// has ended before this one starts, so the read-only path is safe for them.
+// The items are the live (sequence, kv head, split) triples only, whatever the launch shape was rounded up to, so the
+// CTAs, which take ids round robin, get the same number of items to within one.  Sequence w owns the ids from
+// split_start[w] * n_kv (split_start[w] is its first partial slot); inside a sequence the split runs fastest, then the
+// kv head: CTAs that work side by side then read pages that lie far apart, which streams faster than neighbours
+// reading the adjacent 4 KiB pieces of one page (126.8 against 112.4 us at 64 x 2,048 keys).  Finding an id's triple
+// takes a bisection and a division; every role of every CTA needs it for every item, in all layers of a step, and that
+// arithmetic showed in the kernel's time (+18 % at batch 64).  So a small kernel writes the list of triples once per
+// step (decode_items_kernel), and the attention kernels of all layers look an id up with one load.
+__host__ __device__ __forceinline__ int pack_item(int w, int kvh, int split_local) { return (w << 20) | (kvh << 12) | split_local; }
+constexpr int ITEM_MAX_SEQS = 1 << 11, ITEM_MAX_KV = 1 << 8, ITEM_MAX_SPLITS = 1 << 12;
+
 __device__ __forceinline__ Item decode_item(const DecodeParams& p, int id) {
     Item it;
-    it.kvh = id % p.n_kv;
-    const int slot = id / p.n_kv;
-    int a = 0, b = p.n_work;                       // split_start[a] <= slot < split_start[b]
-    while (b - a > 1) {
-        const int mid = (a + b) >> 1;
-        if (__ldg(p.split_start + mid) <= slot) a = mid; else b = mid;
-    }
-    it.w = a;
-    it.split_local = slot - __ldg(p.split_start + a);
+    const int packed = __ldg(p.items + id);
+    it.w = packed >> 20;
+    it.kvh = (packed >> 12) & (ITEM_MAX_KV - 1);
+    it.split_local = packed & (ITEM_MAX_SPLITS - 1);
     it.seq = __ldg(p.work + it.w);
     const int kv_len = __ldg(p.kv_len + it.seq);
     it.kv_len = kv_len;
@@ -86,17 +90,15 @@ __device__ __forceinline__ Item decode_item(const DecodeParams& p, int id) {
     it.key_lo = max(lo, split * SPLIT);
     it.key_hi = min(kv_len, (split + 1) * SPLIT);
     it.k_base = split * SPLIT;
-    it.live = it.key_lo < it.key_hi;
     return it;
 }
 
-// next live item of this CTA at or after id; p.total when there is none
-__device__ __forceinline__ int next_live(const DecodeParams& p, int id, Item& it) {
-    for (; id < p.total; id += gridDim.x) {
-        it = decode_item(p, id);
-        if (it.live) return id;
-    }
-    return p.total;
+// The item with this id, if there is one; every role steps through the ids the same way and skips none.  (An item
+// without visible keys cannot come from a well-formed list; it would load page 0 and leave an empty partial.)
+__device__ __forceinline__ int item_at(const DecodeParams& p, int id, Item& it) {
+    if (id >= p.total) return p.total;
+    it = decode_item(p, id);
+    return id;
 }
 
 template <int HD>
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
         int early = 0;
         {
             Item it;
-            int id_e = next_live(p, blockIdx.x, it);
+            int id_e = item_at(p, blockIdx.x, it);
             while (id_e < p.total && early < stages && it.k_base + SPLIT < it.kv_len) {
                 const int kpos = it.k_base + lane * p.page_size;
                 int pg = 0;
@@ -197,17 +199,17 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
                 __syncwarp();                        // the byte count is expected before any lane's load can land
                 load_pages(it, pg, s);
                 ++early;
-                id_e = next_live(p, id_e + gridDim.x, it);
+                id_e = item_at(p, id_e + gridDim.x, it);
             }
         }
         pdl_wait();
         Item cur, nxt;
         int page, page_n = 0;
         uint4 qv[QV], qn[QV];
-        int id = next_live(p, blockIdx.x, cur);
+        int id = item_at(p, blockIdx.x, cur);
         if (id < p.total) fetch(cur, page, qv);
         for (int n = 0; id < p.total; ++n) {
-            const int id_n = next_live(p, id + gridDim.x, nxt);
+            const int id_n = item_at(p, id + gridDim.x, nxt);
             if (id_n < p.total) fetch(nxt, page_n, qn);
             const int k = n / p.groups;
             const int s = stage_of(n);
@@ -249,7 +251,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
             Item it;
             int n = 0;
             bool go = true;
-            for (int id = next_live(p, blockIdx.x, it); id < p.total && go; id = next_live(p, id + gridDim.x, it), ++n) {
+            for (int id = item_at(p, blockIdx.x, it); id < p.total && go; id = item_at(p, id + gridDim.x, it), ++n) {
                 const int kpos = it.k_base + lane * p.page_size;
                 int page = -1;
                 if (lane < pages_per_item && kpos < it.key_hi && kpos + p.page_size > it.key_lo)
@@ -263,7 +265,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
             }
         }
     } else if (warp < producer_warp) {
-        // ------------------------------------------------------------ consumers: group g takes live items g, g + G, ...
+        // ------------------------------------------------------------ consumers: group g takes the items g, g + G, ... of the CTA
         const int grp = warp / GROUP_WARPS, gw = warp % GROUP_WARPS;
         const int g = lane >> 2, t = lane & 3;
         auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_WARPS * 32) : "memory"); };
@@ -272,9 +274,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
         pdl_wait();                                  // the workspace of partials belongs to earlier kernels until now
         bool ok = true;
         Item it;
-        int n = 0;
-        for (int id = next_live(p, blockIdx.x, it); id < p.total; id = next_live(p, id + gridDim.x, it), ++n) {
-            if (n % p.groups != grp) continue;
+        // the CTA's n-th item has id blockIdx.x + n * gridDim.x: a group looks at its own only
+        for (int n = grp, id = blockIdx.x + grp * gridDim.x; id < p.total; n += p.groups, id += p.groups * gridDim.x) {
+            it = decode_item(p, id);
             const int k = n / p.groups;
             const int s = grp * p.depth + k % p.depth;
             const uint32_t parity = (uint32_t)(k / p.depth) & 1u;
@@ -575,6 +577,19 @@ int cached_page_map(const void* cache, int num_pages, int n_kv, int page_size, i
     return e.refused;
 }
 
+// One thread per (sequence, kv head, split of the launch shape): a live one writes its triple to its id.
+// The attention kernel reads the list before it waits for the kernel in front of it (its first loads start early), so
+// this kernel is an ordinary launch that lets nothing start before it has ended: whatever follows it in the stream,
+// launched early or not, finds the list complete.
+__global__ void decode_items_kernel(const int* __restrict__ split_start, int n_work, int n_kv, int max_splits, int* __restrict__ items) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_work * n_kv * max_splits) return;
+    const int s = i % max_splits, r = i / max_splits;
+    const int kvh = r % n_kv, w = r / n_kv;
+    const int first = split_start[w], n_splits = split_start[w + 1] - first;
+    if (s < n_splits) items[first * n_kv + kvh * n_splits + s] = pack_item(w, kvh, s);
+}
+
 template <int HD>
 int launch(const CUtensorMap& mkv, DecodeParams p, cudaStream_t s) {
     constexpr size_t stage_bytes = (size_t)2 * (HD / 64) * SPLIT * 128 + Q_ROWS * HD * 2 + 16;
@@ -611,6 +626,19 @@ RS_EXPORT int rs_attention_decode_bf16_supported(int n_q, int n_kv, int hd, int 
 
 RS_EXPORT int rs_attention_decode_bf16_split_keys() { return SPLIT; }
 
+// The list of live items of a step (see decode_item): items[split_start[n_work] * n_kv], to be built once per step
+// and handed to every rs_attention_decode_bf16 call of the step with the same work list, split_start, n_kv.  max_splits:
+// at least the largest number of splits of a sequence (the launch shape).
+RS_EXPORT int rs_attention_decode_build_items(const int* split_start, int n_work, int n_kv, int max_splits, int* items, void* stream) {
+    if (n_work <= 0) return 0;
+    if (split_start == nullptr || items == nullptr || n_kv <= 0 || n_kv > ITEM_MAX_KV || n_work > ITEM_MAX_SEQS || max_splits <= 0 ||
+        max_splits > ITEM_MAX_SPLITS || (long)n_work * n_kv * max_splits > 0x7fff0000L)
+        return (int)cudaErrorInvalidValue;
+    const int n = n_work * n_kv * max_splits;
+    decode_items_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(split_start, n_work, n_kv, max_splits, items);
+    return (int)cudaGetLastError();
+}
+
 // TMA loads per page of an item in the most recent launch: 1 with the 5-d map, else 2 * head size / 64.
 RS_EXPORT int rs_attention_decode_bf16_loads_per_page() { return g_last_loads_per_page; }
 
@@ -619,11 +647,12 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
                                        long page_stride, int num_pages, int page_size, const int* block_table,
                                        int table_stride, const int* q_start, const int* kv_len, const int* work,
                                        int n_work, int n_q, int n_kv, int hd, int window, float scale, int split_keys,
-                                       int max_splits, const int* split_start, float* partial, int partial_slots,
-                                       int* status, void* stream) {
+                                       int max_splits, const int* split_start, const int* items, float* partial,
+                                       int partial_slots, int* status, void* stream) {
     if (n_work <= 0) return 0;
     if (!rs_attention_decode_bf16_supported(n_q, n_kv, hd, page_size) || split_keys != SPLIT || max_splits <= 0 ||
-        partial == nullptr || partial_slots <= 0 || split_start == nullptr || (q_stride % 8) || ((long)q & 15) || ((long)cache & 15) ||
+        partial == nullptr || partial_slots <= 0 || split_start == nullptr || items == nullptr || n_kv > ITEM_MAX_KV ||
+        n_work > ITEM_MAX_SEQS || max_splits > ITEM_MAX_SPLITS || (q_stride % 8) || ((long)q & 15) || ((long)cache & 15) ||
         page_stride != (long)2 * n_kv * page_size * hd || (long)n_work * n_kv * max_splits > 0x7fff0000L)
         return (int)cudaErrorInvalidValue;
     DecodeParams p;
@@ -632,7 +661,7 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
     p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
     p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
+    p.split_start = split_start; p.items = items; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
     p.n_work = n_work; p.max_splits = max_splits;
     p.total = n_work * n_kv * max_splits;          // an upper bound, for the size of the grid
     p.groups = p.depth = 0;

