@@ -256,10 +256,15 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
                 int page = -1;
                 if (lane < pages_per_item && kpos < it.key_hi && kpos + p.page_size > it.key_lo)
                     page = __ldg(p.block_table + (size_t)it.seq * p.table_stride + kpos / p.page_size);
-                const unsigned long long t0 = global_ns();
-                while (n >= *produced + PREFETCH_AHEAD) {
+                unsigned long long t0 = 0;                // the clock is slow to read: every 64 naps only
+                for (uint32_t i = 1; n >= *produced + PREFETCH_AHEAD; ++i) {
                     __nanosleep(200);
-                    if (*abort_flag || global_ns() - t0 > RS_WAIT_LIMIT_NS) { go = false; break; }
+                    if (*abort_flag) { go = false; break; }
+                    if ((i & 63u) == 0u) {
+                        const unsigned long long now = global_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > RS_WAIT_LIMIT_NS) { go = false; break; }
+                    }
                 }
                 if (go && page >= 0 && page < p.num_pages) tma_prefetch_5d(&map_kv, 0, 0, 0, 0, page * 2 * p.n_kv + it.kvh);
             }

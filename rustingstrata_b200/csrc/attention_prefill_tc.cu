@@ -33,7 +33,7 @@ constexpr int PARTS = 2;                // softmax threads per row: each takes 1
                                         // (four threads per row, 16 softmax warps, were 4 % slower: the softmax is not short of warps)
 constexpr int SOFTMAX_WARPS = 4 * PARTS;
 constexpr int MMA_WARP = SOFTMAX_WARPS, TMA_WARP = SOFTMAX_WARPS + 1;
-constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+constexpr int THREADS = (SOFTMAX_WARPS + 3) * 32;        // the warp after TMA_WARP loads the values, TMA_WARP the keys
 constexpr int KV_STAGES = 2;
 
 struct TcParams {
@@ -173,10 +173,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t tmem_base = *tmem_slot;
 
     pdl_launch_dependents();
-    if (warp == TMA_WARP) {
-        // ------------------------------------------------------------ TMA producer: lane i loads page i of a block
+    if (warp >= TMA_WARP) {
+        // ------------------------------------------------------------ TMA producers: one warp streams the keys, the
+        // next one the values; lane i loads page i of a block.  A warp needs of the order of 80 cycles per load it
+        // issues and 800 for a block-table entry from L2.  One warp doing both for keys and values, and looking a
+        // block's pages up while the block before it was on its way, took as long per block of 128 keys as the block
+        // takes everything else (2,400 cycles at pages of 16: per-block timestamps of a throw-away build) and was what
+        // the kernel waited for.  So the two streams have a warp each, and the pages are looked up three blocks ahead.
+        const int kv = warp - TMA_WARP;
         pdl_wait();                                           // q and the portion's keys and values come from the kernel before
-        if (lane == 0) {
+        if (kv == 0 && lane == 0) {
             mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
@@ -184,44 +190,47 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         const int* table = p.block_table + (size_t)seq * p.table_stride;
         const int pages_per_block = BKV / p.page_size;
-        auto lookup = [&](int j) {
+        auto lookup = [&](int j) {                            // the value is not looked at before it is used
             const int kpos = (blk_lo + j) * BKV + lane * p.page_size;
             int page = 0;
-            if (j < n_blocks && lane < pages_per_block && kpos < key_hi && kpos + p.page_size > key_lo) {
+            if (j < n_blocks && lane < pages_per_block && kpos < key_hi && kpos + p.page_size > key_lo)
                 page = __ldg(table + kpos / p.page_size);
-                if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
-            }
             return page;
         };
-        int page = lookup(0);
+        constexpr int AHEAD = 3;
+        int pages[AHEAD];
+#pragma unroll
+        for (int a = 0; a < AHEAD; ++a) pages[a] = lookup(a);
+        const uint32_t tiles = kv ? v_smem : k_smem;
         for (int j = 0; j < n_blocks; ++j) {
             const int s = j & 1;
             const uint32_t par = ((j >> 1) & 1) ^ 1u;
-            const int page_next = lookup(j + 1);              // its latency hides behind the waits below
+            const int page_later = lookup(j + AHEAD);
+            const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
             int ok = 1;
-            for (int kv = 0; kv < 2; ++kv) {
-                const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
-                if (lane == 0) {
-                    ok = mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status) ? 1 : 0;
-                    if (ok) mbar_expect_tx(full, TILE_BYTES);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);          // also orders the expect_tx before every lane's loads
-                if (!ok) break;
-                if (lane < pages_per_block) {
-                    const uint32_t dst = (kv ? v_smem : k_smem) + s * TILE_BYTES + lane * (p.page_size / 8) * GROUP_BYTES;
-                    const int block = (page * 2 + kv) * p.n_kv + kvh;
-                    if (p.one_load_per_page) {
-                        tma_load_5d(dst, &map_kv, 0, 0, 0, 0, block, full);
-                    } else {
-                        for (int g8 = 0; g8 < p.page_size / 8; ++g8)
+            if (lane == 0) {
+                ok = mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status) ? 1 : 0;
+                if (ok) mbar_expect_tx(full, TILE_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);              // also orders the expect_tx before every lane's loads
+            if (!ok) break;
+            int page = pages[0];
+            if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
+            if (lane < pages_per_block) {
+                const uint32_t dst = tiles + s * TILE_BYTES + lane * (p.page_size / 8) * GROUP_BYTES;
+                const int block = (page * 2 + kv) * p.n_kv + kvh;
+                if (p.one_load_per_page) {
+                    tma_load_5d(dst, &map_kv, 0, 0, 0, 0, block, full);
+                } else {
+                    for (int g8 = 0; g8 < p.page_size / 8; ++g8)
 #pragma unroll
-                            for (int h = 0; h < HALVES; ++h)
-                                tma_load_2d(dst + g8 * GROUP_BYTES + h * 1024, &map_kv, h * 64, block * p.page_size + g8 * 8, full);
-                    }
+                        for (int h = 0; h < HALVES; ++h)
+                            tma_load_2d(dst + g8 * GROUP_BYTES + h * 1024, &map_kv, h * 64, block * p.page_size + g8 * 8, full);
                 }
             }
-            if (!ok) break;
-            page = page_next;
+#pragma unroll
+            for (int a = 0; a + 1 < AHEAD; ++a) pages[a] = pages[a + 1];
+            pages[AHEAD - 1] = page_later;
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issuer

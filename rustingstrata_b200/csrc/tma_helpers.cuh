@@ -52,14 +52,19 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 // Bounded wait.  Returns false (and flags the status word, and raises the CTA's abort flag) on expiry.
+// The clock is looked at only after 64 polls have failed, and then every 64 polls: %globaltimer is slow to read
+// (of the order of a microsecond), and a waiter that read it after its first failed poll answered that much later
+// to every barrier it really had to wait for, in every kernel that streams through shared memory.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    for (uint32_t i = 0;; ++i) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
+        if ((i & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > RS_WAIT_LIMIT_NS) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > RS_WAIT_LIMIT_NS) {
                 *abort_flag = 1;
                 atomicOr(status, RS_STATUS_WAIT_EXPIRED);
                 return false;
