@@ -122,14 +122,15 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int HALF_BYTES = 128 * 128;                // 128 rows x 128 bytes
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // one Q, K or V tile
     constexpr int GROUP_BYTES = HALVES * 1024;           // 8 keys of a K or V tile: one swizzle atom per half of the head
-    constexpr int TMEM_COLS = 512;                       // S0 | S1 | O  (128 + 128 + HD columns)
+    constexpr int TMEM_COLS = 512;                       // S0 | S1 | S2 | O  (3 x 128 + HD columns)
+    constexpr int S_BUFS = 3, O_COL = S_BUFS * 128;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     const uint32_t q_smem = base, k_smem = base + TILE_BYTES, v_smem = k_smem + KV_STAGES * TILE_BYTES;
     const uint32_t bar0 = v_smem + KV_STAGES * TILE_BYTES;
-    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full
-    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_FULL = 13, NBAR = 14 };
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[3], p_ready[3], o_full
+    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 12, O_FULL = 15, NBAR = 16 };
     auto bar = [&](int i) { return bar0 + 8u * i; };
     uint8_t* aligned = smem_raw + (base - raw);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
@@ -157,8 +158,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1);
-            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), SOFTMAX_WARPS);
         }
+        for (int s = 0; s < S_BUFS; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), SOFTMAX_WARPS); }
         mbar_init(bar(O_FULL), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -237,31 +238,37 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0 && n_blocks > 0) {
             const uint32_t idesc_qk = idesc_bf16(ROWS, BKV, 0), idesc_pv = idesc_bf16(ROWS, HD, 1);
             bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, p.status);
+            // Scores have three buffers: Q K^T of block j + 2 is issued before P V of block j, so the scores of a block
+            // are ready a whole block before the softmax warps ask for them, and those never wait for this thread
+            // (with two buffers Q K^T (j + 2) could only follow P V (j), which follows the softmax of block j: the two
+            // roles then ran in turn for part of every block).  Buffer (j + 2) % 3 held P of block j - 1, which P V
+            // (j - 1) has read: it was issued earlier by this thread, and the tensor core runs them in order.
             auto issue_qk = [&](int j) {
-                const int s = j & 1;
+                const int s = j & 1, sb = j % S_BUFS;
                 if (!mbar_wait(bar(K_FULL + s), (j >> 1) & 1, abort_flag, p.status)) return false;
                 tc_fence_after();
-                const uint32_t d = tmem_base + s * 128;
+                const uint32_t d = tmem_base + sb * 128;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     umma_ss(d, desc_kmajor(q_smem + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
                             desc_kmajor(k_smem + s * TILE_BYTES + (ks >> 2) * 1024 + (ks & 3) * 32, GROUP_BYTES), idesc_qk, ks ? 1u : 0u);
                 }
                 umma_commit(bar(K_EMPTY + s));           // the K stage is free once these have read it
-                umma_commit(bar(S_FULL + s));
+                umma_commit(bar(S_FULL + sb));
                 return true;
             };
             if (ok) ok = issue_qk(0);
+            if (ok && n_blocks > 1) ok = issue_qk(1);
             for (int j = 0; j < n_blocks && ok; ++j) {
-                const int s = j & 1;
-                if (j + 1 < n_blocks) ok = issue_qk(j + 1);
+                const int s = j & 1, sb = j % S_BUFS;
+                if (j + 2 < n_blocks) ok = issue_qk(j + 2);
                 if (!ok) break;
-                if (!mbar_wait(bar(P_READY + s), (j >> 1) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(bar(P_READY + sb), (j / S_BUFS) & 1, abort_flag, p.status)) break;
                 if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag, p.status)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk)
-                    umma_ts(tmem_base + 256, tmem_base + s * 128 + kk * 8,
+                    umma_ts(tmem_base + O_COL, tmem_base + sb * 128 + kk * 8,
                             desc_mnmajor(v_smem + s * TILE_BYTES + kk * 2 * GROUP_BYTES, 1024, GROUP_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
                 umma_commit(bar(V_EMPTY + s));
                 umma_commit(bar(O_FULL));                 // completion j of this barrier: O holds blocks 0..j
@@ -280,7 +287,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int quarter = warp & 3, part = warp >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t o_addr = lane_base + 256 + part * HO;
+        const uint32_t o_addr = lane_base + O_COL + part * HO;
         const int qpos = qpos0 + r / p.pack;
         float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
@@ -290,10 +297,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tmem_ld_wait();
         };
         for (int j = 0; j < n_blocks; ++j) {
-            const int s = j & 1;
+            const int s = j % S_BUFS;
             const int kb0 = (blk_lo + j) * BKV;
             const int k0 = kb0 + part * HK;                            // first key of this thread's part of the block
-            if (ok) ok = mbar_wait(bar(S_FULL + s), (j >> 1) & 1, abort_flag, p.status);
+            if (ok) ok = mbar_wait(bar(S_FULL + s), (j / S_BUFS) & 1, abort_flag, p.status);
             ok = __all_sync(0xffffffffu, ok);                          // tensor-memory loads and stores are warp-wide
             float x[HK];
             float mx = -INFINITY;
@@ -302,13 +309,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
                                        (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
                 // the row's scores of this part of the block, once, into registers (masked)
+                {
+                    uint32_t v[HK];
 #pragma unroll
-                for (int c = 0; c < HK; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_base + s * 128 + part * HK + c, v);
-                    tmem_ld_wait();
+                    for (int c = 0; c < HK; c += 32) tmem_ld32(lane_base + s * 128 + part * HK + c, v + c);
+                    tmem_ld_wait();                                   // one wait for all of the row's loads
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) x[c + i] = __uint_as_float(v[i]);      // raw scores: the scale goes into the exponent's FMA
+                    for (int i = 0; i < HK; ++i) x[i] = __uint_as_float(v[i]);          // raw scores: the scale goes into the exponent's FMA
                 }
                 if (need_mask) {
 #pragma unroll
