@@ -40,7 +40,7 @@ struct TcParams {
     __nv_bfloat16* out; long out_stride;
     int page_size, num_pages;
     const int* block_table; int table_stride;
-    const int* q_start; const int* kv_len; const int* work;
+    const int* q_start; const int* kv_len; const int* work; int n_work;
     int n_q, n_kv, group, pack, tokens_per_cta;
     int window;
     float scale_log2;
@@ -115,6 +115,9 @@ __device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn_major) {
            ((uint32_t)(m >> 4) << 24);
 }
 
+// What a CTA needs to know of one work item: a tile of query rows (sequence, first query, kv group and heads).
+struct TcItem { int seq, q_off, kvh, head0, row0, n_tok, n_rows, qpos0, key_lo, key_hi, blk_lo, n_blocks; };
+
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams p) {
@@ -129,8 +132,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t base = (raw + 1023u) & ~1023u;
     const uint32_t q_smem = base, k_smem = base + TILE_BYTES, v_smem = k_smem + KV_STAGES * TILE_BYTES;
     const uint32_t bar0 = v_smem + KV_STAGES * TILE_BYTES;
-    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[3], p_ready[3], o_full
-    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 12, O_FULL = 15, NBAR = 16 };
+    // barriers: q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[3], p_ready[3], o_full, o_empty
+    enum { Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 13, O_FULL = 16,
+           O_EMPTY = 17, NBAR = 18 };
     auto bar = [&](int i) { return bar0 + 8u * i; };
     uint8_t* aligned = smem_raw + (base - raw);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
@@ -138,29 +142,52 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float* xchg = reinterpret_cast<float*>(tmem_slot + 4);     // [2 blocks parity][PARTS][ROWS] maxima, then [PARTS][ROWS] sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = p.work[2 * blockIdx.x], q_off = p.work[2 * blockIdx.x + 1];
+
+    // The CTAs stay: one per SM, each walks several items.  An item's start (barriers, tensor memory, the first loads'
+    // latency, the first scores) and its end (the last P V, O read back, normalised and stored) keep the tensor cores
+    // and the softmax warps idle for about as long as four blocks of keys take, which at 2,048 tokens was a third of
+    // a CTA's life.  Here the barriers and the tensor memory are set up once, the next item's queries and first keys
+    // are loaded while this item's last blocks are at work, and its first Q K^T is issued while the softmax warps
+    // store this item's result.  All barrier phases count on across the items (g: blocks before this item, nq: items
+    // before it).  The host sorts the items by the keys they walk, longest first; round r gives CTA b item r G + b or,
+    // in odd rounds, r G + (G - 1 - b), so that every CTA gets long and short ones and the sums come out even.
     const int chunks_per_group = p.group / p.pack;
-    const int kvh = blockIdx.y / chunks_per_group;
-    const int head0 = kvh * p.group + (blockIdx.y % chunks_per_group) * p.pack;
-    const int row0 = p.q_start[seq];
-    const int q_len = p.q_start[seq + 1] - row0;
-    const int kv_len = p.kv_len[seq];
-    const int n_tok = min(p.tokens_per_cta, q_len - q_off);
-    const int n_rows = n_tok * p.pack;
-    const int qpos0 = kv_len - q_len + q_off;
-    const int key_lo = p.window > 0 ? max(0, qpos0 - p.window + 1) : 0;
-    const int key_hi = min(kv_len, qpos0 + n_tok);
-    const int blk_lo = key_lo / BKV, blk_hi = (key_hi + BKV - 1) / BKV;
-    const int n_blocks = blk_hi - blk_lo;
+    const int ny = p.n_kv * chunks_per_group;
+    const int total = p.n_work * ny;
+    const int G = (int)gridDim.x;
+    auto item_of_round = [&](int round) {
+        return round * G + ((round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    };
+    auto get_item = [&](int id) {
+        TcItem I;
+        const int x = id / ny, y = id - x * ny;
+        I.seq = __ldg(p.work + 2 * x);
+        I.q_off = __ldg(p.work + 2 * x + 1);
+        I.kvh = y / chunks_per_group;
+        I.head0 = I.kvh * p.group + (y % chunks_per_group) * p.pack;
+        I.row0 = __ldg(p.q_start + I.seq);
+        const int q_len = __ldg(p.q_start + I.seq + 1) - I.row0;
+        const int kv_len = __ldg(p.kv_len + I.seq);
+        I.n_tok = min(p.tokens_per_cta, q_len - I.q_off);
+        I.n_rows = I.n_tok * p.pack;
+        I.qpos0 = kv_len - q_len + I.q_off;
+        I.key_lo = p.window > 0 ? max(0, I.qpos0 - p.window + 1) : 0;
+        I.key_hi = min(kv_len, I.qpos0 + I.n_tok);
+        I.blk_lo = I.key_lo / BKV;
+        I.n_blocks = (I.key_hi + BKV - 1) / BKV - I.blk_lo;
+        return I;
+    };
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
+        mbar_init(bar(Q_EMPTY), 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1);
         }
         for (int s = 0; s < S_BUFS; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), SOFTMAX_WARPS); }
         mbar_init(bar(O_FULL), 1);
+        mbar_init(bar(O_EMPTY), SOFTMAX_WARPS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -182,96 +209,127 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // takes everything else (2,400 cycles at pages of 16: per-block timestamps of a throw-away build) and was what
         // the kernel waited for.  So the two streams have a warp each, and the pages are looked up three blocks ahead.
         const int kv = warp - TMA_WARP;
-        pdl_wait();                                           // q and the portion's keys and values come from the kernel before
-        if (kv == 0 && lane == 0) {
-            mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
-#pragma unroll
-            for (int h = 0; h < HALVES; ++h)
-                tma_load_3d(q_smem + h * HALF_BYTES, &map_q, h * 64, head0, row0 + q_off, bar(Q_FULL));
-        }
-        const int* table = p.block_table + (size_t)seq * p.table_stride;
         const int pages_per_block = BKV / p.page_size;
-        auto lookup = [&](int j) {                            // the value is not looked at before it is used
-            const int kpos = (blk_lo + j) * BKV + lane * p.page_size;
-            int page = 0;
-            if (j < n_blocks && lane < pages_per_block && kpos < key_hi && kpos + p.page_size > key_lo)
-                page = __ldg(table + kpos / p.page_size);
-            return page;
-        };
-        constexpr int AHEAD = 3;
-        int pages[AHEAD];
-#pragma unroll
-        for (int a = 0; a < AHEAD; ++a) pages[a] = lookup(a);
         const uint32_t tiles = kv ? v_smem : k_smem;
-        for (int j = 0; j < n_blocks; ++j) {
-            const int s = j & 1;
-            const uint32_t par = ((j >> 1) & 1) ^ 1u;
-            const int page_later = lookup(j + AHEAD);
-            const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
-            int ok = 1;
-            if (lane == 0) {
-                ok = mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status) ? 1 : 0;
-                if (ok) mbar_expect_tx(full, TILE_BYTES);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);              // also orders the expect_tx before every lane's loads
-            if (!ok) break;
-            int page = pages[0];
-            if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
-            if (lane < pages_per_block) {
-                const uint32_t dst = tiles + s * TILE_BYTES + lane * (p.page_size / 8) * GROUP_BYTES;
-                const int block = (page * 2 + kv) * p.n_kv + kvh;
-                if (p.one_load_per_page) {
-                    tma_load_5d(dst, &map_kv, 0, 0, 0, 0, block, full);
-                } else {
-                    for (int g8 = 0; g8 < p.page_size / 8; ++g8)
+        pdl_wait();                                           // q and the portion's keys and values come from the kernel before
+        int g = 0, nq = 0;
+        bool alive = true;
+        for (int round = 0; round * G < total && alive; ++round) {
+            const int id = item_of_round(round);
+            if (id >= total) continue;
+            const TcItem I = get_item(id);
+            if (I.n_blocks <= 0) continue;
+            if (kv == 0 && lane == 0) {
+                // the queries' tile is free once the last Q K^T of the item before has read it
+                if (nq == 0 || mbar_wait(bar(Q_EMPTY), (nq - 1) & 1, abort_flag, p.status)) {
+                    mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
 #pragma unroll
-                        for (int h = 0; h < HALVES; ++h)
-                            tma_load_2d(dst + g8 * GROUP_BYTES + h * 1024, &map_kv, h * 64, block * p.page_size + g8 * 8, full);
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_3d(q_smem + h * HALF_BYTES, &map_q, h * 64, I.head0, I.row0 + I.q_off, bar(Q_FULL));
                 }
             }
+            const int* table = p.block_table + (size_t)I.seq * p.table_stride;
+            auto lookup = [&](int j) {                            // the value is not looked at before it is used
+                const int kpos = (I.blk_lo + j) * BKV + lane * p.page_size;
+                int page = 0;
+                if (j < I.n_blocks && lane < pages_per_block && kpos < I.key_hi && kpos + p.page_size > I.key_lo)
+                    page = __ldg(table + kpos / p.page_size);
+                return page;
+            };
+            constexpr int AHEAD = 3;
+            int pages[AHEAD];
 #pragma unroll
-            for (int a = 0; a + 1 < AHEAD; ++a) pages[a] = pages[a + 1];
-            pages[AHEAD - 1] = page_later;
+            for (int a = 0; a < AHEAD; ++a) pages[a] = lookup(a);
+            for (int j = 0; j < I.n_blocks; ++j) {
+                const int jj = g + j;
+                const int s = jj & 1;
+                const uint32_t par = ((jj >> 1) & 1) ^ 1u;
+                const int page_later = lookup(j + AHEAD);
+                const uint32_t full = bar((kv ? V_FULL : K_FULL) + s);
+                int ok = 1;
+                if (lane == 0) {
+                    ok = mbar_wait(bar((kv ? V_EMPTY : K_EMPTY) + s), par, abort_flag, p.status) ? 1 : 0;
+                    if (ok) mbar_expect_tx(full, TILE_BYTES);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);              // also orders the expect_tx before every lane's loads
+                if (!ok) { alive = false; break; }
+                int page = pages[0];
+                if (page < 0 || page >= p.num_pages) { atomicOr(p.status, RS_STATUS_BAD_PAGE); page = 0; }
+                if (lane < pages_per_block) {
+                    const uint32_t dst = tiles + s * TILE_BYTES + lane * (p.page_size / 8) * GROUP_BYTES;
+                    const int block = (page * 2 + kv) * p.n_kv + I.kvh;
+                    if (p.one_load_per_page) {
+                        tma_load_5d(dst, &map_kv, 0, 0, 0, 0, block, full);
+                    } else {
+                        for (int g8 = 0; g8 < p.page_size / 8; ++g8)
+#pragma unroll
+                            for (int h = 0; h < HALVES; ++h)
+                                tma_load_2d(dst + g8 * GROUP_BYTES + h * 1024, &map_kv, h * 64, block * p.page_size + g8 * 8, full);
+                    }
+                }
+#pragma unroll
+                for (int a = 0; a + 1 < AHEAD; ++a) pages[a] = pages[a + 1];
+                pages[AHEAD - 1] = page_later;
+            }
+            g += I.n_blocks;
+            ++nq;
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && n_blocks > 0) {
+        if (lane == 0) {
             const uint32_t idesc_qk = idesc_bf16(ROWS, BKV, 0), idesc_pv = idesc_bf16(ROWS, HD, 1);
-            bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, p.status);
-            // Scores have three buffers: Q K^T of block j + 2 is issued before P V of block j, so the scores of a block
-            // are ready a whole block before the softmax warps ask for them, and those never wait for this thread
-            // (with two buffers Q K^T (j + 2) could only follow P V (j), which follows the softmax of block j: the two
-            // roles then ran in turn for part of every block).  Buffer (j + 2) % 3 held P of block j - 1, which P V
-            // (j - 1) has read: it was issued earlier by this thread, and the tensor core runs them in order.
-            auto issue_qk = [&](int j) {
-                const int s = j & 1, sb = j % S_BUFS;
-                if (!mbar_wait(bar(K_FULL + s), (j >> 1) & 1, abort_flag, p.status)) return false;
-                tc_fence_after();
-                const uint32_t d = tmem_base + sb * 128;
+            int g = 0, nq = 0;
+            bool ok = true;
+            for (int round = 0; round * G < total && ok; ++round) {
+                const int id = item_of_round(round);
+                if (id >= total) continue;
+                const TcItem I = get_item(id);
+                const int n_blocks = I.n_blocks;
+                if (n_blocks <= 0) continue;
+                ok = mbar_wait(bar(Q_FULL), nq & 1, abort_flag, p.status);
+                // Scores have three buffers: Q K^T of block j + 2 is issued before P V of block j, so the scores of a
+                // block are ready a whole block before the softmax warps ask for them, and those never wait for this
+                // thread (with two buffers Q K^T (j + 2) could only follow P V (j), which follows the softmax of block
+                // j: the two roles then ran in turn for part of every block).  Buffer (j + 2) % 3 held P of block
+                // j - 1, which P V (j - 1) has read: it was issued earlier by this thread, and the tensor core runs
+                // them in order.
+                auto issue_qk = [&](int j) {
+                    const int jj = g + j;
+                    const int s = jj & 1, sb = jj % S_BUFS;
+                    if (!mbar_wait(bar(K_FULL + s), (jj >> 1) & 1, abort_flag, p.status)) return false;
+                    tc_fence_after();
+                    const uint32_t d = tmem_base + sb * 128;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    umma_ss(d, desc_kmajor(q_smem + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
-                            desc_kmajor(k_smem + s * TILE_BYTES + (ks >> 2) * 1024 + (ks & 3) * 32, GROUP_BYTES), idesc_qk, ks ? 1u : 0u);
+                    for (int ks = 0; ks < HD / 16; ++ks) {
+                        umma_ss(d, desc_kmajor(q_smem + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
+                                desc_kmajor(k_smem + s * TILE_BYTES + (ks >> 2) * 1024 + (ks & 3) * 32, GROUP_BYTES), idesc_qk, ks ? 1u : 0u);
+                    }
+                    umma_commit(bar(K_EMPTY + s));           // the K stage is free once these have read it
+                    umma_commit(bar(S_FULL + sb));
+                    if (j == n_blocks - 1) umma_commit(bar(Q_EMPTY));      // ... and so are the queries after the item's last block
+                    return true;
+                };
+                if (ok) ok = issue_qk(0);
+                if (ok && n_blocks > 1) ok = issue_qk(1);
+                for (int j = 0; j < n_blocks && ok; ++j) {
+                    const int jj = g + j;
+                    const int s = jj & 1, sb = jj % S_BUFS;
+                    if (j + 2 < n_blocks) ok = issue_qk(j + 2);
+                    if (!ok) break;
+                    if (!mbar_wait(bar(P_READY + sb), (jj / S_BUFS) & 1, abort_flag, p.status)) { ok = false; break; }
+                    // the first P V of an item overwrites O: the softmax warps must have read the item before out of it
+                    if (j == 0 && nq > 0 && !mbar_wait(bar(O_EMPTY), (nq - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                    if (!mbar_wait(bar(V_FULL + s), (jj >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < BKV / 16; ++kk)
+                        umma_ts(tmem_base + O_COL, tmem_base + sb * 128 + kk * 8,
+                                desc_mnmajor(v_smem + s * TILE_BYTES + kk * 2 * GROUP_BYTES, 1024, GROUP_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
+                    umma_commit(bar(V_EMPTY + s));
+                    umma_commit(bar(O_FULL));                 // completion g + j of this barrier: O holds the item's blocks 0..j
                 }
-                umma_commit(bar(K_EMPTY + s));           // the K stage is free once these have read it
-                umma_commit(bar(S_FULL + sb));
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
-            if (ok && n_blocks > 1) ok = issue_qk(1);
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                const int s = j & 1, sb = j % S_BUFS;
-                if (j + 2 < n_blocks) ok = issue_qk(j + 2);
-                if (!ok) break;
-                if (!mbar_wait(bar(P_READY + sb), (j / S_BUFS) & 1, abort_flag, p.status)) break;
-                if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag, p.status)) break;
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < BKV / 16; ++kk)
-                    umma_ts(tmem_base + O_COL, tmem_base + sb * 128 + kk * 8,
-                            desc_mnmajor(v_smem + s * TILE_BYTES + kk * 2 * GROUP_BYTES, 1024, GROUP_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
-                umma_commit(bar(V_EMPTY + s));
-                umma_commit(bar(O_FULL));                 // completion j of this barrier: O holds blocks 0..j
+                g += n_blocks;
+                ++nq;
             }
         }
     } else {
@@ -279,7 +337,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // The warps w, w + 4, w + 8, ... own the same 32 rows (tensor-memory lanes 32 (w & 3) ..): warp number `part`
         // of them takes the keys [part * HK, +HK) of a block and the head dims [part * HO, +HO) of O.  They exchange
         // their row maxima through shared memory once per block; their partial sums meet at the end.  A warp whose
-        // wait ran out keeps walking the blocks without touching them, so that the named barriers stay in step.
+        // wait ran out keeps walking the items and blocks without touching them, so that the named barriers stay in step.
         constexpr int HK = BKV / PARTS, HO = HD / PARTS;
         static_assert(HK % 32 == 0 && (HO % 32 == 0 || HO == 16), "scores in loads of 32 columns; O in loads of 32 or 16 columns");
         constexpr int OC = HO >= 32 ? 32 : 16;       // columns of O per load
@@ -288,133 +346,147 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t o_addr = lane_base + O_COL + part * HO;
-        const int qpos = qpos0 + r / p.pack;
-        float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
         auto row_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + quarter), "n"(PARTS * 32) : "memory"); };
-        auto load_o = [&](int c, uint32_t* v) {
-            if (OC == 32) tmem_ld32(o_addr + c, v); else tmem_ld16(o_addr + c, v);
-            tmem_ld_wait();
-        };
-        for (int j = 0; j < n_blocks; ++j) {
-            const int s = j % S_BUFS;
-            const int kb0 = (blk_lo + j) * BKV;
-            const int k0 = kb0 + part * HK;                            // first key of this thread's part of the block
-            if (ok) ok = mbar_wait(bar(S_FULL + s), (j / S_BUFS) & 1, abort_flag, p.status);
-            ok = __all_sync(0xffffffffu, ok);                          // tensor-memory loads and stores are warp-wide
-            float x[HK];
-            float mx = -INFINITY;
+        int g = 0;
+        for (int round = 0; round * G < total; ++round) {
+            const int id = item_of_round(round);
+            if (id >= total) continue;
+            const TcItem I = get_item(id);
+            const int n_blocks = I.n_blocks;
+            if (n_blocks <= 0) continue;
+            const int qpos0 = I.qpos0, key_lo = I.key_lo, key_hi = I.key_hi, n_tok = I.n_tok;
+            const int qpos = qpos0 + r / p.pack;
+            float m_used = -INFINITY, l_run = 0.f;
+            for (int j = 0; j < n_blocks; ++j) {
+                const int jj = g + j;
+                const int s = jj % S_BUFS;
+                const int kb0 = (I.blk_lo + j) * BKV;
+                const int k0 = kb0 + part * HK;                            // first key of this thread's part of the block
+                if (ok) ok = mbar_wait(bar(S_FULL + s), (jj / S_BUFS) & 1, abort_flag, p.status);
+                ok = __all_sync(0xffffffffu, ok);                          // tensor-memory loads and stores are warp-wide
+                float x[HK];
+                float mx = -INFINITY;
+                if (ok) {
+                    tc_fence_after();
+                    const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
+                                           (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
+                    // the row's scores of this part of the block, once, into registers (masked)
+                    {
+                        uint32_t v[HK];
+#pragma unroll
+                        for (int c = 0; c < HK; c += 32) tmem_ld32(lane_base + s * 128 + part * HK + c, v + c);
+                        tmem_ld_wait();                                   // one wait for all of the row's loads
+#pragma unroll
+                        for (int i = 0; i < HK; ++i) x[i] = __uint_as_float(v[i]);          // raw scores: the scale goes into the exponent's FMA
+                    }
+                    if (need_mask) {
+#pragma unroll
+                        for (int i = 0; i < HK; ++i) {
+                            const int kpos = k0 + i;
+                            const bool vis = kpos <= qpos && kpos < key_hi && kpos >= key_lo && (p.window <= 0 || kpos > qpos - p.window);
+                            x[i] = vis ? x[i] : -INFINITY;
+                        }
+                    }
+                    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < HK; i += 4) {
+                        mx0 = fmaxf(mx0, x[i]); mx1 = fmaxf(mx1, x[i + 1]); mx2 = fmaxf(mx2, x[i + 2]); mx3 = fmaxf(mx3, x[i + 3]);
+                    }
+                    mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;         // the scale is positive: it commutes with the maximum
+                }
+                xchg[((j & 1) * PARTS + part) * ROWS + r] = mx;
+                row_sync();
+                float m_blk = mx;
+#pragma unroll
+                for (int q = 0; q < PARTS; ++q) m_blk = fmaxf(m_blk, xchg[((j & 1) * PARTS + q) * ROWS + r]);
+                if (!ok) continue;
+                // The reference maximum only moves when the block's maximum exceeds it by more than 2^8 (or it was
+                // still -inf): then everything accumulated so far, O in tensor memory included, is rescaled.  All
+                // threads of a row see the same numbers and take the same decision.
+                const bool move = m_blk > m_used + RESCALE_ABOVE || (m_used == -INFINITY && m_blk > -INFINITY);
+                if (__any_sync(0xffffffffu, move)) {
+                    const float corr = move ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_blk)) : 1.f;
+                    if (j > 0) {                                          // O holds the products of the item's blocks 0..j-1
+                        ok = __all_sync(0xffffffffu, mbar_wait(bar(O_FULL), (jj - 1) & 1, abort_flag, p.status));
+                        if (ok) {
+                            tc_fence_after();
+#pragma unroll
+                            for (int c = 0; c < HO; c += OC) {
+                                uint32_t v[32];
+                                if (OC == 32) tmem_ld32(o_addr + c, v); else tmem_ld16(o_addr + c, v);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < OC; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                                tmem_st16(o_addr + c, v);
+                                if (OC == 32) tmem_st16(o_addr + c + 16, v + 16);
+                            }
+                            tmem_st_wait();
+                        }
+                    }
+                    l_run *= corr;
+                    if (move) m_used = m_blk;
+                }
+                if (!ok) continue;
+                // P = 2^(x - m), its sum, and P as bfloat16 pairs written over S
+                const float sub = (m_used == -INFINITY) ? 0.f : m_used;     // nothing visible yet: every x is -inf, P = 0
+                float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+                for (int c = 0; c < HK; c += 32) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float e0 = fast_exp2(fmaf(x[c + i], p.scale_log2, -sub)), e1 = fast_exp2(fmaf(x[c + i + 1], p.scale_log2, -sub));
+                        rs0 += e0; rs1 += e1;
+                        __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
+                        pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
+                    }
+                    tmem_st16(lane_base + s * 128 + ((part * HK + c) >> 1), pk);
+                }
+                tmem_st_wait();
+                l_run += rs0 + rs1;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(P_READY + s));
+            }
+            // the row's sum: all parts used the same reference maxima, so their partial sums simply add (in a fixed order)
+            xchg[(2 * PARTS + part) * ROWS + r] = l_run;
+            row_sync();
+            l_run = 0.f;
+#pragma unroll
+            for (int q = 0; q < PARTS; ++q) l_run += xchg[(2 * PARTS + q) * ROWS + r];
+            if (ok) ok = mbar_wait(bar(O_FULL), (g + n_blocks - 1) & 1, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 tc_fence_after();
-                const bool need_mask = (kb0 + BKV - 1 > qpos0) || (kb0 + BKV > key_hi) || kb0 < key_lo ||
-                                       (p.window > 0 && kb0 <= qpos0 + n_tok - 1 - p.window);
-                // the row's scores of this part of the block, once, into registers (masked)
-                {
-                    uint32_t v[HK];
+                // the whole of this thread's part of the row leaves tensor memory first, so that the next item's P V
+                // may start while the result is normalised and stored
+                uint32_t v[HO];
 #pragma unroll
-                    for (int c = 0; c < HK; c += 32) tmem_ld32(lane_base + s * 128 + part * HK + c, v + c);
-                    tmem_ld_wait();                                   // one wait for all of the row's loads
-#pragma unroll
-                    for (int i = 0; i < HK; ++i) x[i] = __uint_as_float(v[i]);          // raw scores: the scale goes into the exponent's FMA
+                for (int c = 0; c < HO; c += OC) {                         // warp-collective: rows beyond the tile load too
+                    if (OC == 32) tmem_ld32(o_addr + c, v + c); else tmem_ld16(o_addr + c, v + c);
                 }
-                if (need_mask) {
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(O_EMPTY));
+                if (r < I.n_rows) {
+                    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                    __nv_bfloat16* dst = p.out + (size_t)(I.row0 + I.q_off + r / p.pack) * p.out_stride +
+                                         (size_t)(I.head0 + r % p.pack) * HD + part * HO;
 #pragma unroll
-                    for (int i = 0; i < HK; ++i) {
-                        const int kpos = k0 + i;
-                        const bool vis = kpos <= qpos && kpos < key_hi && kpos >= key_lo && (p.window <= 0 || kpos > qpos - p.window);
-                        x[i] = vis ? x[i] : -INFINITY;
-                    }
-                }
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-                for (int i = 0; i < HK; i += 4) {
-                    mx0 = fmaxf(mx0, x[i]); mx1 = fmaxf(mx1, x[i + 1]); mx2 = fmaxf(mx2, x[i + 2]); mx3 = fmaxf(mx3, x[i + 3]);
-                }
-                mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;         // the scale is positive: it commutes with the maximum
-            }
-            xchg[((j & 1) * PARTS + part) * ROWS + r] = mx;
-            row_sync();
-            float m_blk = mx;
-#pragma unroll
-            for (int q = 0; q < PARTS; ++q) m_blk = fmaxf(m_blk, xchg[((j & 1) * PARTS + q) * ROWS + r]);
-            if (!ok) continue;
-            // The reference maximum only moves when the block's maximum exceeds it by more than 2^8 (or it was
-            // still -inf): then everything accumulated so far, O in tensor memory included, is rescaled.  All
-            // threads of a row see the same numbers and take the same decision.
-            const bool move = m_blk > m_used + RESCALE_ABOVE || (m_used == -INFINITY && m_blk > -INFINITY);
-            if (__any_sync(0xffffffffu, move)) {
-                const float corr = move ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_blk)) : 1.f;
-                if (j > 0) {                                          // O holds the products of blocks 0..j-1
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(O_FULL), (j - 1) & 1, abort_flag, p.status));
-                    if (ok) {
-                        tc_fence_after();
-#pragma unroll
-                        for (int c = 0; c < HO; c += OC) {
-                            uint32_t v[32];
-                            load_o(c, v);
-#pragma unroll
-                            for (int i = 0; i < OC; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                            tmem_st16(o_addr + c, v);
-                            if (OC == 32) tmem_st16(o_addr + c + 16, v + 16);
-                        }
-                        tmem_st_wait();
-                    }
-                }
-                l_run *= corr;
-                if (move) m_used = m_blk;
-            }
-            if (!ok) continue;
-            // P = 2^(x - m), its sum, and P as bfloat16 pairs written over S
-            const float sub = (m_used == -INFINITY) ? 0.f : m_used;     // nothing visible yet: every x is -inf, P = 0
-            float rs0 = 0.f, rs1 = 0.f;
-#pragma unroll
-            for (int c = 0; c < HK; c += 32) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float e0 = fast_exp2(fmaf(x[c + i], p.scale_log2, -sub)), e1 = fast_exp2(fmaf(x[c + i + 1], p.scale_log2, -sub));
-                    rs0 += e0; rs1 += e1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
-                }
-                tmem_st16(lane_base + s * 128 + ((part * HK + c) >> 1), pk);
-            }
-            tmem_st_wait();
-            l_run += rs0 + rs1;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_READY + s));
-        }
-        // the row's sum: all parts used the same reference maxima, so their partial sums simply add (in a fixed order)
-        xchg[(2 * PARTS + part) * ROWS + r] = l_run;
-        row_sync();
-        l_run = 0.f;
-#pragma unroll
-        for (int q = 0; q < PARTS; ++q) l_run += xchg[(2 * PARTS + q) * ROWS + r];
-        if (ok && n_blocks > 0) ok = mbar_wait(bar(O_FULL), (n_blocks - 1) & 1, abort_flag, p.status);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok && n_blocks > 0) {
-            tc_fence_after();
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            __nv_bfloat16* dst = p.out + (size_t)(row0 + q_off + r / p.pack) * p.out_stride + (size_t)(head0 + r % p.pack) * HD +
-                                 part * HO;
-#pragma unroll
-            for (int c = 0; c < HO; c += OC) {
-                uint32_t v[32];
-                load_o(c, v);                                          // warp-collective: rows beyond the tile load too
-                if (r < n_rows) {
-#pragma unroll
-                    for (int d = 0; d < OC; d += 8) {
+                    for (int d = 0; d < HO; d += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[d + 2 * u]) * inv, __uint_as_float(v[d + 2 * u + 1]) * inv);
                             w[u] = *reinterpret_cast<uint32_t*>(&b);
                         }
-                        *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
+            g += n_blocks;
         }
     }
     __syncthreads();
@@ -514,7 +586,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    return rs_launch_pdl(kern, dim3(n_work, p.n_kv * (p.group / p.pack)), dim3(THREADS), (size_t)smem, s, mq, mkv, p);
+    const long total = (long)n_work * p.n_kv * (p.group / p.pack);
+    const int grid = (int)(total < rs_tma::sm_count() ? total : rs_tma::sm_count());      // one CTA per SM; each walks its items
+    return rs_launch_pdl(kern, dim3(grid), dim3(THREADS), (size_t)smem, s, mq, mkv, p);
 }
 }  // namespace
 
@@ -541,7 +615,7 @@ RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows,
         return (int)cudaErrorInvalidValue;
     TcParams p;
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.page_size = page_size; p.num_pages = num_pages;
-    p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
+    p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work; p.n_work = n_work;
     p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.pack = pack_of(p.group); p.tokens_per_cta = ROWS / p.pack;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
     CUtensorMap mq, mkv;
