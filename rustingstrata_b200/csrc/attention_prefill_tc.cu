@@ -35,13 +35,14 @@ constexpr int SOFTMAX_WARPS = 4 * PARTS;
 constexpr int MMA_WARP = SOFTMAX_WARPS, TMA_WARP = SOFTMAX_WARPS + 1;
 constexpr int THREADS = (SOFTMAX_WARPS + 3) * 32;        // the warp after TMA_WARP loads the values, TMA_WARP the keys
 constexpr int KV_STAGES = 2;
+constexpr int LOCAL_ITEMS = 64;        // items of a CTA whose description is kept in shared memory (later ones are worked out when met)
 
 struct TcParams {
     __nv_bfloat16* out; long out_stride;
     int page_size, num_pages;
     const int* block_table; int table_stride;
     const int* q_start; const int* kv_len; const int* work; int n_work;
-    int n_q, n_kv, group, pack, tokens_per_cta;
+    int n_q, n_kv, group, pack, pack_shift, tokens_per_cta;      // pack = 1 << pack_shift heads side by side in a tile
     int window;
     float scale_log2;
     int* status;
@@ -140,6 +141,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xchg = reinterpret_cast<float*>(tmem_slot + 4);     // [2 blocks parity][PARTS][ROWS] maxima, then [PARTS][ROWS] sums
+    TcItem* item_table = reinterpret_cast<TcItem*>(xchg + 3 * PARTS * ROWS);                       // [LOCAL_ITEMS]
+    uint8_t* stage_out = reinterpret_cast<uint8_t*>(item_table + LOCAL_ITEMS);                     // [SOFTMAX_WARPS][32 rows][HD / PARTS] bf16
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -158,7 +161,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto item_of_round = [&](int round) {
         return round * G + ((round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
     };
-    auto get_item = [&](int id) {
+    auto compute_item = [&](int id) {
         TcItem I;
         const int x = id / ny, y = id - x * ny;
         I.seq = __ldg(p.work + 2 * x);
@@ -177,6 +180,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         I.n_blocks = (I.key_hi + BKV - 1) / BKV - I.blk_lo;
         return I;
     };
+    // What the items of this CTA's first rounds are is worked out once, side by side (three dependent loads each), and
+    // kept in shared memory: every role looks an item up when it gets there, and none waits for global memory then.
+    if (threadIdx.x < LOCAL_ITEMS) {
+        const int id = item_of_round(threadIdx.x);
+        if (threadIdx.x * G < total && id < total) item_table[threadIdx.x] = compute_item(id);
+    }
+    auto get_item = [&](int round, int id) { return round < LOCAL_ITEMS ? item_table[round] : compute_item(id); };
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
@@ -217,7 +227,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int round = 0; round * G < total && alive; ++round) {
             const int id = item_of_round(round);
             if (id >= total) continue;
-            const TcItem I = get_item(id);
+            const TcItem I = get_item(round, id);
             if (I.n_blocks <= 0) continue;
             if (kv == 0 && lane == 0) {
                 // the queries' tile is free once the last Q K^T of the item before has read it
@@ -283,7 +293,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int round = 0; round * G < total && ok; ++round) {
                 const int id = item_of_round(round);
                 if (id >= total) continue;
-                const TcItem I = get_item(id);
+                const TcItem I = get_item(round, id);
                 const int n_blocks = I.n_blocks;
                 if (n_blocks <= 0) continue;
                 ok = mbar_wait(bar(Q_FULL), nq & 1, abort_flag, p.status);
@@ -352,11 +362,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int round = 0; round * G < total; ++round) {
             const int id = item_of_round(round);
             if (id >= total) continue;
-            const TcItem I = get_item(id);
+            const TcItem I = get_item(round, id);
             const int n_blocks = I.n_blocks;
             if (n_blocks <= 0) continue;
             const int qpos0 = I.qpos0, key_lo = I.key_lo, key_hi = I.key_hi, n_tok = I.n_tok;
-            const int qpos = qpos0 + r / p.pack;
+            const int qpos = qpos0 + (r >> p.pack_shift);
             float m_used = -INFINITY, l_run = 0.f;
             for (int j = 0; j < n_blocks; ++j) {
                 const int jj = g + j;
@@ -381,12 +391,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         for (int i = 0; i < HK; ++i) x[i] = __uint_as_float(v[i]);          // raw scores: the scale goes into the exponent's FMA
                     }
                     if (need_mask) {
+                        // the keys a row sees are an interval: one subtraction and one unsigned comparison per score
+                        const int first = max(key_lo, p.window > 0 ? qpos - p.window + 1 : 0) - k0;
+                        const unsigned n_vis = (unsigned)max(0, min(qpos + 1, key_hi) - k0 - first);
 #pragma unroll
-                        for (int i = 0; i < HK; ++i) {
-                            const int kpos = k0 + i;
-                            const bool vis = kpos <= qpos && kpos < key_hi && kpos >= key_lo && (p.window <= 0 || kpos > qpos - p.window);
-                            x[i] = vis ? x[i] : -INFINITY;
-                        }
+                        for (int i = 0; i < HK; ++i) x[i] = (unsigned)(i - first) < n_vis ? x[i] : -INFINITY;
                     }
                     float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -470,21 +479,36 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(O_EMPTY));
-                if (r < I.n_rows) {
-                    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-                    __nv_bfloat16* dst = p.out + (size_t)(I.row0 + I.q_off + r / p.pack) * p.out_stride +
-                                         (size_t)(I.head0 + r % p.pack) * HD + part * HO;
+                // Normalised and rounded, the thread's part of its row goes to the warp's staging rows in shared memory
+                // (16-byte chunks, swizzled by the row), and comes back with consecutive lanes on consecutive chunks of
+                // a row: a store instruction then covers whole 128-byte lines.  Stored straight from the registers,
+                // every lane of an instruction hit a line of its own, 256 lines per warp, and for as long as that took
+                // the MMA thread could not issue the next item's first Q K^T (they share the queue to the memory pipes).
+                constexpr int CH = HO / 8;                                 // 16-byte chunks per row part
+                constexpr int PITCH = HO * 2, ROWS_PER_LINE = 128 / PITCH > 0 ? 128 / PITCH : 1;
+                uint8_t* mine = stage_out + (size_t)warp * 32 * PITCH;
+                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
-                    for (int d = 0; d < HO; d += 8) {
-                        uint32_t w[4];
+                for (int c = 0; c < CH; ++c) {
+                    uint32_t w[4];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[d + 2 * u]) * inv, __uint_as_float(v[d + 2 * u + 1]) * inv);
-                            w[u] = *reinterpret_cast<uint32_t*>(&b);
-                        }
-                        *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int u = 0; u < 4; ++u) {
+                        __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2 * u]) * inv, __uint_as_float(v[8 * c + 2 * u + 1]) * inv);
+                        w[u] = *reinterpret_cast<uint32_t*>(&b);
                     }
+                    *reinterpret_cast<uint4*>(mine + lane * PITCH + ((c ^ ((lane / ROWS_PER_LINE) & (CH - 1))) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < CH; ++k) {
+                    const int lr = k * (32 / CH) + lane / CH, c = lane % CH;   // row of the warp's 32, chunk of the row part
+                    const int rr = quarter * 32 + lr;
+                    const uint4 val = *reinterpret_cast<const uint4*>(mine + lr * PITCH + ((c ^ ((lr / ROWS_PER_LINE) & (CH - 1))) << 4));
+                    if (rr < I.n_rows)
+                        *reinterpret_cast<uint4*>(p.out + (size_t)(I.row0 + I.q_off + (rr >> p.pack_shift)) * p.out_stride +
+                                                  (I.head0 + (rr & (p.pack - 1))) * HD + part * HO + c * 8) = val;
+                }
+                __syncwarp();                                              // the rows are read before the next item writes them
             }
             g += n_blocks;
         }
@@ -578,7 +602,8 @@ int cached_page_map(const void* cache, int num_pages, int n_kv, int page_size, i
 
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int n_work, cudaStream_t s) {
-    constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 17 + 64 + 3 * PARTS * ROWS * 4;
+    constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 18 + 256 + 3 * PARTS * ROWS * 4 +
+                         LOCAL_ITEMS * (int)sizeof(TcItem) + ROWS * HD * 2;
     auto kern = prefill_attention_tc_kernel<HD>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -617,6 +642,8 @@ RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows,
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.page_size = page_size; p.num_pages = num_pages;
     p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work; p.n_work = n_work;
     p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.pack = pack_of(p.group); p.tokens_per_cta = ROWS / p.pack;
+    p.pack_shift = 0;
+    while ((1 << p.pack_shift) < p.pack) ++p.pack_shift;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
     CUtensorMap mq, mkv;
     int rc = cached_q_map(q, q_stride, q_rows, n_q, hd, p.pack, &mq);
