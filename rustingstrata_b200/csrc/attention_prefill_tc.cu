@@ -47,6 +47,7 @@ struct TcParams {
     float scale_log2;
     int* status;
     int one_load_per_page;             // the 5-d map of the cache is in use (else 2-d loads of 8 keys x 64 dims)
+    int out_by_tma;                    // the result has a tensor map: whole tiles are stored by the TMA unit
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
@@ -54,6 +55,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
+// shared memory -> global, tiled; completion is tracked by the issuing thread's bulk groups
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -121,7 +130,8 @@ struct TcItem { int seq, q_off, kvh, head0, row0, n_tok, n_rows, qpos0, key_lo, 
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
-prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams p) {
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            const __grid_constant__ CUtensorMap map_out, const TcParams p) {
     constexpr int HALVES = HD / 64;                      // 64-wide (128-byte) column blocks of a head
     constexpr int HALF_BYTES = 128 * 128;                // 128 rows x 128 bytes
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // one Q, K or V tile
@@ -133,16 +143,23 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t base = (raw + 1023u) & ~1023u;
     const uint32_t q_smem = base, k_smem = base + TILE_BYTES, v_smem = k_smem + KV_STAGES * TILE_BYTES;
     const uint32_t bar0 = v_smem + KV_STAGES * TILE_BYTES;
-    // barriers: q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[3], p_ready[3], o_full, o_empty
+    // barriers: q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[3], p_ready[3], o_full[3], o_empty.
+    // A wait by parity cannot tell "this phase is over" from "the phase before the one before it is not over yet".  Every
+    // barrier but o_full is waited for phase by phase, so its waiter is never that far ahead.  The softmax warps look at
+    // o_full only when they rescale O and at an item's end, and with three score buffers they can be two P V ahead of
+    // the tensor core (values that arrive late hold P V up, scores do not need them): block b's P V completes barrier
+    // b % 3, and scores of block b exist only after P V (b - 3) is over, so a waiter is at most one phase ahead.
     enum { Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 13, O_FULL = 16,
-           O_EMPTY = 17, NBAR = 18 };
+           O_EMPTY = 19, NBAR = 20 };
     auto bar = [&](int i) { return bar0 + 8u * i; };
     uint8_t* aligned = smem_raw + (base - raw);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + (bar0 - base) + 8 * NBAR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xchg = reinterpret_cast<float*>(tmem_slot + 4);     // [2 blocks parity][PARTS][ROWS] maxima, then [PARTS][ROWS] sums
     TcItem* item_table = reinterpret_cast<TcItem*>(xchg + 3 * PARTS * ROWS);                       // [LOCAL_ITEMS]
-    uint8_t* stage_out = reinterpret_cast<uint8_t*>(item_table + LOCAL_ITEMS);                     // [SOFTMAX_WARPS][32 rows][HD / PARTS] bf16
+    // results on their way out: [SOFTMAX_WARPS][32 rows][HD / PARTS] bf16, which for 64 dims per part is the layout of
+    // the query tile ([half of the head][row][128 bytes], chunks swizzled by the row), 1 KiB aligned for the TMA unit
+    uint8_t* stage_out = aligned + ((reinterpret_cast<uint8_t*>(item_table + LOCAL_ITEMS) - aligned + 1023) & ~(size_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -195,8 +212,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1);
         }
-        for (int s = 0; s < S_BUFS; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), SOFTMAX_WARPS); }
-        mbar_init(bar(O_FULL), 1);
+        for (int s = 0; s < S_BUFS; ++s) {
+            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_READY + s), SOFTMAX_WARPS); mbar_init(bar(O_FULL + s), 1);
+        }
         mbar_init(bar(O_EMPTY), SOFTMAX_WARPS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -336,7 +354,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         umma_ts(tmem_base + O_COL, tmem_base + sb * 128 + kk * 8,
                                 desc_mnmajor(v_smem + s * TILE_BYTES + kk * 2 * GROUP_BYTES, 1024, GROUP_BYTES), idesc_pv, (j | kk) ? 1u : 0u);
                     umma_commit(bar(V_EMPTY + s));
-                    umma_commit(bar(O_FULL));                 // completion g + j of this barrier: O holds the item's blocks 0..j
+                    umma_commit(bar(O_FULL + sb));            // O holds the item's blocks 0..j
                 }
                 g += n_blocks;
                 ++nq;
@@ -417,7 +435,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (__any_sync(0xffffffffu, move)) {
                     const float corr = move ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_blk)) : 1.f;
                     if (j > 0) {                                          // O holds the products of the item's blocks 0..j-1
-                        ok = __all_sync(0xffffffffu, mbar_wait(bar(O_FULL), (jj - 1) & 1, abort_flag, p.status));
+                        ok = __all_sync(0xffffffffu, mbar_wait(bar(O_FULL + (jj - 1) % S_BUFS), ((jj - 1) / S_BUFS) & 1, abort_flag, p.status));
                         if (ok) {
                             tc_fence_after();
 #pragma unroll
@@ -464,8 +482,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             l_run = 0.f;
 #pragma unroll
             for (int q = 0; q < PARTS; ++q) l_run += xchg[(2 * PARTS + q) * ROWS + r];
-            if (ok) ok = mbar_wait(bar(O_FULL), (g + n_blocks - 1) & 1, abort_flag, p.status);
+            if (ok) ok = mbar_wait(bar(O_FULL + (g + n_blocks - 1) % S_BUFS), ((g + n_blocks - 1) / S_BUFS) & 1, abort_flag, p.status);
             ok = __all_sync(0xffffffffu, ok);
+            // Normalised and rounded, the thread's part of its row goes to the warp's staging rows in shared memory
+            // (16-byte chunks, swizzled by the row).  Whole tiles of 64 dims per part then leave through the TMA unit:
+            // the staging rows are laid out as the query tile is, one thread issues two stores, and nothing queues up
+            // in front of the other warps' memory instructions.  (Stored straight from the registers, every lane of
+            // an instruction hit a line of its own, 256 lines per warp, and for as long as that took the MMA thread
+            // could not issue the next item's first Q K^T: they share the queue to the memory pipes.)  A sequence's
+            // last, partial tile is read back with consecutive lanes on consecutive chunks of a row and stored row by
+            // row, because the rows after it in the buffer belong to the next sequence.  The barriers among the
+            // softmax warps are taken by all of them, also by a warp whose wait ran out.
+            constexpr int CH = HO / 8;                                 // 16-byte chunks per row part
+            constexpr int PITCH = HO * 2, ROWS_PER_LINE = 128 / PITCH > 0 ? 128 / PITCH : 1;
+            const bool tma_out = HO == 64 && p.out_by_tma;
+            const bool tile_by_tma = tma_out && I.n_tok == p.tokens_per_cta;
+            uint8_t* mine = stage_out + (size_t)warp * 32 * PITCH;
+            if (tma_out) {
+                if (warp == 0 && lane == 0) tma_store_wait_read();       // the store of the item before has read the staging rows
+                asm volatile("bar.sync 5, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+            }
             if (ok) {
                 tc_fence_after();
                 // the whole of this thread's part of the row leaves tensor memory first, so that the next item's P V
@@ -479,14 +515,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(O_EMPTY));
-                // Normalised and rounded, the thread's part of its row goes to the warp's staging rows in shared memory
-                // (16-byte chunks, swizzled by the row), and comes back with consecutive lanes on consecutive chunks of
-                // a row: a store instruction then covers whole 128-byte lines.  Stored straight from the registers,
-                // every lane of an instruction hit a line of its own, 256 lines per warp, and for as long as that took
-                // the MMA thread could not issue the next item's first Q K^T (they share the queue to the memory pipes).
-                constexpr int CH = HO / 8;                                 // 16-byte chunks per row part
-                constexpr int PITCH = HO * 2, ROWS_PER_LINE = 128 / PITCH > 0 ? 128 / PITCH : 1;
-                uint8_t* mine = stage_out + (size_t)warp * 32 * PITCH;
                 const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
@@ -498,6 +526,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     }
                     *reinterpret_cast<uint4*>(mine + lane * PITCH + ((c ^ ((lane / ROWS_PER_LINE) & (CH - 1))) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+            }
+            if (tile_by_tma) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 6, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+                if (ok && warp == 0 && lane == 0) {
+#pragma unroll
+                    for (int h = 0; h < PARTS; ++h)
+                        tma_store_3d(&map_out, smem_u32(stage_out) + h * 4 * 32 * PITCH, h * 64, I.head0, I.row0 + I.q_off);
+                    tma_store_commit();
+                }
+            } else if (ok) {
                 __syncwarp();
 #pragma unroll
                 for (int k = 0; k < CH; ++k) {
@@ -513,6 +552,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             g += n_blocks;
         }
     }
+    if (threadIdx.x == 0) tma_store_wait_all();                 // thread 0 (softmax warp 0, lane 0) issued the result stores
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
         const unsigned long long t0 = global_ns();
@@ -601,9 +641,9 @@ int cached_page_map(const void* cache, int num_pages, int n_kv, int page_size, i
 }
 
 template <int HD>
-int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int n_work, cudaStream_t s) {
-    constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 18 + 256 + 3 * PARTS * ROWS * 4 +
-                         LOCAL_ITEMS * (int)sizeof(TcItem) + ROWS * HD * 2;
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const CUtensorMap& mo, const TcParams& p, int n_work, cudaStream_t s) {
+    constexpr int smem = (1 + 2 * KV_STAGES) * (HD / 64) * 128 * 128 + 1024 + 8 * 20 + 256 + 3 * PARTS * ROWS * 4 +
+                         LOCAL_ITEMS * (int)sizeof(TcItem) + 1024 + ROWS * HD * 2;
     auto kern = prefill_attention_tc_kernel<HD>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -613,7 +653,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
     }
     const long total = (long)n_work * p.n_kv * (p.group / p.pack);
     const int grid = (int)(total < rs_tma::sm_count() ? total : rs_tma::sm_count());      // one CTA per SM; each walks its items
-    return rs_launch_pdl(kern, dim3(grid), dim3(THREADS), (size_t)smem, s, mq, mkv, p);
+    return rs_launch_pdl(kern, dim3(grid), dim3(THREADS), (size_t)smem, s, mq, mkv, mo, p);
 }
 }  // namespace
 
@@ -645,9 +685,12 @@ RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows,
     p.pack_shift = 0;
     while ((1 << p.pack_shift) < p.pack) ++p.pack_shift;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    CUtensorMap mq, mkv;
+    CUtensorMap mq, mkv, mo;
     int rc = cached_q_map(q, q_stride, q_rows, n_q, hd, p.pack, &mq);
     if (rc) return rc;
+    // the result as (head dim, head, token), the queries' layout; its rows are the queries' rows
+    p.out_by_tma = hd == 128 && cached_q_map(out, out_stride, q_rows, n_q, hd, p.pack, &mo) == 0;
+    if (!p.out_by_tma) mo = mq;
     p.one_load_per_page = cached_page_map(cache, num_pages, n_kv, page_size, hd, &mkv) == 0;
     if (!p.one_load_per_page) {
         rc = rs_tma::get_map(cache, (long)num_pages * 2 * n_kv * page_size, hd, hd, 8, &mkv);
@@ -655,6 +698,6 @@ RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows,
     }
     g_last_loads_per_page = p.one_load_per_page ? 2 : 2 * (hd / 64) * (page_size / 8);
     cudaStream_t s = (cudaStream_t)stream;
-    if (hd == 64) return launch<64>(mq, mkv, p, n_work, s);
-    return launch<128>(mq, mkv, p, n_work, s);
+    if (hd == 64) return launch<64>(mq, mkv, mo, p, n_work, s);
+    return launch<128>(mq, mkv, mo, p, n_work, s);
 }

@@ -797,7 +797,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     if kind == "tc":
         fn = bf16lib().rs_attention_prefill_tc
         _check(fn(
-            _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0],
+            _ptr(q), q.stride(0), min(q.shape[0], out.shape[0]), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0],
             page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv,
             head_dim, int(window), float(scale), _ptr(status), _stream()), "attention_prefill_" + kind)
         return

@@ -486,6 +486,24 @@ def test_prefill_tcgen05_kernel(n_q, n_kv, hd, page, window):
     close(fast, want, 1.5e-2)
 
 
+@pytest.mark.parametrize("prefill", ["tc", "mma", "simt"])
+def test_prefill_when_every_block_of_keys_raises_the_maximum(prefill):
+    """Scores that grow with the key's position (by more than 2^8 per 128 keys): the running maximum moves at every
+    block, so the accumulated result is rescaled every time, in the kernels that keep it in tensor memory too."""
+    hd = 128
+    scale = 1.0 / math.sqrt(hd)
+
+    def boost(s, t):
+        if s is None:
+            t[:, :, 0] = 1.0 / scale                      # queries: the first dim picks the keys' ramp up
+        else:
+            t[:, :, 0] = 0.1 * torch.arange(t.shape[0], dtype=torch.float32).to(t.dtype)[:, None]
+    torch.manual_seed(11)
+    seqs = [(700, 257), (1500, 300), (129, 129)]
+    fast, want = run_attention(torch.bfloat16, 8, 2, hd, 16, seqs, boost=boost, prefill=prefill)
+    close(fast, want, 1.5e-2)
+
+
 def test_attention_refuses_unsupported_sizes():
     from rustingstrata_b200.kernels.ops import KernelError
     with pytest.raises(KernelError, match="head size"):
