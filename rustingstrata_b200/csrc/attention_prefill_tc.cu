@@ -16,11 +16,14 @@
 //                  MN-major) in shared memory, accumulated in tensor memory over all blocks.  The reference maximum
 //                  of a row only moves when a block exceeds it by more than 2^8; only then are the row's sum and
 //                  its O (loaded, scaled, stored back) corrected, which after the first blocks is rare.
-// Warp 8 issues the MMAs (one elected lane) and owns the tensor-memory allocation, warp 9 issues the TMA loads
-// (lane i looks page i of a block up and loads it, so the lookups of a block run side by side).
-// S is double buffered, so Q K^T of the next block runs under the softmax of this one.  Every mbarrier wait is
-// bounded (tma_helpers.cuh).  Cache pages a block does not own (beyond the sequence, given back by a window)
-// are replaced by page 0: their keys are masked, and their values only have to be finite.
+// Warp 8 issues the MMAs (one elected lane) and owns the tensor-memory allocation; warp 9 streams the keys and warp
+// 10 the values (lane i looks page i of a block up, three blocks ahead, and loads it).  The scores have three buffers
+// in tensor memory, so Q K^T runs two blocks ahead of P V and the softmax warps never wait for scores.  The CTAs are
+// persistent: one per SM, each walks several tiles (longest first, dealt in a snake), loads the next tile's queries
+// and first keys under this tile's last blocks, and stores a result through a staging tile in shared memory (whole
+// tiles by TMA store).  Every mbarrier wait is bounded (tma_helpers.cuh).  Cache pages a block does not own (beyond
+// the sequence, given back by a window) are replaced by page 0: their keys are masked, and their values only have to
+// be finite.
 //
 // Reference counterpart: attn_prefill_* (src/cuda/kernels.cu:2813-3156), an mma.sync kernel with f16 inputs.
 #include "tma_helpers.cuh"
