@@ -97,6 +97,8 @@ def main() -> int:
     ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long"])
     ap.add_argument("--marginal", action="store_true", help="marginal cost of each kernel family inside the decode step")
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="with --marginal: tokens each request holds")
+    ap.add_argument("--marginal-prefill", action="store_true",
+                    help="marginal cost of each kernel family inside the step that runs one whole prompt of --prompt-len tokens")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (no setup.py/pyproject.toml; "
@@ -107,6 +109,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.marginal_prefill:
+        return marginal_costs_prefill(args)
     if args.marginal:
         return marginal_costs(args)
     if args.workload == "14b-mixed":
@@ -279,6 +283,70 @@ def marginal_costs(args) -> int:
         finally:
             setattr(ops, fn_name, real)
         again = timed()                                  # the whole step once more: clocks drift under a long load
+        per_step = ((whole + again) / 2 - t) * 1000
+        whole = again
+        key = "marginal_us_per_step" if label == "output head" else "marginal_us_per_layer"
+        out[key][label] = per_step if label == "output head" else per_step / L
+    out["ms_per_step_at_the_end"] = whole
+    print(json.dumps(out))
+    return 0
+
+
+def marginal_costs_prefill(args) -> int:
+    """Times the step that runs one whole prompt, then the same step with one kernel family's launches left out."""
+    import numpy as np
+    import torch
+    from rustingstrata_b200 import Engine
+    from rustingstrata_b200.kernels import ops
+    from rustingstrata_b200.sampling import SamplingParams
+    cfg = dict(QWEN3_8B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    L, S = cfg["num_hidden_layers"], args.prompt_len
+    eng = Engine(cfg, dtype="bfloat16", random_seed=0, page_size=16, max_tokens=2 * S + 64, max_batch_tokens=S, max_seqs=2)
+    eng.lookahead = False
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["vocab_size"], size=S).tolist()
+
+    def once():
+        rid = eng.add_request(prompt, 1, SamplingParams())
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        eng.step()
+        ev1.record()
+        torch.cuda.synchronize()
+        eng.drain()
+        for r in list(eng.scheduler.running):
+            eng.scheduler.running.remove(r)
+            eng.runner.release(r.rid)
+            eng._samplers.pop(r.rid, None)
+        return ev0.elapsed_time(ev1)
+
+    def timed():
+        return float(np.median([once() for _ in range(max(5, args.steps // 8))]))
+    for _ in range(3):
+        timed()
+    whole = timed()
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    out = {"prompt_len": S, "layers": L, "ms_per_step": whole, "us_per_layer": whole / L * 1000, "marginal_us_per_layer": {},
+           "marginal_us_per_step": {}}
+    families = [("attention of the portion", "attention_prefill", None), ("qk_norm_rope_kv", "qk_norm_rope_kv", None),
+                ("gate/up product", "linear_swiglu", None), ("row norms (+ owed sums)", "rmsnorm", None),
+                ("qkv product", "linear", (qkv, H)), ("output product", "linear", (H, cfg["num_attention_heads"] * cfg["head_dim"])),
+                ("down product", "linear", (H, I)), ("output head", "linear", (cfg["vocab_size"], H))]
+    for label, fn_name, shape in families:
+        real = getattr(ops, fn_name)
+        if shape is None:
+            setattr(ops, fn_name, lambda *a, **k: None)
+        else:
+            setattr(ops, fn_name, lambda a, w, *r, _real=real, _shape=shape, **k: None if tuple(w.shape) == _shape else _real(a, w, *r, **k))
+        try:
+            t = timed()
+        finally:
+            setattr(ops, fn_name, real)
+        again = timed()
         per_step = ((whole + again) / 2 - t) * 1000
         whole = again
         key = "marginal_us_per_step" if label == "output head" else "marginal_us_per_layer"

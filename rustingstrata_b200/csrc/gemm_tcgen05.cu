@@ -34,7 +34,8 @@ template <int BN> struct Cfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int OUT_STAGE_BYTES = 4 * 2 * 4096;    // results on their way out: per epilogue warp two buffers of 32 rows x 128 bytes
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -73,6 +74,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// shared memory -> global through the TMA unit: a plain tiled store, or an addition to what is there (done in L2)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_out_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_out_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void tma_out_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups of
 // 8 rows 1024 bytes apart (stride byte offset), leading byte offset 1 (unused for swizzled K-major),
@@ -97,6 +110,7 @@ struct GemmParams {
     int M, N, K;
     int vec_ok;            // C rows allow 16-byte vector access
     int bn;                // columns per tile: the template's BN, or less (a multiple of 16) in buffers sized for BN
+    int out_by_tma;        // float32 results leave through shared memory and the TMA unit (map_c is valid)
     int* status;
 };
 
@@ -169,15 +183,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                       // swizzled tiles need 1024-byte alignment
     uint8_t* aligned = smem_raw + (base - raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + C::STAGES * C::STAGE_BYTES);
+    uint8_t* out_stage = aligned + C::STAGES * C::STAGE_BYTES;          // 1 KiB aligned: the stages are multiples of 1 KiB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + C::OUT_STAGE_BYTES);
     // barrier layout: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
-    const uint32_t bar0 = base + C::STAGES * C::STAGE_BYTES;
+    const uint32_t bar0 = base + C::STAGES * C::STAGE_BYTES + C::OUT_STAGE_BYTES;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
     auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * C::STAGES + b); };
@@ -268,6 +284,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;                            // TMEM lanes [32 * quarter, +32) belong to this warp
         int local = 0;
         bool ok = true;
+        // Float32 results (the residual stream) leave through shared memory: a warp writes its 32 rows x 32 columns as a
+        // tile of 128-byte rows, 16-byte chunks swizzled by the row, and one lane hands the tile to the TMA unit, which
+        // stores it or, for +=, adds it to what is there (each element belongs to one tile only, so it is the same single
+        // addition).  Stored from the registers, every lane of an instruction touched a line of its own, and the old
+        // values had to be fetched the same way first: 16 k line accesses per tile in the queue that the MMA and TMA
+        // issue share.
+        const bool tma_out = (EPI == EPI_ADD_F32 || EPI == EPI_STORE_F32) && p.out_by_tma;
+        uint8_t* my_stage = out_stage + (warp - 2) * 2 * 4096;
+        uint32_t n_out = 0;
         pdl_wait();
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
             const int buf = local & 1;
@@ -281,12 +306,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c, r);
                 tmem_ld_wait();
-                if (n0 + c < nmax) epilogue_chunk<EPI>(p, r, row, n0 + c, nmax);
+                if (n0 + c >= nmax) continue;
+                if (tma_out) {
+                    if (m0 + quarter * 32 >= p.M) continue;          // none of this warp's rows exists: nothing to send
+                    uint8_t* dst = my_stage + (n_out & 1u) * 4096;
+                    if (lane == 0) tma_out_wait_read_1();          // the tile sent from this buffer two chunks ago has been read
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(dst + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (EPI == EPI_ADD_F32) tma_add_2d(&map_c, smem_u32(dst), n0 + c, m0 + quarter * 32);
+                        else tma_store_2d(&map_c, smem_u32(dst), n0 + c, m0 + quarter * 32);
+                        tma_out_commit();
+                    }
+                    ++n_out;
+                } else {
+                    epilogue_chunk<EPI>(p, r, row, n0 + c, nmax);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(buf));
         }
+        if (tma_out && lane == 0) tma_out_wait_all();            // the results are in place before the kernel ends
     }
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
@@ -305,8 +350,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 using rs_tma::get_map;
 using rs_tma::sm_count;
 
+// Tensor map of the float32 result [M, N] with row pitch ldc: boxes of 32 columns x 32 rows, 128-byte swizzle.  Rows
+// from M on and columns from N on are outside the tensor, so the TMA unit drops them.
+struct CMapKey { const void* c; long ldc; int M, N; };
+std::vector<std::pair<CMapKey, CUtensorMap>> g_cmaps;
+std::mutex g_cmaps_mutex;
+int c_map_f32(const void* Cptr, long ldc, int M, int N, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_cmaps_mutex);
+    for (auto& e : g_cmaps)
+        if (e.first.c == Cptr && e.first.ldc == ldc && e.first.M == M && e.first.N == N) { *out = e.second; return 0; }
+    rs_tma::EncodeTiledFn enc = rs_tma::get_encoder();
+    if (!enc) return 1;
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(Cptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1;
+    if (g_cmaps.size() > 256) g_cmaps.clear();
+    g_cmaps.push_back({CMapKey{Cptr, ldc, M, N}, m});
+    *out = m;
+    return 0;
+}
+
 template <int BN, int EPI>
-int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, int max_ctas, cudaStream_t s) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mc, const GemmParams& p, int max_ctas, cudaStream_t s) {
     auto kern = gemm_tc_kernel<BN, EPI>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -317,16 +388,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, in
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + p.bn - 1) / p.bn);
     int grid = tiles < sm_count() ? tiles : sm_count();
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    return rs_launch_pdl(kern, dim3(grid), dim3(THREADS), (size_t)Cfg<BN>::SMEM_BYTES, s, ma, mw, p);
+    return rs_launch_pdl(kern, dim3(grid), dim3(THREADS), (size_t)Cfg<BN>::SMEM_BYTES, s, ma, mw, mc, p);
 }
 
 template <int BN>
-int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, int max_ctas, cudaStream_t s) {
+int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mc, const GemmParams& p, int max_ctas, cudaStream_t s) {
     switch (epi) {
-        case EPI_STORE_BF16: return launch<BN, EPI_STORE_BF16>(ma, mw, p, max_ctas, s);
-        case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(ma, mw, p, max_ctas, s);
-        case EPI_ADD_F32: return launch<BN, EPI_ADD_F32>(ma, mw, p, max_ctas, s);
-        case EPI_SWIGLU_BF16: return launch<BN, EPI_SWIGLU_BF16>(ma, mw, p, max_ctas, s);
+        case EPI_STORE_BF16: return launch<BN, EPI_STORE_BF16>(ma, mw, mc, p, max_ctas, s);
+        case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(ma, mw, mc, p, max_ctas, s);
+        case EPI_ADD_F32: return launch<BN, EPI_ADD_F32>(ma, mw, mc, p, max_ctas, s);
+        case EPI_SWIGLU_BF16: return launch<BN, EPI_SWIGLU_BF16>(ma, mw, mc, p, max_ctas, s);
     }
     return (int)cudaErrorInvalidValue;
 }
@@ -372,9 +443,12 @@ RS_EXPORT int rs_gemm_bf16_tc(const void* A, long lda, long a_rows, const void* 
     p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status; p.bn = bn;
     const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
+    // float32 results in whole chunks of 32 columns per tile go out through the TMA unit
+    CUtensorMap mc = ma;
+    p.out_by_tma = (epi == EPI_ADD_F32 || epi == EPI_STORE_F32) && p.vec_ok && bn % 32 == 0 && c_map_f32(C, ldc, M, N, &mc) == 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (tpl == 256) return launch_epi<256>(epi, ma, mw, p, max_ctas, s);
-    if (tpl == 128 && bn == 128) return launch_epi<128>(epi, ma, mw, p, max_ctas, s);
-    if (tpl == 64 && bn == 64) return launch_epi<64>(epi, ma, mw, p, max_ctas, s);
+    if (tpl == 256) return launch_epi<256>(epi, ma, mw, mc, p, max_ctas, s);
+    if (tpl == 128 && bn == 128) return launch_epi<128>(epi, ma, mw, mc, p, max_ctas, s);
+    if (tpl == 64 && bn == 64) return launch_epi<64>(epi, ma, mw, mc, p, max_ctas, s);
     return (int)cudaErrorInvalidValue;
 }
