@@ -224,10 +224,11 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
     const int heads_per_warp = 32 / lanes_per_head;
     const int lane = threadIdx.x & 31;
-    const long unit = (((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * heads_per_warp + lane / lanes_per_head;
+    // 32-bit arithmetic: the launcher takes this kernel only while tokens x heads stays below 2^31
+    const unsigned unit = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (unsigned)heads_per_warp + (unsigned)(lane / lanes_per_head);
     const int sub = lane % lanes_per_head;
-    const bool live = unit < (long)n_tokens * heads_per_token;
-    const int t = live ? (int)(unit / heads_per_token) : 0, h = live ? (int)(unit % heads_per_token) : 0;
+    const bool live = unit < (unsigned)n_tokens * (unsigned)heads_per_token;
+    const int t = live ? (int)(unit / (unsigned)heads_per_token) : 0, h = live ? (int)(unit - (unsigned)t * (unsigned)heads_per_token) : 0;
     const int pos = positions[(size_t)t * pos_stride];                  // stream 0: where the token lies in the cache
     const int rpos = positions[(size_t)t * pos_stride + rot_stream];    // the stream this layer's rotation follows
     __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
@@ -327,7 +328,7 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
     const long blocks = (warps * 32 + threads - 1) / threads;
     const bool weights_ok = (q_w == nullptr && k_w == nullptr) || (w_dt == RS_BF16 && (q_w == nullptr) == (k_w == nullptr || !write_kv) &&
                                                                   ((long)q_w & 7) == 0 && ((long)k_w & 7) == 0);
-    if (dt == RS_BF16 && cos_sin != nullptr && n_rot == hd && hd % 8 == 0 && hd <= 256 && row_stride % 4 == 0 && page_stride % 4 == 0 &&
+    if (dt == RS_BF16 && warps < (1L << 26) && cos_sin != nullptr && n_rot == hd && hd % 8 == 0 && hd <= 256 && row_stride % 4 == 0 && page_stride % 4 == 0 &&
         ((long)qkv & 7) == 0 && ((long)cache & 7) == 0 && ((long)cos_sin & 15) == 0 && weights_ok && (q_w != nullptr || k_w == nullptr)) {
         // 16-byte accesses when half a head is a multiple of 8 elements and everything is 16-byte aligned
         const bool wide = hd % 16 == 0 && row_stride % 8 == 0 && page_stride % 8 == 0 && ((long)qkv & 15) == 0 && ((long)cache & 15) == 0 &&

@@ -290,7 +290,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // addition).  Stored from the registers, every lane of an instruction touched a line of its own, and the old
         // values had to be fetched the same way first: 16 k line accesses per tile in the queue that the MMA and TMA
         // issue share.
-        const bool tma_out = (EPI == EPI_ADD_F32 || EPI == EPI_STORE_F32) && p.out_by_tma;
+        // bfloat16 results go the same way, two chunks (bf16 store) or four (SiLU(gate) * up: 16 results per chunk) to
+        // a row of 128 bytes.
+        const bool tma_out = p.out_by_tma;
+        constexpr int CHUNKS_PER_ROW = (EPI == EPI_STORE_BF16) ? 2 : (EPI == EPI_SWIGLU_BF16 ? 4 : 1);
         uint8_t* my_stage = out_stage + (warp - 2) * 2 * 4096;
         uint32_t n_out = 0;
         pdl_wait();
@@ -306,24 +309,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c, r);
                 tmem_ld_wait();
-                if (n0 + c >= nmax) continue;
                 if (tma_out) {
                     if (m0 + quarter * 32 >= p.M) continue;          // none of this warp's rows exists: nothing to send
+                    // (columns from N on are sent too: they lie outside the tensor, and the TMA unit drops them)
+                    const int part = (c >> 5) % CHUNKS_PER_ROW;      // which piece of the 128-byte row this chunk fills
                     uint8_t* dst = my_stage + (n_out & 1u) * 4096;
-                    if (lane == 0) tma_out_wait_read_1();          // the tile sent from this buffer two chunks ago has been read
-                    __syncwarp();
+                    if (part == 0) {
+                        if (lane == 0) tma_out_wait_read_1();        // the tile sent from this buffer two rows ago has been read
+                        __syncwarp();
+                    }
+                    if (EPI == EPI_ADD_F32 || EPI == EPI_STORE_F32) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        *reinterpret_cast<uint4*>(dst + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<uint4*>(dst + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    } else if (EPI == EPI_STORE_BF16) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * j]), __uint_as_float(r[8 * q + 2 * j + 1]));
+                                w[j] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            *reinterpret_cast<uint4*>(dst + lane * 128 + (((part * 4 + q) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float g0 = __uint_as_float(r[16 * q + 4 * j]), u0 = __uint_as_float(r[16 * q + 4 * j + 1]);
+                                const float g1 = __uint_as_float(r[16 * q + 4 * j + 2]), u1 = __uint_as_float(r[16 * q + 4 * j + 3]);
+                                __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                                w[j] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            *reinterpret_cast<uint4*>(dst + lane * 128 + (((part * 2 + q) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                    if (part != CHUNKS_PER_ROW - 1) continue;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        if (EPI == EPI_ADD_F32) tma_add_2d(&map_c, smem_u32(dst), n0 + c, m0 + quarter * 32);
-                        else tma_store_2d(&map_c, smem_u32(dst), n0 + c, m0 + quarter * 32);
+                        // first result column of the row: accumulator column / 2 for SiLU(gate) * up
+                        const int c_first = n0 + c - 32 * (CHUNKS_PER_ROW - 1);
+                        const int x = EPI == EPI_SWIGLU_BF16 ? c_first >> 1 : c_first;
+                        if (x < (EPI == EPI_SWIGLU_BF16 ? p.N >> 1 : p.N)) {          // else the whole row lies past the last column
+                            if (EPI == EPI_ADD_F32) tma_add_2d(&map_c, smem_u32(dst), x, m0 + quarter * 32);
+                            else tma_store_2d(&map_c, smem_u32(dst), x, m0 + quarter * 32);
+                        }
                         tma_out_commit();
                     }
                     ++n_out;
-                } else {
+                } else if (n0 + c < nmax) {
                     epilogue_chunk<EPI>(p, r, row, n0 + c, nmax);
                 }
             }
@@ -350,28 +388,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 using rs_tma::get_map;
 using rs_tma::sm_count;
 
-// Tensor map of the float32 result [M, N] with row pitch ldc: boxes of 32 columns x 32 rows, 128-byte swizzle.  Rows
-// from M on and columns from N on are outside the tensor, so the TMA unit drops them.
-struct CMapKey { const void* c; long ldc; int M, N; };
+// Tensor map of the result [M, N] (float32 or bfloat16) with row pitch ldc: boxes of 128 bytes x 32 rows, 128-byte
+// swizzle.  Rows from M on and columns from N on are outside the tensor, so the TMA unit drops them.
+struct CMapKey { const void* c; long ldc; int M, N, elem; };
 std::vector<std::pair<CMapKey, CUtensorMap>> g_cmaps;
 std::mutex g_cmaps_mutex;
-int c_map_f32(const void* Cptr, long ldc, int M, int N, CUtensorMap* out) {
+int c_map(const void* Cptr, long ldc, int M, int N, int elem, CUtensorMap* out) {
     std::lock_guard<std::mutex> lock(g_cmaps_mutex);
     for (auto& e : g_cmaps)
-        if (e.first.c == Cptr && e.first.ldc == ldc && e.first.M == M && e.first.N == N) { *out = e.second; return 0; }
+        if (e.first.c == Cptr && e.first.ldc == ldc && e.first.M == M && e.first.N == N && e.first.elem == elem) { *out = e.second; return 0; }
     rs_tma::EncodeTiledFn enc = rs_tma::get_encoder();
     if (!enc) return 1;
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
-    cuuint32_t box[2] = {32, 32};
+    cuuint64_t strides[1] = {(cuuint64_t)ldc * elem};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / elem), 32};
     cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
-    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(Cptr), dims, strides, box, estr,
+    CUresult r = enc(&m, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(Cptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return 1;
     if (g_cmaps.size() > 256) g_cmaps.clear();
-    g_cmaps.push_back({CMapKey{Cptr, ldc, M, N}, m});
+    g_cmaps.push_back({CMapKey{Cptr, ldc, M, N, elem}, m});
     *out = m;
     return 0;
 }
@@ -443,9 +481,11 @@ RS_EXPORT int rs_gemm_bf16_tc(const void* A, long lda, long a_rows, const void* 
     p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status; p.bn = bn;
     const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
-    // float32 results in whole chunks of 32 columns per tile go out through the TMA unit
+    // results go out through the TMA unit when a tile's columns fill whole 128-byte rows of the staging tiles
     CUtensorMap mc = ma;
-    p.out_by_tma = (epi == EPI_ADD_F32 || epi == EPI_STORE_F32) && p.vec_ok && bn % 32 == 0 && c_map_f32(C, ldc, M, N, &mc) == 0;
+    const int acc_cols_per_row = out_elem == 4 ? 32 : (epi == EPI_SWIGLU_BF16 ? 128 : 64);
+    p.out_by_tma = p.vec_ok && bn % acc_cols_per_row == 0 &&
+                   c_map(C, ldc, M, epi == EPI_SWIGLU_BF16 ? N / 2 : N, out_elem, &mc) == 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (tpl == 256) return launch_epi<256>(epi, ma, mw, mc, p, max_ctas, s);
     if (tpl == 128 && bn == 128) return launch_epi<128>(epi, ma, mw, mc, p, max_ctas, s);
