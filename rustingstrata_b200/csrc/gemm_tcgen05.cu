@@ -460,15 +460,21 @@ RS_EXPORT int rs_gemm_bf16_tc(const void* A, long lda, long a_rows, const void* 
     if (!rs_gemm_tc_supported((long)A, lda, (long)W, ldw, N, K, epi) || a_rows < M) return (int)cudaErrorInvalidValue;
     int tpl = bn;                                        // template instantiation (buffer sizes): 64, 128 or 256
     if (bn == 0) {
-        // widest tile that still gives every SM work: 256 columns need the fewest loads of A per flop
+        // The tile width that needs the least time by a model fitted to measurements at 256 to 2,048 rows: the time is
+        // the number of waves of tiles over the SMs times what a wave of that width costs (256 columns: 1, 192: 0.94,
+        // 128: 0.745, 64: 0.68 - narrower tiles load the rows of A more often per flop).  Many waves always end at 256.
+        // (240 or 176 columns for 4,096 or 6,144 were measured at 2,048 rows: slower than 256 by 2 to 17 %.)
         const long tm = (M + BM - 1) / BM;
         const int sms = sm_count();
-        // (Narrower tiles that would fill the last wave better, 240 or 176 columns for 4096 or 6144, were measured: each
-        // was slower than 256 by 2 to 17 %, the narrower tile costs more than the fuller wave gives.)
-        if (tm * ((N + 255) / 256) * 4 >= 3L * sms) {
-            bn = tpl = 256;
-        } else if (tm * ((N + 127) / 128) * 4 >= 3L * sms) bn = tpl = 128;
-        else bn = tpl = 64;
+        const int widths[4] = {256, 192, 128, 64};
+        const double wave_cost[4] = {1.0, 0.94, 0.745, 0.68};
+        double best = 0;
+        for (int i = 0; i < 4; ++i) {
+            const long tiles = tm * ((N + widths[i] - 1) / widths[i]);
+            const double cost = (double)((tiles + sms - 1) / sms) * wave_cost[i];
+            if (i == 0 || cost < best - 1e-9) { best = cost; bn = widths[i]; }
+        }
+        tpl = bn == 192 ? 256 : bn;
     } else if (bn > 128 && bn <= 256 && bn % 16 == 0) {
         tpl = 256;
     }
