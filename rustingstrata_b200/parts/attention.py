@@ -78,8 +78,8 @@ class PagedAttention(Mixer):
         rt.scratch("attn_partial", 1, self.partial_slots * self.n_heads * (self.hd + 2), torch.float32)
         # The step's list of (sequence, kv head, split) items of the tensor-core decode kernel.  The first layer of a
         # step that needs it writes it and the later ones read it, so it has a name that only layers with the same
-        # plan (window, tiling) and kv-head count share: nobody else may write it in between.
-        self.items_name = f"attn_items{self.plan_key()[1:]}x{self.n_kv}"
+        # plan (the plan's key follows from window and head shape) share: nobody else may write it in between.
+        self.items_name = f"attn_items_w{self.window}_h{self.n_heads}x{self.n_kv}x{self.hd}"
         rt.scratch(self.items_name, 1, self.partial_slots * self.n_kv, torch.int32)
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
 

@@ -45,6 +45,25 @@ def test_norm_scales_and_integer_tables():
     assert bits.dtype == np.int32 and set(np.unique(bits)) == {0, 1} and abs(bits.mean() - 0.5) < 0.05
 
 
+def test_writing_a_model_folder_needs_no_kernel_library(tmp_path, monkeypatch):
+    """``init-random`` is a host-side command: naming the tensors of a configuration and drawing them must not build
+    or load a CUDA library (a part that asked a kernel about its tiling while it was being put together once did)."""
+    from rustingstrata_b200.kernels import build
+    from rustingstrata_b200.models import manifest_for
+
+    def refuse(name, verbose=True):
+        raise AssertionError(f"kernel library '{name}' asked for on a host-only path")
+    monkeypatch.setattr(build, "compile_library", refuse)
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 96, "hidden_size": 64,
+           "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+           "intermediate_size": 80, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 128,
+           "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
+    m = manifest_for(cfg)
+    assert len(m) == 3 + 2 * 11
+    R.write_random_model(str(tmp_path / "m"), cfg, m, seed=1)
+    assert (tmp_path / "m" / "model.safetensors").exists()
+
+
 @pytest.mark.gpu
 def test_host_and_device_draw_the_same_bits():
     import torch
