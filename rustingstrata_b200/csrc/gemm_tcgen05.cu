@@ -128,7 +128,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
             for (int j = 0; j < 8; ++j) {
                 const float g0 = __uint_as_float(r[4 * j]), u0 = __uint_as_float(r[4 * j + 1]);
                 const float g1 = __uint_as_float(r[4 * j + 2]), u1 = __uint_as_float(r[4 * j + 3]);
-                __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul_fast(g0, u0), silu_mul_fast(g1, u1));
                 packed[j] = *reinterpret_cast<uint32_t*>(&v);
             }
             reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -138,7 +138,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
             for (int j = 0; j < 16; ++j) {
                 if (oc0 + j < half_n) {
                     const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-                    out[j] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+                    out[j] = __float2bfloat16_rn(silu_mul_fast(g, u));
                 }
             }
         }
@@ -341,7 +341,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (int j = 0; j < 4; ++j) {
                                 const float g0 = __uint_as_float(r[16 * q + 4 * j]), u0 = __uint_as_float(r[16 * q + 4 * j + 1]);
                                 const float g1 = __uint_as_float(r[16 * q + 4 * j + 2]), u1 = __uint_as_float(r[16 * q + 4 * j + 3]);
-                                __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                                __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul_fast(g0, u0), silu_mul_fast(g1, u1));
                                 w[j] = *reinterpret_cast<uint32_t*>(&v);
                             }
                             *reinterpret_cast<uint4*>(dst + lane * 128 + (((part * 2 + q) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);

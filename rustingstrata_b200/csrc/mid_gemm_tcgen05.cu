@@ -97,7 +97,7 @@ __device__ __forceinline__ void store_value(const MidParams& p, float v, int m, 
         // rows of W alternate gate, up: the even lane of a pair writes
         const float up = __shfl_xor_sync(0xffffffffu, v, 1);
         if ((n & 1) == 0 && n + 1 < p.N)
-            ((__nv_bfloat16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(v / (1.0f + __expf(-v)) * up);
+            ((__nv_bfloat16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul_fast(v, up));
     } else if (n < p.N) {
         const size_t o = (size_t)m * p.ldc + n;
         if (EPI == EPI_STORE_BF16) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(v);
@@ -112,7 +112,7 @@ template <int EPI>
 __device__ __forceinline__ void store_four(const MidParams& p, float4 v, float4 old, int m, int n0) {
     if (EPI == EPI_SWIGLU_BF16) {
         __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)m * p.ldc + (n0 >> 1);
-        const float a = v.x / (1.0f + __expf(-v.x)) * v.y, b = v.z / (1.0f + __expf(-v.z)) * v.w;
+        const float a = silu_mul_fast(v.x, v.y), b = silu_mul_fast(v.z, v.w);
         if (p.vec_ok && n0 + 3 < p.N) {
             *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(a, b);
         } else {

@@ -54,7 +54,7 @@ __device__ __forceinline__ void store_tile(const SkinnyParams& p, const float (&
                     const int m = m0 + (i & 1), n = (i >> 1) ? nb : na;
                     if (m < p.M && n + 1 < p.N) {
                         const float gate = acc[j][i], up = partner[i];
-                        out[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+                        out[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul_fast(gate, up));
                     }
                 }
             }
