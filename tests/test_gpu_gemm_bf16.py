@@ -72,6 +72,27 @@ def test_tcgen05_gemm_swiglu_and_several_tiles_per_cta(M, N, K, max_ctas):
     assert err(f, a.double() @ w.double().T) < 1e-5 and st.item() == 0
 
 
+@pytest.mark.parametrize("M,N,K,bn,max_ctas", [(300, 1280, 512, 256, 9), (640, 1024, 1024, 128, 12), (200, 2000, 200, 64, 20),
+                                               (2048, 4096, 1024, 0, 0), (1000, 2304, 448, 256, 11), (257, 1536, 4096, 256, 5)])
+def test_tcgen05_gemm_float32_accumulate_several_tiles_per_cta_same_bits_every_run(M, N, K, bn, max_ctas):
+    """A float32 += over tile counts that do not fill the last wave of CTAs, against the float64 product, and the same
+    bits run after run (the additions to C go through the TMA unit; each element belongs to one tile)."""
+    o = ops()
+    a, w = make(M, N, K, cap=M + 3, seed=4)
+    want = a[:M].double() @ w.double().T
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    base = torch.randn(M + 3, N, device=DEV)
+    first = None
+    for _ in range(6):
+        acc = base.clone()
+        o.gemm_bf16_tc(a, w, acc, M, accumulate=True, status=st, bn=bn, max_ctas=max_ctas)
+        assert err(acc[:M], base[:M].double() + want) < 1e-5 and torch.equal(acc[M:], base[M:])
+        if first is None:
+            first = acc
+        assert torch.equal(acc, first)
+    assert st.item() == 0
+
+
 @pytest.mark.parametrize("bn", [144, 208, 224, 240])
 def test_tcgen05_gemm_tile_widths_between_128_and_256_with_the_fused_epilogue(bn):
     """Tiles whose width is not a multiple of the 32-column epilogue step: the last step of a tile must not write
