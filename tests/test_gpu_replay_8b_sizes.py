@@ -210,3 +210,32 @@ def test_the_mixed_cutting_at_8b_sizes_used_pages_again():
     assert 2 * st["pool"] <= 2 * sum(round64(n) for n in LENGTHS.values())
     for pool in got.pools:
         assert pool["reuses"] > 0 and pool["allocations"] > pool["pages"] and pool["held_at_end"] == 0, pool
+
+
+def test_a_whole_prompt_gives_the_same_bits_whatever_ran_before():
+    """At the layer sizes of Qwen3-8B (2 layers, a smaller vocabulary): a prompt run whole, again and again, between
+    other prompts that leave other keys and values in the pages it is given.  The logits of its first run equal those
+    of the later ones to the bit.  A kernel that reads what the step itself has not finished writing (a wait that
+    lets it through too early) shows here: the first run then sees the other prompt's leftovers, the later ones see
+    a copy of what they are about to write."""
+    import torch
+    from rustingstrata_b200 import Engine
+    from rustingstrata_b200.engine import StepEntry
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 4096, "hidden_size": 4096,
+           "num_hidden_layers": 2, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+           "intermediate_size": 12288, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 40960,
+           "tie_word_embeddings": False, "use_sliding_window": False, "torch_dtype": "bfloat16"}
+    eng = Engine(cfg, dtype="bfloat16", random_seed=7, max_tokens=4096, max_batch_tokens=2304)
+    rng = np.random.default_rng(1)
+    for n in (1045, 300, 150, 300, 2070, 300):
+        toks = rng.integers(0, cfg["vocab_size"], n).tolist()
+        places = sorted({0, 1, 127, 128, 129, n // 2, n - 2, n - 1})
+        first = None
+        for _ in range(3):
+            rows = eng.step_raw([StepEntry("x", toks, places)]).float().cpu()
+            eng.release("x")
+            if first is None:
+                first = rows
+            assert torch.equal(rows, first), f"{n} tokens: a later run differs from the first"
+        assert torch.isfinite(first).all()
+    eng.runner.check_status()
