@@ -396,21 +396,24 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
                 auto lds = [&](uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; };
                 const bool in_workspace = slot < (size_t)p.partial_slots;
                 if (!in_workspace && gw == 0 && lane == 0) atomicOr(p.status, RS_STATUS_BAD_PLAN);
-                for (int i = gw * 32 + lane; in_workspace && i < p.group * (HD + 2); i += GROUP_WARPS * 32) {
-                    const int r = i / (HD + 2), d = i % (HD + 2);
-                    float mw[GROUP_WARPS], M = -INFINITY;
+                // a warp takes the heads gw, gw + 4, ...: the four warps' maxima and weights of a head once, then a
+                // lane per column of the partial (head dims, then maximum and sum)
+                for (int r = gw; in_workspace && r < p.group; r += GROUP_WARPS) {
+                    float mw[GROUP_WARPS], e[GROUP_WARPS], M = -INFINITY;
 #pragma unroll
                     for (int ww = 0; ww < GROUP_WARPS; ++ww) { mw[ww] = lds(result_row(ww, r) + HD * 4); M = fmaxf(M, mw[ww]); }
-                    float val = M;
-                    if (d != HD) {
-                        val = 0.f;
 #pragma unroll
-                        for (int ww = 0; ww < GROUP_WARPS; ++ww) {
-                            const float e = (mw[ww] == -INFINITY) ? 0.f : fast_exp2(mw[ww] - M);
-                            val = fmaf(lds(result_row(ww, r) + (d < HD ? d : HD + 1) * 4), e, val);
+                    for (int ww = 0; ww < GROUP_WARPS; ++ww) e[ww] = (mw[ww] == -INFINITY) ? 0.f : fast_exp2(mw[ww] - M);
+                    for (int d = lane; d < HD + 2; d += 32) {
+                        float val = M;
+                        if (d != HD) {
+                            val = 0.f;
+#pragma unroll
+                            for (int ww = 0; ww < GROUP_WARPS; ++ww)
+                                val = fmaf(lds(result_row(ww, r) + (d < HD ? d : HD + 1) * 4), e[ww], val);
                         }
+                        dst[r * (HD + 2) + d] = val;
                     }
-                    dst[i] = val;
                 }
                 // the next writes to these rows come from TMA
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
