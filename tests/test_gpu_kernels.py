@@ -504,6 +504,32 @@ def test_prefill_when_every_block_of_keys_raises_the_maximum(prefill):
     close(fast, want, 1.5e-2)
 
 
+def test_prefill_tcgen05_kernel_beyond_the_items_it_keeps_in_shared_memory():
+    """A portion so long that a persistent CTA walks more items than it describes up front in shared memory (64): the
+    later ones are worked out when they are met.  Against the mma.sync kernel on the same 40,000 tokens."""
+    o = ops()
+    n_q, n_kv, hd, page, T = 32, 8, 128, 16, 40000
+    torch.manual_seed(0)
+    width = (T + page - 1) // page
+    perm = torch.randperm(width + 3)[:width].reshape(1, width).to(torch.int32).to(DEV)
+    cache = (torch.randn(width + 3, 2, n_kv, page, hd, device=DEV) * 0.5).to(torch.bfloat16)
+    q = (torch.randn(T, n_q * hd, device=DEV) * 0.5).to(torch.bfloat16)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)  # noqa: E731
+    st, outs = status(), {}
+    for force in ("tc", "mma"):
+        qpc = o.attention_prefill_q_per_cta(torch.bfloat16, n_q, n_kv, hd, page, force)
+        tiles = sorted(((0, off) for off in range(0, T, qpc)), key=lambda t: -t[1])
+        if force == "tc":
+            assert len(tiles) * n_kv > 64 * torch.cuda.get_device_properties(0).multi_processor_count
+        out = torch.zeros(T, n_q * hd, device=DEV, dtype=torch.bfloat16)
+        o.attention_prefill(q=q, out=out, cache=cache, block_table=perm, q_start=dev(np.array([0, T])), kv_len=dev(np.array([T])),
+                            n_q=n_q, n_kv=n_kv, head_dim=hd, page_size=page, window=0, scale=1 / math.sqrt(hd), status=st,
+                            work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), force=force)
+        outs[force] = out.float()
+    assert st.item() == 0
+    close(outs["tc"], outs["mma"].double().cpu(), 1.5e-2)
+
+
 def test_attention_refuses_unsupported_sizes():
     from rustingstrata_b200.kernels.ops import KernelError
     with pytest.raises(KernelError, match="head size"):
