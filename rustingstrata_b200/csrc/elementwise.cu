@@ -216,19 +216,22 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
                                             const int* __restrict__ seq_of_token,
                                             const int* __restrict__ block_table, int table_stride, int page_size,
                                             __nv_bfloat16* __restrict__ cache, long page_stride, int num_pages, int write_kv,
-                                            int n_tokens, int lanes_per_head, int* status) {
+                                            int n_tokens, int lanes_shift, int page_shift, int* status) {
     struct alignas(2 * E) Vec { uint32_t w[E / 2]; };           // E bfloat16 values
+    const int lanes_per_head = 1 << lanes_shift;
     pdl_launch_dependents();
     // Positions, block tables, norm weights and the rotation table are in place before the step's first kernel, so they
     // are fetched here, while the projection before this kernel is still at work; only qkv has to wait for it.
     const int heads_per_token = n_q + (write_kv ? 2 * n_kv : 0);
-    const int heads_per_warp = 32 / lanes_per_head;
+    // The kernel is bound by instructions (over 400 per warp for 16 elements a lane), so token and head come without a
+    // division: blockIdx.x is the token, blockIdx.y and the thread number give the head; lanes per head and, where it
+    // is one, the page size are powers of two.
     const int lane = threadIdx.x & 31;
-    // 32-bit arithmetic: the launcher takes this kernel only while tokens x heads stays below 2^31
-    const unsigned unit = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (unsigned)heads_per_warp + (unsigned)(lane / lanes_per_head);
-    const int sub = lane % lanes_per_head;
-    const bool live = unit < (unsigned)n_tokens * (unsigned)heads_per_token;
-    const int t = live ? (int)(unit / (unsigned)heads_per_token) : 0, h = live ? (int)(unit - (unsigned)t * (unsigned)heads_per_token) : 0;
+    const int sub = lane & (lanes_per_head - 1);
+    const int t = blockIdx.x;
+    const int head = (int)((blockIdx.y * blockDim.x + threadIdx.x) >> lanes_shift);
+    const bool live = head < heads_per_token;
+    const int h = live ? head : 0;
     const int pos = positions[(size_t)t * pos_stride];                  // stream 0: where the token lies in the cache
     const int rpos = positions[(size_t)t * pos_stride + rot_stream];    // the stream this layer's rotation follows
     __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
@@ -237,14 +240,16 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     const bool bad_pos = rpos < 0 || rpos >= table_rows;
     if (bad_pos) ok = false;
     if (h >= n_q) {
-        const int kvh = (h - n_q) % n_kv;
-        is_v = (h - n_q) / n_kv != 0;
-        const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
+        const int plane = h - n_q;                                       // (K|V) * n_kv + kv head: the page's planes in that order
+        is_v = plane >= n_kv;
+        const int block = page_shift >= 0 ? pos >> page_shift : pos / page_size;
+        const int in_page = pos - block * page_size;
+        const int page = block_table[(size_t)seq_of_token[t] * table_stride + block];
         if (page < 0 || page >= num_pages) {
             bad_page = sub == 0 && live;
             ok = false;
         } else {
-            dst = cache + (size_t)page * page_stride + ((size_t)((is_v ? 1 : 0) * n_kv + kvh) * page_size + (pos % page_size)) * hd;
+            dst = cache + (size_t)page * page_stride + ((size_t)plane * page_size + in_page) * hd;
         }
     }
     const __nv_bfloat16* w = h < n_q ? q_w : k_w;
@@ -299,7 +304,7 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* qkv, long row_stride,
     for (int u = 0; u < E; ++u) { ss = fmaf(a[u], a[u], ss); ss = fmaf(b[u], b[u], ss); }
     for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // within the head's lanes
     if (!mine || is_v) return;
-    const float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;
+    const float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;       // as the row norms compute it
     float ra[E], rb[E];
 #pragma unroll
     for (int u = 0; u < E; ++u) {
@@ -335,14 +340,18 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
                           ((long)q_w & 15) == 0 && ((long)k_w & 15) == 0;
         int lanes = hd / (wide ? 16 : 8);                     // lanes a head needs; a power of two packs several heads per warp
         if (lanes & (lanes - 1)) lanes = 32;
-        const long heads_per_warp = 32 / lanes;
-        const long nwarps = (warps + heads_per_warp - 1) / heads_per_warp;
-        const long nblocks = (nwarps * 32 + threads - 1) / threads;
+        int lanes_shift = 0;
+        while ((1 << lanes_shift) < lanes) ++lanes_shift;
+        int page_shift = -1;
+        if ((page_size & (page_size - 1)) == 0) { page_shift = 0; while ((1 << page_shift) < page_size) ++page_shift; }
+        const int token_threads = (n_q + (write_kv ? 2 * n_kv : 0)) << lanes_shift;       // threads a token's heads need
+        const int rope_threads = 128;
+        const dim3 rope_grid((unsigned)n_tokens, (unsigned)((token_threads + rope_threads - 1) / rope_threads));
         auto kern = wide ? qk_norm_rope_kv_bf16_kernel<8> : qk_norm_rope_kv_bf16_kernel<4>;
-        return rs_launch_pdl(kern, dim3((unsigned)nblocks), dim3(threads), 0, (cudaStream_t)stream,
+        return rs_launch_pdl(kern, rope_grid, dim3(rope_threads), 0, (cudaStream_t)stream,
                              (__nv_bfloat16*)qkv, row_stride, n_q, n_kv, hd, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, eps,
                              cos_sin, table_rows, positions, pos_stride, rot_stream, seq_of_token, block_table, table_stride,
-                             page_size, (__nv_bfloat16*)cache, page_stride, num_pages, write_kv, n_tokens, lanes, status);
+                             page_size, (__nv_bfloat16*)cache, page_stride, num_pages, write_kv, n_tokens, lanes_shift, page_shift, status);
     }
     RS_DISPATCH_DTYPE(dt, T,
         return rs_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
