@@ -17,6 +17,7 @@ present, else from the fallback figures of this pool.
 ``--batch``, prompts of ``--prompt-len`` tokens): the step is timed whole and again with that family's launches left out
 (the results are then wrong, only the clock is read).  The difference is what the family adds to the step with all the
 overlap between neighbouring kernels that programmatic dependent launch gives, which a kernel timed alone cannot show.
+``--marginal-prefill``: the same for the step that runs one whole prompt of ``--prompt-len`` tokens.
 
 ``--workload 14b-mixed``: Qwen3-14B layer sizes, 32 requests with prompts of 128 to 4,096
 random tokens, all present at the start, run by the engine's scheduler with portions of 512
